@@ -1,0 +1,106 @@
+/*
+ * venom_b200 C ABI: V:N:M (VENOM) sparse x dense matrix product for NVIDIA B200 (sm_100a).
+ *
+ * Every entry point returns 0 on success and a non-zero VNM_ERR_* code otherwise; none of them exits
+ * or throws.  vnm_last_error_string() returns the message of the last failure on the calling thread.
+ * All data pointers are DEVICE pointers owned by the caller unless a name ends in _host.  `stream`
+ * is a cudaStream_t passed as void* (NULL = the legacy default stream); work is asynchronous on it.
+ *
+ * Storage format ("reference format"): the three arrays of the reference's Format_sr_nm<half>
+ * (src/format/format_sr_nm.cpp:53-60 of UDC-GAC/venom), bit-for-bit:
+ *   values   fp16[M * Ksp]              Ksp = ROUND_UP(ceil(K/m) * 2, 16)
+ *   metadata u32 [(M/2) * (Ksp/8)]      2-bit positions, 16 per word, two rows per word
+ *   colloc   u32 [(M/V) * (Ksp/2) * 4]  four ascending column offsets in [0,m) per V x m block
+ * n must be 2, m >= 4, V % 32 == 0, M % V == 0.  The SpMM additionally needs V in {32, 64, 128}.
+ */
+#ifndef VENOM_B200_H_
+#define VENOM_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+    VNM_OK = 0,
+    VNM_ERR_BAD_ARG = 1,     /* shape / alignment / null pointer */
+    VNM_ERR_CUDA = 2,        /* a CUDA runtime or driver call failed */
+    VNM_ERR_UNSUPPORTED = 3, /* valid format, but not implemented by the kernels (e.g. V = 96) */
+    VNM_ERR_DEVICE_TIMEOUT = 4 /* a bounded device-side wait gave up; the context stays usable */
+};
+
+/* Output layouts of vnm_spmm_f16. */
+enum {
+    VNM_LAYOUT_MN = 0, /* out[r * ldo + c]: [M, N] row-major, the CLI kernel's layout */
+    VNM_LAYOUT_NM = 1  /* out[c * ldo + r] = fp16(acc) + bias[r]: [N, M] row-major, the torch op's layout */
+};
+
+typedef struct vnm_prepared_s *vnm_handle_t;
+
+const char *vnm_last_error_string(void);
+int vnm_version(void);
+
+/* Array sizes of the reference format.
+ * Replaces: the size arithmetic of Format_sr_nm<T>::init, src/format/format_sr_nm.cpp:53-60. */
+int vnm_sizes(int M, int K, int V, int n, int m,
+              int64_t *ksp, int64_t *values_elems, int64_t *meta_words, int64_t *colloc_words);
+
+/* Dense -> V:N:M compressor and metadata packer (CUDA).
+ * Replaces: Format_sr_nm<T>::init_from_dense -> to_sparse_sr_nm, src/format/format_sr_nm.cpp:108-149,
+ * 419-543, and its Python twin to_sparse_sr_nm, end2end/grouped_nmv_tensor.py:487-675.
+ *   dense   fp16 [M, K] row-major with leading dimension ldd (already pruned to the pattern)
+ *   mask    optional int32 [M, K] (same ldd): kept entries are mask != 0 (Python twin); NULL = kept
+ *           entries are the non-zero values (C++ reference)
+ *   colloc  column-loc, an input exactly as in the reference
+ *   values, meta  outputs, fully overwritten
+ *   violations    optional device counter (unsigned 64-bit), incremented by the number of (row, group)
+ *                 pairs that did not yield exactly two kept entries (the reference is undefined there;
+ *                 this library keeps the first two and zero-fills missing slots) */
+int vnm_compress_f16(const void *dense, int64_t ldd, const int32_t *mask, const uint32_t *colloc,
+                     int M, int K, int V, int n, int m,
+                     void *values, uint32_t *meta, unsigned long long *violations, void *stream);
+
+/* V:N:M -> dense decompressor (CUDA).  dense [M, K] fp16, leading dimension ldd, fully overwritten.
+ * Replaces: Format_sr_nm<T>::to_dense, src/format/format_sr_nm.cpp:327-417. */
+int vnm_decompress_f16(const void *values, const uint32_t *meta, const uint32_t *colloc,
+                       int M, int K, int V, int n, int m, void *dense, int64_t ldd, void *stream);
+
+/* Re-pack reference-format arrays into the kernel-private layout and return a handle that owns only
+ * that private copy (the inputs may be freed once `stream` has drained).
+ * Replaces: BlockwiseSpMatrix<half>::init_sparse + transform_and_sync_device,
+ * include/spatha/block_sparse/spmm/blockwise_format.h:248-283,327-373, and
+ * Format_sr_nm<T>::transform_and_sync_device, src/format/format_sr_nm.cpp:239-285. */
+int vnm_prepare(const void *values, const uint32_t *meta, const uint32_t *colloc,
+                int M, int K, int V, int n, int m, vnm_handle_t *handle, void *stream);
+int vnm_prepared_bytes(int M, int K, int V, int n, int m, int64_t *bytes);
+int vnm_destroy(vnm_handle_t handle);
+
+/* out = A_vnm * B (+ bias), fp16 in, fp32 accumulate, fp16 out.
+ * Replaces: SpmmNMInitFn_t / SpmmNMExecFn_t -> SpmmBlockwiseOp::initialize / operator(),
+ * include/spatha/block_sparse/spmm/blockwise_op.h:90-161,209-246 (layout MN, bias must be NULL) and
+ * spmm_cuda, end2end/spatha_mod/block_sparse/spmm/blockwise_library.cu:294-386 (layout NM + bias).
+ *   B    fp16 [K, N] row-major, leading dimension ldb (ldb % 8 == 0, 16-byte aligned base)
+ *   bias fp16 [M] or NULL (layout NM only)
+ *   out  fp16, leading dimension ldo (ldo % 8 == 0 for layout MN), 16-byte aligned base
+ * N must be a multiple of 8. */
+int vnm_spmm_f16(vnm_handle_t handle, const void *B, int64_t ldb, int N,
+                 const void *bias, void *out, int64_t ldo, int layout, void *stream);
+
+/* Same product with HOST buffers: copies B (and bias) to the device, runs vnm_spmm_f16 and copies the
+ * result back, all on `stream`, then synchronises it.  Device staging buffers are owned by the handle
+ * and grown on demand.  B_host [K, N] and out_host are dense row-major ([M,N] or [N,M]). */
+int vnm_spmm_f16_host(vnm_handle_t handle, const void *B_host, int N, const void *bias_host,
+                      void *out_host, int layout, void *stream);
+
+/* Reads and clears the sticky device-side status word of the handle (0 = no bounded wait ever gave
+ * up).  Synchronises `stream`. */
+int vnm_device_status(vnm_handle_t handle, int *status, void *stream);
+
+/* Kernel configuration that vnm_spmm_f16 would launch for this handle and N (for reporting). */
+int vnm_spmm_config(vnm_handle_t handle, int N, int *tile_m, int *tile_n, int *stages, int *grid, int *smem_bytes);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* VENOM_B200_H_ */

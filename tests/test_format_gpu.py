@@ -1,0 +1,107 @@
+"""GPU parity tests of the format kernels (compressor + metadata packer, decompressor) through the C
+ABI, bit-exact against the CPU oracle and the golden vectors of the reference."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+SHAPES = [
+    # (M, K, V, m)
+    (64, 64, 32, 4), (64, 128, 64, 8), (128, 256, 128, 16), (256, 512, 128, 32), (128, 280, 64, 10),
+    (64, 140, 32, 7), (64, 100, 32, 8), (64, 99, 32, 8), (64, 98, 32, 8), (1024, 4096, 64, 8),
+    (4096, 1024, 128, 4), (1024, 1024, 32, 32), (512, 2000, 64, 20), (256, 4000, 128, 100),
+]
+
+
+def _u16(a):
+    return np.ascontiguousarray(a).view(np.uint16)
+
+
+@pytest.fixture(scope="module")
+def capi():
+    import torch
+    assert torch.cuda.is_available(), "GPU tests need a CUDA device"
+    from venom_b200 import capi
+    capi.lib()
+    return capi
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+def test_compress_decompress_bit_exact(capi, oracle, shape):
+    import torch
+    from venom_b200.synth import random_vnm_dense
+    M, K, V, m = shape
+    dense, cols, mask = random_vnm_dense(M, K, V, m, seed=hash(shape) % 1000)
+    ov, om, obad = oracle.compress(dense, cols, V, m)
+    assert obad == 0
+    d = torch.from_numpy(dense).cuda()
+    c = torch.from_numpy(cols.view(np.int32)).cuda()
+    v, me, bad = capi.compress(d, c, V, m)
+    assert bad == 0
+    assert np.array_equal(_u16(v.cpu().numpy()), _u16(ov))
+    assert np.array_equal(me.cpu().numpy().view(np.uint32), om)
+    # mask mode (Python-twin semantics) gives the same arrays on contract-conforming input
+    v2, me2, bad2 = capi.compress(d, c, V, m, mask=torch.from_numpy(mask).cuda())
+    assert bad2 == 0 and torch.equal(v2, v) and torch.equal(me2, me)
+    back = capi.decompress(v, me, c, M, K, V, m)
+    assert np.array_equal(_u16(back.cpu().numpy()), _u16(oracle.to_dense(ov, om, cols, M, K, V, m)))
+    assert np.array_equal(_u16(back.cpu().numpy()), _u16(dense))
+
+
+@pytest.mark.parametrize("i", range(10))
+def test_compress_matches_reference_golden(capi, golden_format, i):
+    import torch
+    p = "fmt%d_" % i
+    M, K, V, m = (int(x) for x in golden_format[p + "shape"])
+    d = torch.from_numpy(golden_format[p + "dense"].view(np.float16).reshape(M, K).copy()).cuda()
+    c = torch.from_numpy(golden_format[p + "columns"].view(np.int32).copy()).cuda()
+    v, me, bad = capi.compress(d, c, V, m)
+    assert bad == 0
+    assert np.array_equal(_u16(v.cpu().numpy()), golden_format[p + "values"])
+    assert np.array_equal(me.cpu().numpy().view(np.uint32), golden_format[p + "meta"])
+    back = capi.decompress(v, me, c, M, K, V, m)
+    assert np.array_equal(_u16(back.cpu().numpy()).reshape(-1), golden_format[p + "to_dense"].reshape(-1))
+
+
+@pytest.mark.parametrize("i", range(3))
+def test_decompress_reference_random_instances(capi, golden_format, i):
+    import torch
+    p = "rnd%d_" % i
+    M, K, V, m = (int(x) for x in golden_format[p + "shape"])
+    v = torch.from_numpy(golden_format[p + "values"].view(np.float16).copy()).cuda()
+    me = torch.from_numpy(golden_format[p + "meta"].view(np.int32).copy()).cuda()
+    c = torch.from_numpy(golden_format[p + "columns"].view(np.int32).copy()).cuda()
+    back = capi.decompress(v, me, c, M, K, V, m)
+    assert np.array_equal(_u16(back.cpu().numpy()).reshape(-1), golden_format[p + "to_dense"].reshape(-1))
+
+
+def test_violations_are_counted_and_mask_mode_keeps_zeros(capi, oracle):
+    import torch
+    from venom_b200.synth import random_vnm_dense
+    M, K, V, m = 128, 256, 64, 8
+    dense, cols, mask = random_vnm_dense(M, K, V, m, seed=5)
+    kept = np.argwhere(mask)
+    for r, c in kept[[3, 500, 4000]]:
+        dense[r, c] = 0                       # three kept entries become exact zeros
+    d = torch.from_numpy(dense).cuda()
+    c = torch.from_numpy(cols.view(np.int32)).cuda()
+    v, me, bad = capi.compress(d, c, V, m)
+    ov, om, obad = oracle.compress(dense, cols, V, m)
+    assert bad == obad == 3
+    assert np.array_equal(_u16(v.cpu().numpy()), _u16(ov)) and np.array_equal(me.cpu().numpy().view(np.uint32), om)
+    v2, me2, bad2 = capi.compress(d, c, V, m, mask=torch.from_numpy(mask).cuda())
+    ov2, om2, obad2 = oracle.compress(dense, cols, V, m, mask=mask)
+    assert bad2 == obad2 == 0
+    assert np.array_equal(_u16(v2.cpu().numpy()), _u16(ov2)) and np.array_equal(me2.cpu().numpy().view(np.uint32), om2)
+
+
+def test_compress_strided_dense(capi, oracle):
+    import torch
+    from venom_b200.synth import random_vnm_dense
+    M, K, V, m = 128, 256, 32, 16
+    dense, cols, _ = random_vnm_dense(M, K, V, m, seed=9)
+    big = torch.zeros((M, K + 64), dtype=torch.float16, device="cuda")
+    big[:, :K] = torch.from_numpy(dense).cuda()
+    v, me, bad = capi.compress(big[:, :K], torch.from_numpy(cols.view(np.int32)).cuda(), V, m)
+    ov, om, _ = oracle.compress(dense, cols, V, m)
+    assert bad == 0 and np.array_equal(_u16(v.cpu().numpy()), _u16(ov)) and np.array_equal(me.cpu().numpy().view(np.uint32), om)

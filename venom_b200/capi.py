@@ -1,0 +1,164 @@
+"""ctypes binding of the C ABI (include/venom_b200.h).
+
+PyTorch is used only for device memory and streams: every wrapper takes CUDA tensors, passes their
+data pointers through the C ABI and runs on torch's current stream.  There is no CPU fallback: loading
+fails loudly if the library has not been built, and every call raises VenomError on a non-zero status.
+"""
+import ctypes as C
+import os
+
+import torch
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "libvenom_b200.so")
+
+VNM_LAYOUT_MN = 0
+VNM_LAYOUT_NM = 1
+
+
+class VenomError(RuntimeError):
+    pass
+
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise VenomError("venom_b200 CUDA library is not built: run `python -m venom_b200.build` "
+                             "(expected %s)" % LIB_PATH)
+        L = C.CDLL(LIB_PATH)
+        i64p = C.POINTER(C.c_int64)
+        L.vnm_last_error_string.restype = C.c_char_p
+        L.vnm_version.restype = C.c_int
+        L.vnm_sizes.argtypes = [C.c_int] * 5 + [i64p] * 4
+        L.vnm_compress_f16.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p] + [C.c_int] * 5 + [C.c_void_p] * 4
+        L.vnm_decompress_f16.argtypes = [C.c_void_p] * 3 + [C.c_int] * 5 + [C.c_void_p, C.c_int64, C.c_void_p]
+        L.vnm_prepare.argtypes = [C.c_void_p] * 3 + [C.c_int] * 5 + [C.POINTER(C.c_void_p), C.c_void_p]
+        L.vnm_prepared_bytes.argtypes = [C.c_int] * 5 + [i64p]
+        L.vnm_destroy.argtypes = [C.c_void_p]
+        L.vnm_spmm_f16.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_void_p, C.c_void_p, C.c_int64,
+                                   C.c_int, C.c_void_p]
+        L.vnm_spmm_f16_host.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]
+        L.vnm_device_status.argtypes = [C.c_void_p, C.POINTER(C.c_int), C.c_void_p]
+        L.vnm_spmm_config.argtypes = [C.c_void_p, C.c_int] + [C.POINTER(C.c_int)] * 5
+        for name in ("vnm_sizes", "vnm_compress_f16", "vnm_decompress_f16", "vnm_prepare", "vnm_prepared_bytes",
+                     "vnm_destroy", "vnm_spmm_f16", "vnm_spmm_f16_host", "vnm_device_status", "vnm_spmm_config"):
+            getattr(L, name).restype = C.c_int
+        _lib = L
+    return _lib
+
+
+def _check(rc):
+    if rc != 0:
+        raise VenomError("venom_b200 error %d: %s" % (rc, lib().vnm_last_error_string().decode()))
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _need_cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise VenomError("expected CUDA tensors (there is no CPU path)")
+
+
+def sizes(M, K, V, m, n=2):
+    """(Ksp, values_elems, meta_words, colloc_words) from the library."""
+    out = [C.c_int64() for _ in range(4)]
+    _check(lib().vnm_sizes(M, K, V, n, m, *[C.byref(o) for o in out]))
+    return tuple(int(o.value) for o in out)
+
+
+def compress(dense, colloc, V, m, n=2, mask=None, count_violations=True):
+    """dense: [M,K] fp16 CUDA (pruned); colloc: int32/uint32 CUDA.  Returns (values fp16, meta int32,
+    violations int or None).  Reading the violation count synchronises the stream."""
+    _need_cuda(dense, colloc, mask)
+    if dense.dtype != torch.float16 or dense.dim() != 2 or dense.stride(1) != 1:
+        raise VenomError("dense must be a 2-D fp16 tensor with unit inner stride")
+    M, K = dense.shape
+    ksp, nv, nm, nc = sizes(M, K, V, m, n)
+    if colloc.numel() != nc or colloc.element_size() != 4 or not colloc.is_contiguous():
+        raise VenomError("colloc must hold %d 32-bit words" % nc)
+    if mask is not None and (mask.dtype != torch.int32 or tuple(mask.shape) != (M, K) or mask.stride() != dense.stride()):
+        raise VenomError("mask must be int32 with the shape and strides of dense")
+    values = torch.empty(nv, dtype=torch.float16, device=dense.device)
+    meta = torch.empty(nm, dtype=torch.int32, device=dense.device)
+    viol = torch.zeros(1, dtype=torch.int64, device=dense.device) if count_violations else None
+    _check(lib().vnm_compress_f16(dense.data_ptr(), dense.stride(0), None if mask is None else mask.data_ptr(),
+                                  colloc.data_ptr(), M, K, V, n, m, values.data_ptr(), meta.data_ptr(),
+                                  None if viol is None else viol.data_ptr(), _stream()))
+    return values, meta, (int(viol.item()) if viol is not None else None)
+
+
+def decompress(values, meta, colloc, M, K, V, m, n=2):
+    _need_cuda(values, meta, colloc)
+    dense = torch.empty((M, K), dtype=torch.float16, device=values.device)
+    _check(lib().vnm_decompress_f16(values.data_ptr(), meta.data_ptr(), colloc.data_ptr(), M, K, V, n, m,
+                                    dense.data_ptr(), K, _stream()))
+    return dense
+
+
+class Prepared:
+    """Owns a vnm_handle_t: the kernel-private copy of one sparse operand."""
+
+    def __init__(self, values, meta, colloc, M, K, V, m, n=2):
+        _need_cuda(values, meta, colloc)
+        ksp, nv, nm, nc = sizes(M, K, V, m, n)
+        if values.numel() != nv or meta.numel() != nm or colloc.numel() != nc:
+            raise VenomError("array sizes do not match the format (%d, %d, %d expected)" % (nv, nm, nc))
+        if values.dtype != torch.float16 or meta.element_size() != 4 or colloc.element_size() != 4:
+            raise VenomError("values must be fp16, metadata and colloc 32-bit")
+        self.M, self.K, self.V, self.m, self.n = M, K, V, m, n
+        self.device = values.device
+        self._h = C.c_void_p()
+        _check(lib().vnm_prepare(values.data_ptr(), meta.data_ptr(), colloc.data_ptr(), M, K, V, n, m,
+                                 C.byref(self._h), _stream()))
+
+    def close(self):
+        if getattr(self, "_h", None) is not None and self._h.value:
+            lib().vnm_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def spmm(self, B, bias=None, layout=VNM_LAYOUT_MN, out=None):
+        """B: [K,N] fp16 CUDA (unit inner stride).  Returns [M,N] (layout MN) or [N,M] (layout NM)."""
+        _need_cuda(B, bias, out)
+        if B.dtype != torch.float16 or B.dim() != 2 or B.shape[0] != self.K or B.stride(1) != 1:
+            raise VenomError("B must be a [K,N] fp16 tensor with unit inner stride (K=%d)" % self.K)
+        N = B.shape[1]
+        if out is None:
+            shape = (self.M, N) if layout == VNM_LAYOUT_MN else (N, self.M)
+            out = torch.empty(shape, dtype=torch.float16, device=B.device)
+        if bias is not None and (bias.dtype != torch.float16 or bias.numel() != self.M or not bias.is_contiguous()):
+            raise VenomError("bias must be a contiguous fp16 vector of M elements")
+        _check(lib().vnm_spmm_f16(self._h, B.data_ptr(), B.stride(0), N, None if bias is None else bias.data_ptr(),
+                                  out.data_ptr(), out.stride(0), layout, _stream()))
+        return out
+
+    def spmm_host(self, B_host, out_host, bias_host=None, layout=VNM_LAYOUT_MN):
+        """End-to-end call with HOST tensors (ideally pinned): H2D, kernel, D2H, synchronise."""
+        N = B_host.shape[1]
+        _check(lib().vnm_spmm_f16_host(self._h, B_host.data_ptr(), N, None if bias_host is None else bias_host.data_ptr(),
+                                       out_host.data_ptr(), layout, _stream()))
+        return out_host
+
+    def device_status(self):
+        st = C.c_int(0)
+        rc = lib().vnm_device_status(self._h, C.byref(st), _stream())
+        if rc != 0:
+            raise VenomError("venom_b200 error %d: %s" % (rc, lib().vnm_last_error_string().decode()))
+        return int(st.value)
+
+    def config(self, N):
+        v = [C.c_int() for _ in range(5)]
+        _check(lib().vnm_spmm_config(self._h, N, *[C.byref(x) for x in v]))
+        return dict(zip(("tile_m", "tile_n", "stages", "grid", "smem_bytes"), (int(x.value) for x in v)))

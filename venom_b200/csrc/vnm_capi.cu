@@ -1,0 +1,305 @@
+// C ABI of venom_b200 (see include/venom_b200.h).  Host-side argument checking, the prepared-operand
+// handle, TMA descriptor construction for the dense operand, and kernel dispatch.
+#include "../../include/venom_b200.h"
+#include "vnm_internal.h"
+
+#include <cstdio>
+#include <cstdarg>
+#include <cstring>
+#include <new>
+#include <string>
+
+using namespace vnm;
+
+namespace {
+
+thread_local std::string g_last_error;
+
+int fail(int code, const char *fmt, ...)
+{
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    g_last_error = buf;
+    return code;
+}
+
+int fail_cuda(cudaError_t e, const char *what)
+{
+    return fail(VNM_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+}
+
+#define VNM_CUDA(call, what)                                   \
+    do {                                                       \
+        cudaError_t e__ = (call);                              \
+        if (e__ != cudaSuccess) return fail_cuda(e__, what);   \
+    } while (0)
+
+int check_format(int M, int K, int V, int n, int m)
+{
+    if (n != 2) return fail(VNM_ERR_BAD_ARG, "n must be 2 (got %d)", n);
+    if (m < 4) return fail(VNM_ERR_BAD_ARG, "m must be >= 4 (got %d)", m);
+    if (M <= 0 || K <= 0 || V <= 0) return fail(VNM_ERR_BAD_ARG, "M, K, V must be positive (got %d, %d, %d)", M, K, V);
+    if (V % 32 != 0) return fail(VNM_ERR_BAD_ARG, "V must be a multiple of 32 (got %d)", V);
+    if (M % V != 0) return fail(VNM_ERR_BAD_ARG, "M (%d) must be a multiple of V (%d)", M, V);
+    if ((int64_t)K + m >= (int64_t)1 << 30) return fail(VNM_ERR_BAD_ARG, "K too large");
+    return VNM_OK;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn()
+{
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+bool g_kernels_ready = false;
+
+}  // namespace
+
+struct vnm_prepared_s {
+    int M, K, V, n, m;
+    int64_t Ksp;
+    int mtiles, ktiles, nb, vblocks_padded;
+    int device;
+    void *am;
+    void *rows;
+    int *status;
+    // cached TMA descriptor of the last dense operand
+    const void *tm_B;
+    int64_t tm_ldb;
+    int tm_N;
+    bool tm_valid;
+    CUtensorMap tmap;
+    // device staging of the host-buffer entry point
+    void *stage_B;
+    size_t stage_B_bytes;
+    void *stage_out;
+    size_t stage_out_bytes;
+    void *stage_bias;
+};
+
+extern "C" {
+
+const char *vnm_last_error_string(void) { return g_last_error.c_str(); }
+
+int vnm_version(void) { return 100; }
+
+int vnm_sizes(int M, int K, int V, int n, int m, int64_t *ksp, int64_t *values_elems, int64_t *meta_words, int64_t *colloc_words)
+{
+    int rc = check_format(M, K, V, n, m);
+    if (rc) return rc;
+    const int64_t Ksp = ksp_of(K, m);
+    if (ksp) *ksp = Ksp;
+    if (values_elems) *values_elems = (int64_t)M * Ksp;
+    if (meta_words) *meta_words = (int64_t)(M / 2) * (Ksp / 8);
+    if (colloc_words) *colloc_words = (int64_t)(M / V) * (Ksp / 2) * 4;
+    return VNM_OK;
+}
+
+int vnm_compress_f16(const void *dense, int64_t ldd, const int32_t *mask, const uint32_t *colloc, int M, int K, int V, int n, int m,
+                     void *values, uint32_t *meta, unsigned long long *violations, void *stream)
+{
+    int rc = check_format(M, K, V, n, m);
+    if (rc) return rc;
+    if (!dense || !colloc || !values || !meta) return fail(VNM_ERR_BAD_ARG, "vnm_compress_f16: null pointer");
+    if (ldd < K) return fail(VNM_ERR_BAD_ARG, "vnm_compress_f16: ldd (%lld) < K (%d)", (long long)ldd, K);
+    if (((uintptr_t)colloc & 15) || ((uintptr_t)values & 15)) return fail(VNM_ERR_BAD_ARG, "vnm_compress_f16: colloc/values must be 16-byte aligned");
+    VNM_CUDA(launch_compress(dense, ldd, mask, colloc, M, K, V, m, values, meta, violations, (cudaStream_t)stream), "compress launch");
+    return VNM_OK;
+}
+
+int vnm_decompress_f16(const void *values, const uint32_t *meta, const uint32_t *colloc, int M, int K, int V, int n, int m,
+                       void *dense, int64_t ldd, void *stream)
+{
+    int rc = check_format(M, K, V, n, m);
+    if (rc) return rc;
+    if (!dense || !colloc || !values || !meta) return fail(VNM_ERR_BAD_ARG, "vnm_decompress_f16: null pointer");
+    if (ldd < K) return fail(VNM_ERR_BAD_ARG, "vnm_decompress_f16: ldd (%lld) < K (%d)", (long long)ldd, K);
+    VNM_CUDA(launch_decompress(values, meta, colloc, M, K, V, m, dense, ldd, (cudaStream_t)stream), "decompress launch");
+    return VNM_OK;
+}
+
+int vnm_prepared_bytes(int M, int K, int V, int n, int m, int64_t *bytes)
+{
+    int rc = check_format(M, K, V, n, m);
+    if (rc) return rc;
+    if (V != 32 && V != 64 && V != 128) return fail(VNM_ERR_UNSUPPORTED, "SpMM supports V in {32, 64, 128} (got %d)", V);
+    const int64_t Ksp = ksp_of(K, m);
+    const int64_t mtiles = (M + TILE_M - 1) / TILE_M, ktiles = (Ksp + KT_COMP - 1) / KT_COMP;
+    const int64_t nb = TILE_M / V;
+    if (bytes) *bytes = mtiles * ktiles * AM_BLOCK_BYTES + mtiles * nb * ktiles * KT_GROUPS * 16 + 256;
+    return VNM_OK;
+}
+
+int vnm_prepare(const void *values, const uint32_t *meta, const uint32_t *colloc, int M, int K, int V, int n, int m,
+                vnm_handle_t *handle, void *stream)
+{
+    int rc = check_format(M, K, V, n, m);
+    if (rc) return rc;
+    if (!values || !meta || !colloc || !handle) return fail(VNM_ERR_BAD_ARG, "vnm_prepare: null pointer");
+    if (V != 32 && V != 64 && V != 128) return fail(VNM_ERR_UNSUPPORTED, "SpMM supports V in {32, 64, 128} (got %d)", V);
+    if (((uintptr_t)colloc & 15) || ((uintptr_t)values & 3)) return fail(VNM_ERR_BAD_ARG, "vnm_prepare: colloc must be 16-byte and values 4-byte aligned");
+    if (!g_kernels_ready) {
+        VNM_CUDA(spmm_init_kernels(), "cudaFuncSetAttribute(max dynamic shared memory)");
+        g_kernels_ready = true;
+    }
+    vnm_prepared_s *h = new (std::nothrow) vnm_prepared_s();
+    if (!h) return fail(VNM_ERR_CUDA, "out of host memory");
+    memset(h, 0, sizeof(*h));
+    h->M = M; h->K = K; h->V = V; h->n = n; h->m = m;
+    h->Ksp = ksp_of(K, m);
+    h->mtiles = (M + TILE_M - 1) / TILE_M;
+    h->ktiles = (int)((h->Ksp + KT_COMP - 1) / KT_COMP);
+    h->nb = TILE_M / V;
+    h->vblocks_padded = h->mtiles * h->nb;
+    cudaError_t e = cudaGetDevice(&h->device);
+    if (e == cudaSuccess) e = cudaMalloc(&h->am, (size_t)h->mtiles * h->ktiles * AM_BLOCK_BYTES);
+    if (e == cudaSuccess) e = cudaMalloc(&h->rows, (size_t)h->vblocks_padded * h->ktiles * KT_GROUPS * sizeof(int4));
+    if (e == cudaSuccess) e = cudaMalloc((void **)&h->status, sizeof(int));
+    if (e == cudaSuccess) e = cudaMemsetAsync(h->status, 0, sizeof(int), (cudaStream_t)stream);
+    if (e == cudaSuccess)
+        e = launch_prepare(values, meta, colloc, M, K, V, m, h->am, h->rows, h->mtiles, h->ktiles, h->vblocks_padded, (cudaStream_t)stream);
+    if (e != cudaSuccess) {
+        vnm_destroy(h);
+        return fail_cuda(e, "vnm_prepare");
+    }
+    *handle = h;
+    return VNM_OK;
+}
+
+int vnm_destroy(vnm_handle_t h)
+{
+    if (!h) return VNM_OK;
+    cudaFree(h->am);
+    cudaFree(h->rows);
+    cudaFree(h->status);
+    cudaFree(h->stage_B);
+    cudaFree(h->stage_out);
+    cudaFree(h->stage_bias);
+    delete h;
+    return VNM_OK;
+}
+
+int vnm_spmm_config(vnm_handle_t h, int N, int *tile_m, int *tile_n, int *stages, int *grid, int *smem_bytes)
+{
+    if (!h) return fail(VNM_ERR_BAD_ARG, "null handle");
+    SpmmConfig cfg;
+    if (!spmm_select_config(h->V, N, h->M, &cfg)) return fail(VNM_ERR_UNSUPPORTED, "unsupported V");
+    if (tile_m) *tile_m = TILE_M;
+    if (tile_n) *tile_n = cfg.bn;
+    if (stages) *stages = cfg.stages;
+    if (grid) *grid = h->mtiles * ((N + cfg.bn - 1) / cfg.bn);
+    if (smem_bytes) *smem_bytes = cfg.smem_bytes;
+    return VNM_OK;
+}
+
+int vnm_spmm_f16(vnm_handle_t h, const void *B, int64_t ldb, int N, const void *bias, void *out, int64_t ldo, int layout, void *stream)
+{
+    if (!h || !B || !out) return fail(VNM_ERR_BAD_ARG, "vnm_spmm_f16: null pointer");
+    if (N <= 0 || N % 8 != 0) return fail(VNM_ERR_BAD_ARG, "vnm_spmm_f16: N (%d) must be a positive multiple of 8", N);
+    if (ldb < N || ldb % 8 != 0) return fail(VNM_ERR_BAD_ARG, "vnm_spmm_f16: ldb (%lld) must be >= N and a multiple of 8", (long long)ldb);
+    if ((uintptr_t)B & 15) return fail(VNM_ERR_BAD_ARG, "vnm_spmm_f16: B must be 16-byte aligned");
+    if (layout == VNM_LAYOUT_MN) {
+        if (bias) return fail(VNM_ERR_BAD_ARG, "vnm_spmm_f16: bias is only supported with layout NM");
+        if (ldo < N || ldo % 8 != 0 || ((uintptr_t)out & 15))
+            return fail(VNM_ERR_BAD_ARG, "vnm_spmm_f16: layout MN needs ldo >= N, ldo %% 8 == 0 and a 16-byte aligned out");
+    } else if (layout == VNM_LAYOUT_NM) {
+        if (ldo < h->M) return fail(VNM_ERR_BAD_ARG, "vnm_spmm_f16: layout NM needs ldo >= M");
+    } else {
+        return fail(VNM_ERR_BAD_ARG, "vnm_spmm_f16: unknown layout %d", layout);
+    }
+    SpmmConfig cfg;
+    if (!spmm_select_config(h->V, N, h->M, &cfg)) return fail(VNM_ERR_UNSUPPORTED, "unsupported V");
+
+    if (!h->tm_valid || h->tm_B != B || h->tm_ldb != ldb || h->tm_N != N) {
+        EncodeTiledFn enc = get_encode_fn();
+        if (!enc) return fail(VNM_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+        // B viewed as a 2-D tensor {N (contiguous), K}; one box = 64 columns of one row (128 bytes),
+        // written with the 128-byte swizzle the MMA's N-major operand layout expects.  Rows >= K and
+        // columns >= N read as zeros.
+        cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)h->K};
+        cuuint64_t strides[1] = {(cuuint64_t)ldb * 2};
+        cuuint32_t box[2] = {64, 1};
+        cuuint32_t estr[2] = {1, 1};
+        CUresult r = enc(&h->tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(B), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return fail(VNM_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+        h->tm_B = B; h->tm_ldb = ldb; h->tm_N = N; h->tm_valid = true;
+    }
+
+    SpmmParams p;
+    p.am = (const uint8_t *)h->am;
+    p.rows = (const int4 *)h->rows;
+    p.bias = (const __half *)bias;
+    p.out = (__half *)out;
+    p.ldo = ldo;
+    p.M = h->M; p.N = N; p.K = h->K; p.V = h->V;
+    p.mtiles = h->mtiles; p.ktiles = h->ktiles; p.ntiles = (N + cfg.bn - 1) / cfg.bn;
+    p.layout = layout;
+    p.status = h->status;
+    VNM_CUDA(launch_spmm(cfg, h->tmap, p, (cudaStream_t)stream), "spmm launch");
+    return VNM_OK;
+}
+
+static int grow(void **buf, size_t *cap, size_t need)
+{
+    if (*cap >= need) return VNM_OK;
+    if (*buf) cudaFree(*buf);
+    *buf = nullptr; *cap = 0;
+    cudaError_t e = cudaMalloc(buf, need);
+    if (e != cudaSuccess) return fail_cuda(e, "staging cudaMalloc");
+    *cap = need;
+    return VNM_OK;
+}
+
+int vnm_spmm_f16_host(vnm_handle_t h, const void *B_host, int N, const void *bias_host, void *out_host, int layout, void *stream)
+{
+    if (!h || !B_host || !out_host) return fail(VNM_ERR_BAD_ARG, "vnm_spmm_f16_host: null pointer");
+    if (N <= 0 || N % 8 != 0) return fail(VNM_ERR_BAD_ARG, "vnm_spmm_f16_host: N (%d) must be a positive multiple of 8", N);
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t b_bytes = (size_t)h->K * N * 2, o_bytes = (size_t)h->M * N * 2;
+    int rc;
+    if ((rc = grow(&h->stage_B, &h->stage_B_bytes, b_bytes))) return rc;
+    if ((rc = grow(&h->stage_out, &h->stage_out_bytes, o_bytes))) return rc;
+    VNM_CUDA(cudaMemcpyAsync(h->stage_B, B_host, b_bytes, cudaMemcpyHostToDevice, s), "H2D copy of B");
+    if (bias_host) {
+        if (!h->stage_bias) VNM_CUDA(cudaMalloc(&h->stage_bias, (size_t)h->M * 2), "bias cudaMalloc");
+        VNM_CUDA(cudaMemcpyAsync(h->stage_bias, bias_host, (size_t)h->M * 2, cudaMemcpyHostToDevice, s), "H2D copy of bias");
+    }
+    rc = vnm_spmm_f16(h, h->stage_B, N, N, bias_host ? h->stage_bias : nullptr, h->stage_out, layout == VNM_LAYOUT_MN ? N : h->M, layout, stream);
+    if (rc) return rc;
+    VNM_CUDA(cudaMemcpyAsync(out_host, h->stage_out, o_bytes, cudaMemcpyDeviceToHost, s), "D2H copy of the result");
+    VNM_CUDA(cudaStreamSynchronize(s), "stream synchronize");
+    return VNM_OK;
+}
+
+int vnm_device_status(vnm_handle_t h, int *status, void *stream)
+{
+    if (!h || !status) return fail(VNM_ERR_BAD_ARG, "vnm_device_status: null pointer");
+    cudaStream_t s = (cudaStream_t)stream;
+    int v = 0;
+    VNM_CUDA(cudaMemcpyAsync(&v, h->status, sizeof(int), cudaMemcpyDeviceToHost, s), "status copy");
+    VNM_CUDA(cudaStreamSynchronize(s), "stream synchronize");
+    if (v != 0) VNM_CUDA(cudaMemsetAsync(h->status, 0, sizeof(int), s), "status clear");
+    *status = v;
+    if (v != 0) return fail(VNM_ERR_DEVICE_TIMEOUT, "a bounded device-side wait gave up (status bits 0x%x)", v);
+    return VNM_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,225 @@
+// Format kernels: dense -> V:N:M compressor + metadata packer, decompressor, and the re-pack of the
+// reference-format arrays into the kernel-private layout.  All are HBM-bound byte/bit shuffles.
+#include "vnm_internal.h"
+
+namespace vnm {
+
+// ------------------------------------------------------------------------------------------------
+// Compressor.  One thread owns one metadata word = (row pair 2p,2p+1) x (tile t of four groups):
+// it scans 2 x 4 groups x 4 column-loc candidates of the pruned dense matrix in ascending order,
+// emits the first two kept entries of every (row, group) as values + 2-bit positions, and writes one
+// 32-bit metadata word plus four 8-byte value pieces.  Threads of a warp walk consecutive tiles of
+// the same row pair, so the dense reads of a warp cover 32*4*m consecutive columns of two rows.
+// Follows Format_sr_nm<T>::to_sparse_sr_nm (format_sr_nm.cpp:441-536): candidates with an original
+// column >= K contribute a (position 0, value 0) slot for j < 2 only (:486-500).
+// ------------------------------------------------------------------------------------------------
+template <bool kHasMask>
+__global__ void __launch_bounds__(256) compress_kernel(const __half *__restrict__ dense, int64_t ldd, const int32_t *__restrict__ mask,
+                                                       const uint32_t *__restrict__ colloc, int M, int K, int V, int m, int64_t Ksp,
+                                                       __half *__restrict__ values, uint32_t *__restrict__ meta,
+                                                       unsigned long long *violations)
+{
+    const int64_t tiles = Ksp / 8;
+    const int64_t total = (int64_t)(M / 2) * tiles;
+    unsigned int bad = 0;
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t rp = idx / tiles;
+        const int64_t t = idx - rp * tiles;
+        uint32_t word = 0;
+        const int64_t r0 = rp * 2;
+        const uint4 *c4p = reinterpret_cast<const uint4 *>(colloc + (r0 / V) * (Ksp / 2) * 4 + t * 16);
+        // values of rows r0, r0+1 for group gi are 4 consecutive halves at vbase + gi*8
+        const int64_t vbase = (r0 / 16) * 16 * Ksp + t * 128 + ((r0 % 16) / 4) * 32 + (r0 % 4) * 2;
+#pragma unroll
+        for (int gi = 0; gi < 4; gi++) {
+            const uint4 c4 = __ldg(c4p + gi);
+            const uint32_t cand[4] = {c4.x, c4.y, c4.z, c4.w};
+            const int64_t g = t * 4 + gi;
+            unsigned short out[4] = {0, 0, 0, 0};
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                const __half *drow = dense + (r0 + h) * ldd;
+                const int32_t *mrow = kHasMask ? mask + (r0 + h) * ldd : nullptr;
+                int pos = 0;
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const int64_t col = g * m + (int64_t)cand[j];
+                    if (col < K) {
+                        const unsigned short bits = __half_as_ushort(drow[col]);
+                        const bool keep = kHasMask ? (mrow[col] != 0) : ((bits & 0x7FFFu) != 0);  // value != +-0
+                        if (keep) {
+                            if (pos < 2) {
+                                out[h * 2 + pos] = bits;
+                                word |= (uint32_t)j << (h * 16 + gi * 4 + pos * 2);
+                            }
+                            pos++;
+                        }
+                    } else if (j < 2) {
+                        pos++;  // slot (position 0, value 0): nothing to OR in
+                    }
+                }
+                bad += (pos != 2);
+            }
+            uint2 pk;
+            pk.x = (uint32_t)out[0] | ((uint32_t)out[1] << 16);
+            pk.y = (uint32_t)out[2] | ((uint32_t)out[3] << 16);
+            *reinterpret_cast<uint2 *>(values + vbase + gi * 8) = pk;
+        }
+        meta[(r0 / 32) * 16 * tiles + t * 16 + (r0 % 32) / 2] = word;
+    }
+    if (violations != nullptr) {
+        for (int o = 16; o > 0; o >>= 1) bad += __shfl_xor_sync(0xffffffffu, bad, o);
+        if ((threadIdx.x & 31) == 0 && bad) atomicAdd(violations, (unsigned long long)bad);
+    }
+}
+
+cudaError_t launch_compress(const void *dense, int64_t ldd, const int32_t *mask, const uint32_t *colloc, int M, int K, int V, int m,
+                            void *values, uint32_t *meta, unsigned long long *violations, cudaStream_t stream)
+{
+    const int64_t Ksp = ksp_of(K, m);
+    const int64_t total = (int64_t)(M / 2) * (Ksp / 8);
+    const int threads = 256;
+    int64_t blocks = (total + threads - 1) / threads;
+    const int64_t cap = (int64_t)148 * 64;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    if (mask)
+        compress_kernel<true><<<(unsigned)blocks, threads, 0, stream>>>((const __half *)dense, ldd, mask, colloc, M, K, V, m, Ksp,
+                                                                       (__half *)values, meta, violations);
+    else
+        compress_kernel<false><<<(unsigned)blocks, threads, 0, stream>>>((const __half *)dense, ldd, mask, colloc, M, K, V, m, Ksp,
+                                                                        (__half *)values, meta, violations);
+    return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------------------
+// Decompressor (Format_sr_nm<T>::to_dense, format_sr_nm.cpp:327-417).  The output is zero-filled by
+// the caller side of the launch; one thread scatters the two values of one (row, group), slot 0
+// first, so a padded slot overwrites exactly as the reference's loop order does.
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) decompress_kernel(const __half *__restrict__ values, const uint32_t *__restrict__ meta,
+                                                         const uint32_t *__restrict__ colloc, int M, int K, int V, int m, int64_t Ksp,
+                                                         __half *__restrict__ dense, int64_t ldd)
+{
+    const int64_t G = Ksp / 2;
+    const int64_t total = (int64_t)M * G;
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = idx / G;
+        const int64_t g = idx - r * G;
+        const uint32_t w = meta[meta_index(r, g, Ksp)];
+        const uint32_t *c4 = colloc + (r / V) * G * 4 + g * 4;
+#pragma unroll
+        for (int s = 0; s < 2; s++) {
+            const uint32_t sel = (w >> meta_shift(r, g, s)) & 3u;
+            const int64_t col = g * m + (int64_t)c4[sel];
+            if (col < K) dense[r * ldd + col] = values[values_index(r, g, s, Ksp)];
+        }
+    }
+}
+
+cudaError_t launch_decompress(const void *values, const uint32_t *meta, const uint32_t *colloc, int M, int K, int V, int m,
+                              void *dense, int64_t ldd, cudaStream_t stream)
+{
+    const int64_t Ksp = ksp_of(K, m);
+    cudaError_t e = cudaMemset2DAsync(dense, (size_t)ldd * 2, 0, (size_t)K * 2, (size_t)M, stream);
+    if (e != cudaSuccess) return e;
+    const int64_t total = (int64_t)M * (Ksp / 2);
+    int64_t blocks = (total + 255) / 256;
+    const int64_t cap = (int64_t)148 * 64;
+    if (blocks > cap) blocks = cap;
+    decompress_kernel<<<(unsigned)blocks, 256, 0, stream>>>((const __half *)values, meta, colloc, M, K, V, m, Ksp, (__half *)dense, ldd);
+    return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------------------
+// Re-pack into the kernel-private layout (see vnm_common.cuh).  One thread writes one 16-byte chunk:
+// chunks [0, 1024) of a block are the swizzled value image, chunks [1024, 1152) the metadata image.
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) prepare_am_kernel(const __half *__restrict__ values, const uint32_t *__restrict__ meta, int M,
+                                                         int64_t Ksp, int mtiles, int ktiles, uint4 *__restrict__ am)
+{
+    const int chunks_per_block = AM_BLOCK_BYTES / 16;  // 1152
+    const int64_t total = (int64_t)mtiles * ktiles * chunks_per_block;
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t blk = idx / chunks_per_block;
+        const int ch = (int)(idx - blk * chunks_per_block);
+        const int mt = (int)(blk / ktiles);
+        const int kt = (int)(blk - (int64_t)mt * ktiles);
+        uint4 o = make_uint4(0, 0, 0, 0);
+        if (ch < A_IMG_BYTES / 16) {
+            const int i = ch >> 3;                  // MMA row inside the tile
+            const int cphys = ch & 7;               // stored chunk
+            const int c = cphys ^ (i & 7);          // logical chunk = 8 compressed columns = one reference tile
+            const int64_t r = (int64_t)mt * TILE_M + mma_row_to_actual(i);
+            const int64_t t = (int64_t)kt * 8 + c;  // reference tile index (four groups)
+            if (r < M && t < Ksp / 8) {
+                const __half *src = values + (r / 16) * 16 * Ksp + t * 128 + ((r % 16) / 4) * 32 + (r % 4) * 2;
+                uint32_t w[4];
+#pragma unroll
+                for (int gi = 0; gi < 4; gi++) w[gi] = *reinterpret_cast<const uint32_t *>(src + gi * 8);
+                o = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+        } else {
+            const int lane = ch - A_IMG_BYTES / 16;  // tensor-memory lane 0..127
+            const int m0 = lane & 7, k1 = (lane >> 3) & 1, m2 = lane >> 4;
+            const int64_t r = (int64_t)mt * TILE_M + m2 * 16 + m0 * 2;  // even row of the pair
+            uint32_t w[4];
+#pragma unroll
+            for (int kb = 0; kb < 4; kb++) {
+                const int64_t t = (int64_t)kt * 8 + kb * 2 + k1;
+                // padding: positions (0,1) in every group, a valid 2:4 pattern for zero values
+                w[kb] = (r < M && t < Ksp / 8) ? meta[(r / 32) * 16 * (Ksp / 8) + t * 16 + (r % 32) / 2] : 0x44444444u;
+            }
+            o = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+        am[idx] = o;
+    }
+}
+
+// Absolute B rows per (V-block, group); groups are padded to whole k-tiles and V-blocks to whole row tiles.
+__global__ void __launch_bounds__(256) prepare_rows_kernel(const uint32_t *__restrict__ colloc, int M, int K, int V, int m, int64_t Ksp,
+                                                           int vblocks_padded, int ktiles, int4 *__restrict__ rows)
+{
+    const int64_t gpad = (int64_t)ktiles * KT_GROUPS;
+    const int64_t total = (int64_t)vblocks_padded * gpad;
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t vb = idx / gpad;
+        const int64_t g = idx - vb * gpad;
+        int4 o = make_int4(K, K, K, K);
+        if (vb < M / V && g < Ksp / 2) {
+            const uint4 c4 = *reinterpret_cast<const uint4 *>(colloc + vb * (Ksp / 2) * 4 + g * 4);
+            const int64_t base = g * m;
+            const int64_t a = base + c4.x, b = base + c4.y, c = base + c4.z, d = base + c4.w;
+            o.x = a < K ? (int)a : K;
+            o.y = b < K ? (int)b : K;
+            o.z = c < K ? (int)c : K;
+            o.w = d < K ? (int)d : K;
+        }
+        rows[idx] = o;
+    }
+}
+
+cudaError_t launch_prepare(const void *values, const uint32_t *meta, const uint32_t *colloc, int M, int K, int V, int m,
+                           void *am, void *rows, int mtiles, int ktiles, int vblocks_padded, cudaStream_t stream)
+{
+    const int64_t Ksp = ksp_of(K, m);
+    {
+        const int64_t total = (int64_t)mtiles * ktiles * (AM_BLOCK_BYTES / 16);
+        int64_t blocks = (total + 255) / 256;
+        const int64_t cap = (int64_t)148 * 64;
+        if (blocks > cap) blocks = cap;
+        prepare_am_kernel<<<(unsigned)blocks, 256, 0, stream>>>((const __half *)values, meta, M, Ksp, mtiles, ktiles, (uint4 *)am);
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return e;
+    }
+    {
+        const int64_t total = (int64_t)vblocks_padded * ktiles * KT_GROUPS;
+        int64_t blocks = (total + 255) / 256;
+        const int64_t cap = (int64_t)148 * 64;
+        if (blocks > cap) blocks = cap;
+        prepare_rows_kernel<<<(unsigned)blocks, 256, 0, stream>>>(colloc, M, K, V, m, Ksp, vblocks_padded, ktiles, (int4 *)rows);
+        return cudaGetLastError();
+    }
+}
+
+}  // namespace vnm

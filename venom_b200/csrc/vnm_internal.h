@@ -1,0 +1,52 @@
+// Internal interface between the C ABI (vnm_capi.cu) and the kernel translation units.
+#pragma once
+
+#include "vnm_common.cuh"
+#include <cuda.h>
+
+namespace vnm {
+
+// Device-side status word values (sticky, OR-ed): which bounded wait gave up.
+enum : int {
+    DEV_OK = 0,
+    DEV_TIMEOUT_PRODUCER = 1,  // producer waited for a free stage
+    DEV_TIMEOUT_MMA = 2,       // MMA issuer waited for a filled stage
+    DEV_TIMEOUT_EPILOGUE = 4,  // epilogue waited for the accumulator
+    DEV_TIMEOUT_DRAIN = 8      // drain of in-flight copies after an abort gave up
+};
+
+struct SpmmParams {
+    const uint8_t *am;    // [mtiles][ktiles][AM_BLOCK_BYTES] value + metadata images
+    const int4 *rows;     // [vblocks_padded][ktiles*32] absolute B rows
+    const __half *bias;   // [M] or null
+    __half *out;
+    int64_t ldo;
+    int M, N, K;
+    int V;
+    int mtiles, ktiles, ntiles;
+    int layout;           // 0 = [M,N], 1 = [N,M] + bias
+    int *status;          // device status word
+};
+
+struct SpmmConfig {
+    int bn;      // tile N
+    int nb;      // V-blocks per 128-row tile
+    int stages;
+    int smem_bytes;
+    int threads;
+};
+
+cudaError_t launch_compress(const void *dense, int64_t ldd, const int32_t *mask, const uint32_t *colloc, int M, int K, int V, int m,
+                            void *values, uint32_t *meta, unsigned long long *violations, cudaStream_t stream);
+cudaError_t launch_decompress(const void *values, const uint32_t *meta, const uint32_t *colloc, int M, int K, int V, int m,
+                              void *dense, int64_t ldd, cudaStream_t stream);
+cudaError_t launch_prepare(const void *values, const uint32_t *meta, const uint32_t *colloc, int M, int K, int V, int m, void *am,
+                           void *rows, int mtiles, int ktiles, int vblocks_padded, cudaStream_t stream);
+
+// Chooses the tile configuration for (V, N).  Returns false for an unsupported V.
+bool spmm_select_config(int V, int N, int M, SpmmConfig *cfg);
+// One-time per-process opt-in to large dynamic shared memory for every kernel instance.
+cudaError_t spmm_init_kernels();
+cudaError_t launch_spmm(const SpmmConfig &cfg, const CUtensorMap &tmap_b, const SpmmParams &p, cudaStream_t stream);
+
+}  // namespace vnm
