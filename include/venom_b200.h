@@ -97,6 +97,17 @@ int vnm_spmm_f16_host(vnm_handle_t handle, const void *B_host, int N, const void
  * up).  Synchronises `stream`. */
 int vnm_device_status(vnm_handle_t handle, int *status, void *stream);
 
+/* Ablation switches.
+ * Gather mode: how the selected rows of B reach shared memory.  0 = TMA tile::gather4, one group of four
+ * rows per instruction (default for m > 4); 1 = plain TMA tiles of 64 consecutive rows, which is exact
+ * for m == 4 (every row is selected; the default there) and otherwise removes the column-loc
+ * indirection exactly like the reference's compile-time IDEAL_KERNEL experiment
+ * (include/spatha/block_sparse/spmm/blockwise_kernel.h:328-642, row = nz_block_idx % 4 at :536);
+ * 2 = B is not loaded at all (timing floor; results are meaningless).
+ * Producer warps: 4 or 8 warps issue the gather loads (default 8). */
+int vnm_set_gather_mode(vnm_handle_t handle, int mode);
+int vnm_set_producer_warps(vnm_handle_t handle, int warps);
+
 /* Kernel configuration that vnm_spmm_f16 would launch for this handle and N (for reporting). */
 int vnm_spmm_config(vnm_handle_t handle, int N, int *tile_m, int *tile_n, int *stages, int *grid, int *smem_bytes);
 

@@ -144,3 +144,18 @@ def test_spmm_baseline_shapes_sampled_rows(capi, oracle, shape):
     s = prep_i.spmm(B1).float() + prep_i.spmm(B2).float()
     t = prep_i.spmm(B1 + B2).float()
     assert torch.equal(s, t)
+
+
+def test_gather_modes_agree_when_every_row_is_selected(capi, oracle):
+    """m == 4: the 64-row tile loads (default) and the gather4 loads must give identical bits; both
+    producer-warp counts too."""
+    import torch
+    M, K, V, m, N = 256, 1024, 128, 4, 512
+    prep, Bd, _ = _setup(capi, oracle, M, K, V, m, N, seed=5, ints=False)
+    a = prep.spmm(Bd)
+    prep.set_gather_mode(0)
+    b = prep.spmm(Bd)
+    prep.set_producer_warps(4)
+    c = prep.spmm(Bd)
+    assert prep.device_status() == 0
+    assert torch.equal(a, b) and torch.equal(a, c)

@@ -44,6 +44,10 @@ def lib():
         L.vnm_spmm_f16_host.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]
         L.vnm_device_status.argtypes = [C.c_void_p, C.POINTER(C.c_int), C.c_void_p]
         L.vnm_spmm_config.argtypes = [C.c_void_p, C.c_int] + [C.POINTER(C.c_int)] * 5
+        L.vnm_set_gather_mode.argtypes = [C.c_void_p, C.c_int]
+        L.vnm_set_gather_mode.restype = C.c_int
+        L.vnm_set_producer_warps.argtypes = [C.c_void_p, C.c_int]
+        L.vnm_set_producer_warps.restype = C.c_int
         for name in ("vnm_sizes", "vnm_compress_f16", "vnm_decompress_f16", "vnm_prepare", "vnm_prepared_bytes",
                      "vnm_destroy", "vnm_spmm_f16", "vnm_spmm_f16_host", "vnm_device_status", "vnm_spmm_config"):
             getattr(L, name).restype = C.c_int
@@ -157,6 +161,14 @@ class Prepared:
         if rc != 0:
             raise VenomError("venom_b200 error %d: %s" % (rc, lib().vnm_last_error_string().decode()))
         return int(st.value)
+
+    def set_gather_mode(self, mode):
+        """0 = TMA gather4 (default for m > 4), 1 = 64-row TMA tiles (exact for m == 4, otherwise the
+        "no column-loc" ablation), 2 = no B loads (timing floor only)."""
+        _check(lib().vnm_set_gather_mode(self._h, mode))
+
+    def set_producer_warps(self, warps):
+        _check(lib().vnm_set_producer_warps(self._h, warps))
 
     def config(self, N):
         v = [C.c_int() for _ in range(5)]

@@ -79,18 +79,22 @@ struct vnm_prepared_s {
     void *am;
     void *rows;
     int *status;
-    // cached TMA descriptor of the last dense operand
+    // cached TMA descriptors of the last dense operand: single rows (for gather4) and 64-row tiles
     const void *tm_B;
     int64_t tm_ldb;
     int tm_N;
     bool tm_valid;
-    CUtensorMap tmap;
+    CUtensorMap tmap_rows;
+    CUtensorMap tmap_tile;
+    int producer_warps;
     // device staging of the host-buffer entry point
     void *stage_B;
     size_t stage_B_bytes;
     void *stage_out;
     size_t stage_out_bytes;
     void *stage_bias;
+    int gather_mode;
+    long long *trace;  // debug builds only
 };
 
 extern "C" {
@@ -167,6 +171,8 @@ int vnm_prepare(const void *values, const uint32_t *meta, const uint32_t *colloc
     h->ktiles = (int)((h->Ksp + KT_COMP - 1) / KT_COMP);
     h->nb = TILE_M / V;
     h->vblocks_padded = h->mtiles * h->nb;
+    h->gather_mode = (m == 4) ? GATHER_CONTIG : GATHER_TMA4;  // with m == 4 every row of B is selected
+    h->producer_warps = 8;
     cudaError_t e = cudaGetDevice(&h->device);
     if (e == cudaSuccess) e = cudaMalloc(&h->am, (size_t)h->mtiles * h->ktiles * AM_BLOCK_BYTES);
     if (e == cudaSuccess) e = cudaMalloc(&h->rows, (size_t)h->vblocks_padded * h->ktiles * KT_GROUPS * sizeof(int4));
@@ -195,15 +201,41 @@ int vnm_destroy(vnm_handle_t h)
     return VNM_OK;
 }
 
+int vnm_set_gather_mode(vnm_handle_t h, int mode)
+{
+    if (!h) return fail(VNM_ERR_BAD_ARG, "null handle");
+    if (mode != GATHER_TMA4 && mode != GATHER_CONTIG && mode != GATHER_NONE) return fail(VNM_ERR_BAD_ARG, "unknown gather mode %d", mode);
+    h->gather_mode = mode;
+    return VNM_OK;
+}
+
+#ifdef VNM_TRACE
+// Debug builds only: device buffer of 8 x 4096 clock stamps written by CTA 0 of the next launches.
+int vnm_debug_set_trace(vnm_handle_t h, long long *device_buffer)
+{
+    if (!h) return fail(VNM_ERR_BAD_ARG, "null handle");
+    h->trace = device_buffer;
+    return VNM_OK;
+}
+#endif
+
+int vnm_set_producer_warps(vnm_handle_t h, int warps)
+{
+    if (!h) return fail(VNM_ERR_BAD_ARG, "null handle");
+    if (warps != 4 && warps != 8) return fail(VNM_ERR_BAD_ARG, "producer warps must be 4 or 8 (got %d)", warps);
+    h->producer_warps = warps;
+    return VNM_OK;
+}
+
 int vnm_spmm_config(vnm_handle_t h, int N, int *tile_m, int *tile_n, int *stages, int *grid, int *smem_bytes)
 {
     if (!h) return fail(VNM_ERR_BAD_ARG, "null handle");
     SpmmConfig cfg;
-    if (!spmm_select_config(h->V, N, h->M, &cfg)) return fail(VNM_ERR_UNSUPPORTED, "unsupported V");
+    if (!spmm_select_config(h->V, N, h->M, h->producer_warps, &cfg)) return fail(VNM_ERR_UNSUPPORTED, "unsupported V");
     if (tile_m) *tile_m = TILE_M;
     if (tile_n) *tile_n = cfg.bn;
     if (stages) *stages = cfg.stages;
-    if (grid) *grid = h->mtiles * ((N + cfg.bn - 1) / cfg.bn);
+    if (grid) *grid = cfg.grid;
     if (smem_bytes) *smem_bytes = cfg.smem_bytes;
     return VNM_OK;
 }
@@ -224,21 +256,26 @@ int vnm_spmm_f16(vnm_handle_t h, const void *B, int64_t ldb, int N, const void *
         return fail(VNM_ERR_BAD_ARG, "vnm_spmm_f16: unknown layout %d", layout);
     }
     SpmmConfig cfg;
-    if (!spmm_select_config(h->V, N, h->M, &cfg)) return fail(VNM_ERR_UNSUPPORTED, "unsupported V");
+    if (!spmm_select_config(h->V, N, h->M, h->producer_warps, &cfg)) return fail(VNM_ERR_UNSUPPORTED, "unsupported V");
 
     if (!h->tm_valid || h->tm_B != B || h->tm_ldb != ldb || h->tm_N != N) {
         EncodeTiledFn enc = get_encode_fn();
         if (!enc) return fail(VNM_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
-        // B viewed as a 2-D tensor {N (contiguous), K}; one box = 64 columns of one row (128 bytes),
-        // written with the 128-byte swizzle the MMA's N-major operand layout expects.  Rows >= K and
-        // columns >= N read as zeros.
+        // B viewed as a 2-D tensor {N (contiguous), K}; one box = 64 columns (128 bytes) of one row
+        // (gather4 picks four such rows) or of 64 consecutive rows, written with the 128-byte swizzle
+        // the MMA's N-major operand layout expects.  Rows >= K and columns >= N read as zeros.
         cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)h->K};
         cuuint64_t strides[1] = {(cuuint64_t)ldb * 2};
-        cuuint32_t box[2] = {64, 1};
+        cuuint32_t box_rows[2] = {64, 1};
+        cuuint32_t box_tile[2] = {64, 64};
         cuuint32_t estr[2] = {1, 1};
-        CUresult r = enc(&h->tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(B), dims, strides, box, estr,
+        CUresult r = enc(&h->tmap_rows, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(B), dims, strides, box_rows, estr,
                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r == CUDA_SUCCESS)
+            r = enc(&h->tmap_tile, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(B), dims, strides, box_tile, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return fail(VNM_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
         h->tm_B = B; h->tm_ldb = ldb; h->tm_N = N; h->tm_valid = true;
     }
@@ -253,7 +290,10 @@ int vnm_spmm_f16(vnm_handle_t h, const void *B, int64_t ldb, int N, const void *
     p.mtiles = h->mtiles; p.ktiles = h->ktiles; p.ntiles = (N + cfg.bn - 1) / cfg.bn;
     p.layout = layout;
     p.status = h->status;
-    VNM_CUDA(launch_spmm(cfg, h->tmap, p, (cudaStream_t)stream), "spmm launch");
+    p.gather_mode = h->gather_mode;
+    p.total_tiles = p.mtiles * p.ntiles;
+    p.trace = h->trace;
+    VNM_CUDA(launch_spmm(cfg, h->tmap_rows, h->tmap_tile, p, (cudaStream_t)stream), "spmm launch");
     return VNM_OK;
 }
 

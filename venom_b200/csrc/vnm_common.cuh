@@ -115,6 +115,17 @@ __device__ __forceinline__ void tma_load_2d(void *smem_dst, const void *tmap, in
                  "l"(tmap), "r"(col), "r"(row), "r"(smem_u32(bar))
                  : "memory");
 }
+// 16-byte asynchronous copy global -> shared; src_bytes < 16 zero-fills the remainder (0 = all zeros).
+__device__ __forceinline__ void cp_async_16(uint32_t saddr, const void *gsrc, uint32_t src_bytes)
+{
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(saddr), "l"(gsrc), "r"(src_bytes) : "memory");
+}
+// The barrier receives one arrival from this thread once all its earlier cp.async copies have landed
+// (the arrival must be part of the barrier's expected count).
+__device__ __forceinline__ void cp_async_mbar_arrive_noinc(uint64_t *bar)
+{
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
 __device__ __forceinline__ void tma_prefetch_desc(const void *tmap)
 {
     asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");

@@ -26,14 +26,26 @@ struct SpmmParams {
     int mtiles, ktiles, ntiles;
     int layout;           // 0 = [M,N], 1 = [N,M] + bias
     int *status;          // device status word
+    int gather_mode;      // GATHER_* below
+    int total_tiles;      // mtiles * ntiles
+    long long *trace;     // debug builds (-DVNM_TRACE) only: clock stamps of CTA 0, else null
+};
+
+// How the producer warps bring the selected rows of B into shared memory.
+enum : int {
+    GATHER_TMA4 = 0,    // TMA tile::gather4, four rows (one group) per instruction (default)
+    GATHER_CONTIG = 1,  // plain TMA tiles of 64 consecutive rows: exact when m == 4 (every row is
+                        // selected), otherwise an ablation that drops the column-loc indirection
+    GATHER_NONE = 2     // ablation only: B is not loaded at all (results are meaningless)
 };
 
 struct SpmmConfig {
     int bn;      // tile N
     int nb;      // V-blocks per 128-row tile
-    int stages;
+    int stages;  // number of B-producer warps (4 or 8)
     int smem_bytes;
     int threads;
+    int grid;    // persistent CTAs
 };
 
 cudaError_t launch_compress(const void *dense, int64_t ldd, const int32_t *mask, const uint32_t *colloc, int M, int K, int V, int m,
@@ -44,9 +56,10 @@ cudaError_t launch_prepare(const void *values, const uint32_t *meta, const uint3
                            void *rows, int mtiles, int ktiles, int vblocks_padded, cudaStream_t stream);
 
 // Chooses the tile configuration for (V, N).  Returns false for an unsupported V.
-bool spmm_select_config(int V, int N, int M, SpmmConfig *cfg);
+bool spmm_select_config(int V, int N, int M, int producer_warps, SpmmConfig *cfg);
 // One-time per-process opt-in to large dynamic shared memory for every kernel instance.
 cudaError_t spmm_init_kernels();
-cudaError_t launch_spmm(const SpmmConfig &cfg, const CUtensorMap &tmap_b, const SpmmParams &p, cudaStream_t stream);
+cudaError_t launch_spmm(const SpmmConfig &cfg, const CUtensorMap &tmap_rows, const CUtensorMap &tmap_tile, const SpmmParams &p,
+                        cudaStream_t stream);
 
 }  // namespace vnm

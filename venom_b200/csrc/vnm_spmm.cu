@@ -1,18 +1,28 @@
 // V:N:M SpMM for sm_100a: C[M,N] = A_vnm[M,K] * B[K,N], fp16 in, fp32 accumulate in tensor memory.
 //
-// One CTA computes one 128 x BN output tile.  The 128 rows hold NB = 128/V vector blocks; each block
-// has its own column-loc, hence its own gathered rows of B.  Per k-tile (64 compressed columns of A =
-// 128 gathered rows of B) a stage of shared memory holds
-//     [ value image 16 KiB | metadata image 2 KiB | NB gathered B tiles of 128 x BN fp16 ]
-// Warp roles (192 threads):
-//   warp 0      producer: one bulk copy for the value+metadata block, and TMA gather4 loads of B driven
-//               by the precomputed absolute row numbers (each lane owns one group = four rows);
-//   warp 1      tensor-memory allocation and MMA issue: copies the metadata image to tensor memory
-//               (tcgen05.cp) and issues four K=32 tcgen05.mma.sp per block; for NB > 1 each MMA runs on
-//               all 128 rows of the value tile with the output lanes of the other blocks disabled;
-//   warps 2..5  epilogue: tcgen05.ld -> fp16 -> global ([M,N], or [N,M] with fused bias).
-// Stages are handed over with mbarriers (full: producer -> MMA, empty: tcgen05.commit -> producer).
-// Every wait is bounded: on expiry the kernel records a status bit, drains and returns.
+// Persistent kernel: one CTA per SM walks over 128 x BN output tiles (row tiles fastest, so the CTAs
+// that run together share a column panel of B in L2).  The 128 rows of a tile hold NB = 128/V vector
+// blocks; each block has its own column-loc, hence its own gathered rows of B.
+//
+// Two shared-memory rings feed the tensor core:
+//   A ring  SA stages of 18 KiB: the value image (128 rows x 64 compressed columns, K-major,
+//           128-byte swizzle) and the metadata image of one k-tile, one bulk copy each;
+//   B ring  SB stages of 32 KiB: 64 gathered rows (16 groups) of B for each of the NB blocks, N-major,
+//           128-byte swizzle, i.e. half a k-tile; two K=32 MMAs per block consume one stage.
+// Warp roles:
+//   warp 0            A producer (one elected lane).
+//   warps 1..PB       B producers.  All of them take part in every B stage: one lane arms the barrier
+//                     with the byte count and 64 / PB lanes of each warp issue one TMA gather4 load each
+//                     (four absolute row numbers per instruction, precomputed by the prepare step);
+//                     spreading the loads over many warps matters because a warp issues them one lane
+//                     after the other.
+//   warp PB+1         tensor-memory allocation and MMA issue: metadata image -> tensor memory
+//                     (tcgen05.cp), tcgen05.mma.sp; for NB > 1 each MMA runs on all 128 rows of the
+//                     value tile with the output lanes of the other blocks disabled.
+//   last four warps   epilogue: tcgen05.ld -> packed fp16 registers, release the accumulator, store
+//                     ([M,N], or [N,M] with fused bias).
+// Producers run ahead into the next tile while the epilogue drains.  Every wait is bounded: on expiry
+// the kernel records a status bit, drains and returns.
 #include "vnm_internal.h"
 
 namespace vnm {
@@ -21,21 +31,39 @@ namespace {
 
 constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;  // ~2 s at B200 clocks
 
-template <int BN, int NB, int STAGES>
+#ifdef VNM_TRACE
+// Debug build only: CTA 0 records clock64() stamps of its pipeline hand-offs into p.trace.
+#define TRACE(slot, idx) do { if (blockIdx.x == 0 && lane == 0 && (idx) < 4096 && p.trace) p.trace[(slot) * 4096 + (idx)] = clock64(); } while (0)
+#else
+#define TRACE(slot, idx) do { } while (0)
+#endif
+
+constexpr int BS_ROWS = 64;     // gathered rows per B stage
+constexpr int BS_GROUPS = 16;   // groups per B stage
+
+template <int BN, int NB, int SA, int SB, int PB>
 struct Traits {
-    static_assert(BN % 64 == 0 && BN >= 64 && BN <= 256, "tile N must be 64, 128, 192 or 256");
+    static_assert(BN == 64 || BN == 128 || BN == 256, "tile N must be 64, 128 or 256");
     static_assert(NB == 1 || NB == 2 || NB == 4, "128 rows hold 1, 2 or 4 vector blocks");
-    static constexpr int B_BLOCK_BYTES = KT_ROWS * BN * 2;  // gathered tile of one vector block
-    static constexpr int B_CHUNK_BYTES = KT_ROWS * 128;     // one 64-column slice: 128 rows x 128 B
-    static constexpr int STAGE_BYTES = AM_BLOCK_BYTES + NB * B_BLOCK_BYTES;
-    static_assert(STAGE_BYTES % 1024 == 0 && AM_BLOCK_BYTES % 1024 == 0, "swizzled tiles need 1024-byte alignment");
+    static constexpr int CH = BN / 64;                        // 64-column slices per block
+    static constexpr int B_CHUNK_BYTES = BS_ROWS * 128;       // one slice: 64 rows x 128 B
+    static constexpr int B_BLOCK_BYTES = CH * B_CHUNK_BYTES;  // gathered half k-tile of one block
+    static constexpr int B_STAGE_BYTES = NB * B_BLOCK_BYTES;
+    static constexpr int GATHERS = NB * BS_GROUPS * CH;       // gather4 instructions per B stage (always 64)
+    static_assert(GATHERS % PB == 0 && GATHERS / PB <= 32 && NB * CH <= PB, "producer warp count does not divide the loads");
+    static_assert(B_STAGE_BYTES % 1024 == 0 && AM_BLOCK_BYTES % 1024 == 0, "swizzled tiles need 1024-byte alignment");
     static constexpr int ACC_COLS = BN;
     static constexpr int META_COLS = 8;  // two alternating sets of four columns
-    static constexpr int TMEM_COLS = (BN + META_COLS <= 32) ? 32 : (BN + META_COLS <= 64) ? 64 : (BN + META_COLS <= 128) ? 128
-                                     : (BN + META_COLS <= 256) ? 256 : 512;
+    static constexpr int TMEM_COLS = (BN + META_COLS <= 128) ? 128 : (BN + META_COLS <= 256) ? 256 : 512;
+    static constexpr int A_RING_BYTES = SA * AM_BLOCK_BYTES;
+    static constexpr int B_RING_BYTES = SB * B_STAGE_BYTES;
     static constexpr int BAR_BYTES = 256;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // + alignment slack
-    static constexpr int THREADS = 192;
+    static constexpr int SMEM_BYTES = A_RING_BYTES + B_RING_BYTES + BAR_BYTES + 1024;  // + alignment slack
+    static constexpr int MMA_WARP = 1 + PB;
+    static constexpr int NUM_WARPS = 1 + PB + 1 + 4;
+    static constexpr int NUM_THREADS = NUM_WARPS * 32;
+    static_assert(2 * (SA + SB) * 8 + 32 <= BAR_BYTES, "barrier area too small");
+    static_assert(SB >= 2 * SA - 1, "the A producer reuses the B-stage barriers: see the A producer");
 };
 
 // Whole-warp bounded wait on an mbarrier phase; lane 0 polls.  Returns false if the wait expired or
@@ -45,15 +73,19 @@ __device__ __forceinline__ bool wait_bounded(uint64_t *bar, uint32_t parity, vol
     int ok = 1;
     if ((threadIdx.x & 31) == 0) {
         ok = 0;
-        const long long t0 = clock64();
-        for (uint32_t it = 0;; ++it) {
-            if (mbar_try_wait(bar, parity)) { ok = 1; break; }
-            if ((it & 63u) == 63u) {
-                if (*abort_flag) break;
-                if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
-                    *abort_flag = 1;
-                    atomicOr(status, code);
-                    break;
+        if (mbar_try_wait(bar, parity)) {
+            ok = 1;
+        } else {
+            const long long t0 = clock64();
+            for (uint32_t it = 0;; ++it) {
+                if (mbar_try_wait(bar, parity)) { ok = 1; break; }
+                if ((it & 63u) == 63u) {
+                    if (*abort_flag) break;
+                    if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+                        *abort_flag = 1;
+                        atomicOr(status, code);
+                        break;
+                    }
                 }
             }
         }
@@ -62,34 +94,66 @@ __device__ __forceinline__ bool wait_bounded(uint64_t *bar, uint32_t parity, vol
     return ok != 0;
 }
 
-template <int BN, int NB, int STAGES>
-__global__ void __launch_bounds__(192, 1) spmm_kernel(const __grid_constant__ CUtensorMap tmap_b, const SpmmParams p)
+// Single-thread bounded wait (no warp convergence needed): the fast path is one try_wait.
+__device__ __forceinline__ bool wait_one(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int *status, int code)
 {
-    using T = Traits<BN, NB, STAGES>;
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (uint32_t it = 0;; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((it & 63u) == 63u) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+                *abort_flag = 1;
+                atomicOr(status, code);
+                return false;
+            }
+        }
+    }
+}
+
+// Bounded wait used only while draining after an abort: until the copies of one ring slot have landed.
+__device__ __forceinline__ void drain_slot(uint64_t *bar, uint32_t parity, int *status)
+{
+    const long long t0 = clock64();
+    while (clock64() - t0 < WAIT_LIMIT_CYCLES / 4) {
+        if (mbar_try_wait(bar, parity)) return;
+    }
+    atomicOr(status, DEV_TIMEOUT_DRAIN);
+}
+
+template <int BN, int NB, int SA, int SB, int PB>
+__global__ void __launch_bounds__(Traits<BN, NB, SA, SB, PB>::NUM_THREADS, 1)
+    spmm_kernel(const __grid_constant__ CUtensorMap tmap_rows, const __grid_constant__ CUtensorMap tmap_tile, const SpmmParams p)
+{
+    using T = Traits<BN, NB, SA, SB, PB>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    uint64_t *full_bar = reinterpret_cast<uint64_t *>(smem + STAGES * T::STAGE_BYTES);
-    uint64_t *empty_bar = full_bar + STAGES;
-    uint64_t *accum_bar = empty_bar + STAGES;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(accum_bar + 1);
+    uint8_t *a_ring = smem;
+    uint8_t *b_ring = smem + T::A_RING_BYTES;
+    uint64_t *a_full = reinterpret_cast<uint64_t *>(smem + T::A_RING_BYTES + T::B_RING_BYTES);
+    uint64_t *a_empty = a_full + SA;
+    uint64_t *b_full = a_empty + SA;
+    uint64_t *b_empty = b_full + SB;
+    uint64_t *acc_full_bar = b_empty + SB;
+    uint64_t *acc_empty_bar = acc_full_bar + 1;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty_bar + 1);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int mt = blockIdx.x % p.mtiles;  // row tiles fastest: CTAs that run together share a column panel of B
-    const int nt = blockIdx.x / p.mtiles;
-    const int n0 = nt * BN;
+    const int gmode = p.gather_mode;
+    const int bstages_per_tile = 2 * p.ktiles;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; s++) {
-            mbar_init(&full_bar[s], 1);
-            mbar_init(&empty_bar[s], 1);
-        }
-        mbar_init(accum_bar, 1);
+        for (int s = 0; s < SA; s++) { mbar_init(&a_full[s], 1); mbar_init(&a_empty[s], 1); }
+        for (int s = 0; s < SB; s++) { mbar_init(&b_full[s], 1); mbar_init(&b_empty[s], 1); }
+        mbar_init(acc_full_bar, 1);
+        mbar_init(acc_empty_bar, 4);
         *abort_flag = 0;
         fence_barrier_init();
     }
-    if (warp == 1) {
+    if (warp == T::MMA_WARP) {
         tmem_alloc(tmem_slot, T::TMEM_COLS);
         tmem_relinquish();
     }
@@ -99,206 +163,313 @@ __global__ void __launch_bounds__(192, 1) spmm_kernel(const __grid_constant__ CU
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp == 0) {
-        // ---------------- producer ----------------
-        if (lane == 0) tma_prefetch_desc(&tmap_b);
-        int issued = 0;
-        for (int kt = 0; kt < p.ktiles; ++kt) {
-            const int s = kt % STAGES;
-            const uint32_t ph = (uint32_t)(kt / STAGES) & 1u;
-            if (!wait_bounded(&empty_bar[s], ph ^ 1u, abort_flag, p.status, DEV_TIMEOUT_PRODUCER)) break;
-            uint8_t *st = smem + s * T::STAGE_BYTES;
-            if (lane == 0) {
-                mbar_arrive_expect_tx(&full_bar[s], T::STAGE_BYTES);
-                bulk_g2s(st, p.am + ((size_t)mt * p.ktiles + kt) * AM_BLOCK_BYTES, AM_BLOCK_BYTES, &full_bar[s]);
-            }
-            __syncwarp();
-#pragma unroll
-            for (int b = 0; b < NB; b++) {
-                const int4 r = __ldg(p.rows + ((size_t)(mt * NB + b) * p.ktiles + kt) * KT_GROUPS + lane);
-                uint8_t *dst = st + AM_BLOCK_BYTES + b * T::B_BLOCK_BYTES + lane * 512;
-#pragma unroll
-                for (int c = 0; c < BN / 64; c++) tma_gather4(dst + c * T::B_CHUNK_BYTES, &tmap_b, n0 + c * 64, r, &full_bar[s]);
-            }
-            issued = kt + 1;
-        }
-        if (*abort_flag) {
-            // Drain: wait (bounded) until the copies of the stages still in flight have landed.
-            const int first = issued > STAGES ? issued - STAGES : 0;
-            for (int kt = first; kt < issued; ++kt) {
-                const int s = kt % STAGES;
-                const uint32_t ph = (uint32_t)(kt / STAGES) & 1u;
-                int ok = 1;
-                if (lane == 0) {
-                    ok = 0;
-                    const long long t0 = clock64();
-                    while (clock64() - t0 < WAIT_LIMIT_CYCLES / 4) {
-                        if (mbar_try_wait(&full_bar[s], ph)) { ok = 1; break; }
+        // ---------------- A producer (one thread) ----------------
+        int it = 0;
+        if (lane == 0) {
+            bool alive = true;
+            for (int tile = blockIdx.x; alive && tile < p.total_tiles; tile += gridDim.x) {
+                const int mt = tile % p.mtiles;
+                for (int kt = 0; kt < p.ktiles; ++kt, ++it) {
+                    const int s = it % SA;
+                    if (it >= SA) {
+                        // slot s was last used by k-tile it - SA; it is free once the MMAs of that k-tile's
+                        // second B stage (ring position jb) have completed.  That barrier cannot advance a
+                        // further phase before this k-tile is loaded, because B stage jb + SB belongs to
+                        // k-tile it - SA + SB/2 + ... >= it (SB >= 2 * SA - 1), which needs this slot.
+                        const int jb = 2 * (it - SA) + 1;
+                        if (!wait_one(&b_empty[jb % SB], (uint32_t)(jb / SB) & 1u, abort_flag, p.status, DEV_TIMEOUT_PRODUCER)) { alive = false; break; }
                     }
-                    if (!ok) atomicOr(p.status, DEV_TIMEOUT_DRAIN);
+                    TRACE(0, it);
+                    mbar_arrive_expect_tx(&a_full[s], AM_BLOCK_BYTES);
+                    bulk_g2s(a_ring + s * AM_BLOCK_BYTES, p.am + ((size_t)mt * p.ktiles + kt) * AM_BLOCK_BYTES, AM_BLOCK_BYTES, &a_full[s]);
                 }
-                __syncwarp();
+            }
+            if (*abort_flag) {
+                for (int k = it > SA ? it - SA : 0; k < it; ++k) drain_slot(&a_full[k % SA], (uint32_t)(k / SA) & 1u, p.status);
             }
         }
-    } else if (warp == 1) {
-        // ---------------- MMA issuer ----------------
-        const uint32_t acc = tmem_base;
-        const uint32_t meta0 = tmem_base + T::ACC_COLS;
-        for (int kt = 0; kt < p.ktiles; ++kt) {
-            const int s = kt % STAGES;
-            const uint32_t ph = (uint32_t)(kt / STAGES) & 1u;
-            if (!wait_bounded(&full_bar[s], ph, abort_flag, p.status, DEV_TIMEOUT_MMA)) break;
-            tc_fence_after();
-            if (lane == 0) {
-                const uint32_t sbase = smem_u32(smem + s * T::STAGE_BYTES);
-                const uint32_t mcol = meta0 + (uint32_t)(kt & 1) * 4u;
-                // metadata image: 128 rows x 16 bytes, 8-row core matrices stored back to back
-                tc_cp_128x128b(mcol, make_smem_desc(sbase + A_IMG_BYTES, 0, 128, 0));
-#pragma unroll
-                for (int b = 0; b < NB; b++) {
-                    uint32_t mk[4] = {0u, 0u, 0u, 0u};  // bit set = output lane NOT written
-                    if (NB == 2) {
-                        mk[0] = mk[1] = (b == 0) ? 0u : 0xFFFFFFFFu;
-                        mk[2] = mk[3] = (b == 0) ? 0xFFFFFFFFu : 0u;
-                    } else if (NB == 4) {
-                        mk[0] = (b == 0) ? 0u : 0xFFFFFFFFu;
-                        mk[1] = (b == 1) ? 0u : 0xFFFFFFFFu;
-                        mk[2] = (b == 2) ? 0u : 0xFFFFFFFFu;
-                        mk[3] = (b == 3) ? 0u : 0xFFFFFFFFu;
+        __syncwarp();
+    } else if (warp <= PB) {
+        // ---------------- B producers ----------------
+        // Every producer warp takes part in every stage (GATHERS / PB of its lanes issue one load each),
+        // so each lane meets the ring slots strictly in order and the phase parity stays unambiguous.
+        // The row numbers of the next stage are fetched before waiting for the current slot.
+        const int pw = warp - 1;
+        constexpr int ACTIVE = T::GATHERS / PB;  // lanes of this warp that issue gather4 loads
+        const bool leader = (pw == 0 && lane == 0);
+        if (leader) { tma_prefetch_desc(&tmap_rows); tma_prefetch_desc(&tmap_tile); }
+        // this lane's fixed share of a stage: block b, group g, 64-column slice c
+        const int idx = lane * PB + pw;
+        const int gb = idx / (BS_GROUPS * T::CH);
+        const int gg = (idx % (BS_GROUPS * T::CH)) / T::CH;
+        const int gc = idx % T::CH;
+        const bool gather_lane = (gmode == GATHER_TMA4) && lane < ACTIVE;
+        const bool tile_lane = (gmode == GATHER_CONTIG) && lane == 0 && pw < NB * T::CH;
+        const int tb = pw / T::CH, tc = pw % T::CH;  // CONTIG: (block, slice) of this warp
+        if (gather_lane || tile_lane || leader) {
+            int j = 0;
+            int tile = blockIdx.x, jl = 0;
+            bool valid = tile < p.total_tiles;
+            auto rows_of = [&](int tl, int l) -> const int4 * {
+                const int mt = tl % p.mtiles;
+                const int b = gather_lane ? gb : tb;
+                return p.rows + ((size_t)(mt * NB + b) * p.ktiles) * KT_GROUPS + (size_t)l * BS_GROUPS + (gather_lane ? gg : 0);
+            };
+            int4 r_cur = make_int4(0, 0, 0, 0);
+            if (valid && (gather_lane || tile_lane)) r_cur = __ldg(rows_of(tile, jl));
+            while (valid) {
+                int ntile = tile, njl = jl + 1;
+                if (njl == bstages_per_tile) { njl = 0; ntile += gridDim.x; }
+                const bool nvalid = ntile < p.total_tiles;
+                int4 r_nxt = make_int4(0, 0, 0, 0);
+                if (nvalid && (gather_lane || tile_lane)) r_nxt = __ldg(rows_of(ntile, njl));
+                const int s = j % SB;
+                if (!wait_one(&b_empty[s], ((uint32_t)(j / SB) & 1u) ^ 1u, abort_flag, p.status, DEV_TIMEOUT_PRODUCER)) break;
+                uint8_t *st = b_ring + s * T::B_STAGE_BYTES;
+                const int n0 = (tile / p.mtiles) * BN;
+                if (leader) {
+                    TRACE(1, j);
+                    if (gmode == GATHER_NONE) mbar_arrive(&b_full[s]);
+                    else mbar_arrive_expect_tx(&b_full[s], T::B_STAGE_BYTES);
+                }
+                if (gather_lane)
+                    tma_gather4(st + gb * T::B_BLOCK_BYTES + gc * T::B_CHUNK_BYTES + gg * 512, &tmap_rows, n0 + gc * 64, r_cur, &b_full[s]);
+                else if (tile_lane)  // 64 consecutive rows starting at the first selected row of the stage
+                    tma_load_2d(st + tb * T::B_BLOCK_BYTES + tc * T::B_CHUNK_BYTES, &tmap_tile, n0 + tc * 64, r_cur.x, &b_full[s]);
+                tile = ntile; jl = njl; valid = nvalid; r_cur = r_nxt; ++j;
+            }
+            if (*abort_flag && leader && gmode != GATHER_NONE) {
+                for (int k = j > SB ? j - SB : 0; k < j; ++k) drain_slot(&b_full[k % SB], (uint32_t)(k / SB) & 1u, p.status);
+            }
+        }
+        __syncwarp();
+    } else if (warp == T::MMA_WARP) {
+        // ---------------- MMA issuer (one thread) ----------------
+        // The metadata image of k-tile it+1 is copied to tensor memory before the MMAs of k-tile it are
+        // issued, so that the copy never sits on the critical path.  One commit per B stage: the commit of
+        // the second half of a k-tile also releases the A stage (the A producer waits on that barrier).
+        if (lane == 0) {
+            const uint32_t acc = tmem_base;
+            const uint32_t meta0 = tmem_base + T::ACC_COLS;
+            const uint32_t idesc0 = make_idesc_f16(TILE_M, BN, true, 0u, true);
+            // descriptor templates: only the start-address field (low 14 bits, in 16-byte units) varies
+            const uint64_t adesc0 = make_smem_desc(smem_u32(a_ring), 16, 1024, 2);
+            const uint64_t bdesc0 = make_smem_desc(smem_u32(b_ring), T::B_CHUNK_BYTES, 1024, 2);
+            const uint64_t mdesc0 = make_smem_desc(smem_u32(a_ring) + A_IMG_BYTES, 0, 128, 0);
+            const int my_tiles = (p.total_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+            const int total_it = my_tiles * p.ktiles;
+            int it = 0, j = 0;
+            bool alive = total_it > 0;
+            if (alive) {
+                alive = wait_one(&a_full[0], 0u, abort_flag, p.status, DEV_TIMEOUT_MMA);
+                if (alive) { tc_fence_after(); tc_cp_128x128b(meta0, mdesc0); }
+            }
+            for (int ti = 0; alive && ti < my_tiles; ++ti) {
+                // the epilogue must have read the previous tile's accumulator
+                TRACE(7, ti * 2);
+                if (!wait_one(acc_empty_bar, ((uint32_t)ti & 1u) ^ 1u, abort_flag, p.status, DEV_TIMEOUT_MMA)) break;
+                tc_fence_after();
+                TRACE(7, ti * 2 + 1);
+                for (int kt = 0; alive && kt < p.ktiles; ++kt, ++it) {
+                    const int sa = it % SA;
+                    const uint32_t aoff = (uint32_t)(sa * AM_BLOCK_BYTES) >> 4;
+                    const uint32_t mcol = meta0 + (uint32_t)(it & 1) * 4u;
+                    TRACE(2, it);
+                    if (it + 1 < total_it) {
+                        // metadata of the next k-tile -> the other column set (last read by k-tile it-1)
+                        const int sn = (it + 1) % SA;
+                        if (!wait_one(&a_full[sn], (uint32_t)((it + 1) / SA) & 1u, abort_flag, p.status, DEV_TIMEOUT_MMA)) { alive = false; break; }
+                        tc_fence_after();
+                        tc_cp_128x128b(meta0 + (uint32_t)((it + 1) & 1) * 4u, mdesc0 + ((uint32_t)(sn * AM_BLOCK_BYTES) >> 4));
                     }
+                    TRACE(3, it);
 #pragma unroll
-                    for (int kb = 0; kb < 4; kb++) {
-                        // A: K-major, 128-byte swizzle, 8-row groups 1024 B apart; one MMA reads 32 B of each row
-                        const uint64_t adesc = make_smem_desc(sbase + kb * 32, 16, 1024, 2);
-                        // B: N-major, 128-byte swizzle; 8 gathered rows = 1024 B, next 64 columns = one chunk further
-                        const uint64_t bdesc =
-                            make_smem_desc(sbase + AM_BLOCK_BYTES + b * T::B_BLOCK_BYTES + kb * 4096, T::B_CHUNK_BYTES, 1024, 2);
-                        const uint32_t idesc = make_idesc_f16(TILE_M, BN, true, (uint32_t)(kb & 1), true);
-                        tc_mma_sp_f16(acc, adesc, bdesc, mcol + (uint32_t)(kb & ~1), idesc, (kt | kb) != 0 ? 1u : 0u, mk[0], mk[1],
-                                      mk[2], mk[3]);
+                    for (int h = 0; h < 2; ++h, ++j) {
+                        const int sb = j % SB;
+                        if (!wait_one(&b_full[sb], (uint32_t)(j / SB) & 1u, abort_flag, p.status, DEV_TIMEOUT_MMA)) { alive = false; break; }
+                        tc_fence_after();
+                        TRACE(4, j);
+                        const uint32_t boff = (uint32_t)(sb * T::B_STAGE_BYTES) >> 4;
+#pragma unroll
+                        for (int b = 0; b < NB; b++) {
+                            uint32_t mk[4] = {0u, 0u, 0u, 0u};  // bit set = output lane NOT written
+                            if (NB == 2) {
+                                mk[0] = mk[1] = (b == 0) ? 0u : 0xFFFFFFFFu;
+                                mk[2] = mk[3] = (b == 0) ? 0xFFFFFFFFu : 0u;
+                            } else if (NB == 4) {
+                                mk[0] = (b == 0) ? 0u : 0xFFFFFFFFu;
+                                mk[1] = (b == 1) ? 0u : 0xFFFFFFFFu;
+                                mk[2] = (b == 2) ? 0u : 0xFFFFFFFFu;
+                                mk[3] = (b == 3) ? 0u : 0xFFFFFFFFu;
+                            }
+#pragma unroll
+                            for (int k2 = 0; k2 < 2; k2++) {
+                                const int kb = h * 2 + k2;  // K=32 block inside the k-tile
+                                // A: K-major, 128-byte swizzle, 8-row groups 1024 B apart; one MMA reads 32 B of each row.
+                                // B: N-major, 128-byte swizzle; 8 gathered rows = 1024 B, next 64 columns = one slice further.
+                                const uint64_t adesc = adesc0 + aoff + (uint32_t)(kb * 32 >> 4);
+                                const uint64_t bdesc = bdesc0 + boff + (uint32_t)((b * T::B_BLOCK_BYTES + k2 * 4096) >> 4);
+                                tc_mma_sp_f16(acc, adesc, bdesc, mcol + (uint32_t)(kb & ~1), idesc0 | (uint32_t)(kb & 1),
+                                              (kt | kb) != 0 ? 1u : 0u, mk[0], mk[1], mk[2], mk[3]);
+                            }
+                        }
+                        tc_commit(&b_empty[sb]);
+                        if (h == 1 && kt == p.ktiles - 1) tc_commit(acc_full_bar);
+                        TRACE(5, j);
                     }
                 }
-                tc_commit(&empty_bar[s]);
-                if (kt == p.ktiles - 1) tc_commit(accum_bar);
             }
-            __syncwarp();
         }
+        __syncwarp();
     } else {
         // ---------------- epilogue ----------------
         const int q = warp & 3;  // tensor-memory lane quadrant this warp may read
-        if (wait_bounded(accum_bar, 0, abort_flag, p.status, DEV_TIMEOUT_EPILOGUE)) {
+        const int i = q * 32 + lane;
+        const int arow = mma_row_to_actual(i);
+        int ti = 0;
+        for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x, ++ti) {
+            const int mt = tile % p.mtiles;
+            const int n0 = (tile / p.mtiles) * BN;
+            if (!wait_bounded(acc_full_bar, (uint32_t)ti & 1u, abort_flag, p.status, DEV_TIMEOUT_EPILOGUE)) break;
             tc_fence_after();
-            const int i = q * 32 + lane;
-            const int64_t row = (int64_t)mt * TILE_M + mma_row_to_actual(i);
+            if (q == 0) TRACE(6, ti * 3);
+            // The tile is drained in parts of 64 columns to bound the register footprint; the
+            // accumulator goes back to the MMA warp as soon as the last part is in registers.
+            constexpr int PART = 64;
+            const int64_t row = (int64_t)mt * TILE_M + arow;
             const bool row_ok = row < p.M;
-            __half bias = __ushort_as_half((unsigned short)0);
-            if (p.layout == 1 && p.bias != nullptr && row_ok) bias = p.bias[row];
-#pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
-                uint32_t v[32];
-                tc_ld_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
-                tc_wait_ld();
-                if (!row_ok) continue;
-                const int n = n0 + c0;
-                if (p.layout == 0) {
-                    __half *dst = p.out + row * p.ldo + n;
+            const bool has_bias = p.layout == 1 && p.bias != nullptr;
+            const __half bias = (has_bias && row_ok) ? p.bias[row] : __ushort_as_half((unsigned short)0);
 #pragma unroll
-                    for (int j = 0; j < 4; j++) {
-                        if (n + j * 8 + 8 <= p.N) {
-                            uint4 o;
-                            __half2 h;
-                            h = __floats2half2_rn(__uint_as_float(v[j * 8 + 0]), __uint_as_float(v[j * 8 + 1]));
-                            o.x = *reinterpret_cast<uint32_t *>(&h);
-                            h = __floats2half2_rn(__uint_as_float(v[j * 8 + 2]), __uint_as_float(v[j * 8 + 3]));
-                            o.y = *reinterpret_cast<uint32_t *>(&h);
-                            h = __floats2half2_rn(__uint_as_float(v[j * 8 + 4]), __uint_as_float(v[j * 8 + 5]));
-                            o.z = *reinterpret_cast<uint32_t *>(&h);
-                            h = __floats2half2_rn(__uint_as_float(v[j * 8 + 6]), __uint_as_float(v[j * 8 + 7]));
-                            o.w = *reinterpret_cast<uint32_t *>(&h);
-                            *reinterpret_cast<uint4 *>(dst + j * 8) = o;
-                        }
+            for (int part = 0; part < BN / PART; part++) {
+                uint32_t pk[PART / 2];  // packed fp16 pairs: pk[c] = columns 2c, 2c+1 of this part
+#pragma unroll
+                for (int c0 = 0; c0 < PART; c0 += 32) {
+                    uint32_t v[32];
+                    tc_ld_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(part * PART + c0), v);
+                    tc_wait_ld();
+#pragma unroll
+                    for (int jj = 0; jj < 16; jj++) {
+                        __half2 h = __floats2half2_rn(__uint_as_float(v[2 * jj]), __uint_as_float(v[2 * jj + 1]));
+                        pk[c0 / 2 + jj] = *reinterpret_cast<uint32_t *>(&h);
                     }
-                } else {
-                    const bool has_bias = p.bias != nullptr;
+                }
+                if (part == BN / PART - 1) {
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(acc_empty_bar);
+                    if (q == 0) TRACE(6, ti * 3 + 1);
+                }
+                if (row_ok) {
+                    const int nbase = n0 + part * PART;
+                    if (p.layout == 0) {
+                        __half *dst = p.out + row * p.ldo + nbase;
 #pragma unroll
-                    for (int j = 0; j < 32; j++) {
-                        if (n + j < p.N) {
-                            __half h = __float2half_rn(__uint_as_float(v[j]));
-                            if (has_bias) h = __hadd(h, bias);
-                            p.out[(int64_t)(n + j) * p.ldo + row] = h;
+                        for (int jj = 0; jj < PART / 8; jj++) {
+                            if (nbase + jj * 8 + 8 <= p.N)
+                                *reinterpret_cast<uint4 *>(dst + jj * 8) = make_uint4(pk[4 * jj], pk[4 * jj + 1], pk[4 * jj + 2], pk[4 * jj + 3]);
+                        }
+                    } else {
+                        __half *dst = p.out + (int64_t)nbase * p.ldo + row;
+                        const int64_t step = p.ldo;
+#pragma unroll
+                        for (int jj = 0; jj < PART / 2; jj++) {
+                            __half2 h = *reinterpret_cast<__half2 *>(&pk[jj]);
+                            __half lo = __low2half(h), hi = __high2half(h);
+                            if (has_bias) { lo = __hadd(lo, bias); hi = __hadd(hi, bias); }
+                            if (nbase + 2 * jj < p.N) *dst = lo;
+                            dst += step;
+                            if (nbase + 2 * jj + 1 < p.N) *dst = hi;
+                            dst += step;
                         }
                     }
                 }
             }
+            if (q == 0) TRACE(6, ti * 3 + 2);
         }
     }
 
     tc_fence_before();
     __syncthreads();
-    if (warp == 1) {
+    if (warp == T::MMA_WARP) {
         tc_fence_after();
         tmem_dealloc(tmem_base, T::TMEM_COLS);
     }
 }
 
-template <int BN, int NB, int STAGES>
+template <int BN, int NB, int SA, int SB, int PB>
 cudaError_t set_attr()
 {
-    return cudaFuncSetAttribute(spmm_kernel<BN, NB, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, Traits<BN, NB, STAGES>::SMEM_BYTES);
+    return cudaFuncSetAttribute(spmm_kernel<BN, NB, SA, SB, PB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                Traits<BN, NB, SA, SB, PB>::SMEM_BYTES);
 }
 
-template <int BN, int NB, int STAGES>
-cudaError_t launch_one(const CUtensorMap &tmap_b, const SpmmParams &p, cudaStream_t stream)
+template <int BN, int NB, int SA, int SB, int PB>
+cudaError_t launch_one(const SpmmConfig &cfg, const CUtensorMap &tmap_rows, const CUtensorMap &tmap_tile, const SpmmParams &p,
+                       cudaStream_t stream)
 {
-    using T = Traits<BN, NB, STAGES>;
-    const unsigned grid = (unsigned)p.mtiles * (unsigned)p.ntiles;
-    spmm_kernel<BN, NB, STAGES><<<grid, T::THREADS, T::SMEM_BYTES, stream>>>(tmap_b, p);
+    using T = Traits<BN, NB, SA, SB, PB>;
+    spmm_kernel<BN, NB, SA, SB, PB><<<(unsigned)cfg.grid, T::NUM_THREADS, T::SMEM_BYTES, stream>>>(tmap_rows, tmap_tile, p);
     return cudaGetLastError();
 }
 
+int g_num_sms = 0;
+
+constexpr int kSA = 3, kSB = 5;
+
 }  // namespace
 
-// Tile configurations: V=128 -> one block per tile, N tile 256 (2 stages) or 128 (4 stages) when the
-// wide tile would leave most SMs idle; V=64 -> two blocks, N tile 128; V=32 -> four blocks, N tile 64.
-bool spmm_select_config(int V, int N, int M, SpmmConfig *cfg)
+// Tile configurations (128 rows x BN columns with NB * BN = 256, so every B stage is 32 KiB):
+// V=128 -> one block per tile, BN 256; V=64 -> two blocks, BN 128; V=32 -> four blocks, BN 64.
+// cfg->stages carries the number of B-producer warps (4 or 8).
+bool spmm_select_config(int V, int N, int M, int producer_warps, SpmmConfig *cfg)
 {
     const int mtiles = (M + TILE_M - 1) / TILE_M;
-    cfg->threads = 192;
+    const int pb = (producer_warps == 4) ? 4 : 8;
+    cfg->stages = pb;
+    cfg->threads = (1 + pb + 1 + 4) * 32;
     if (V == 128) {
-        const long long wide_tiles = (long long)mtiles * ((N + 255) / 256);
-        if (wide_tiles >= 148) {
-            cfg->bn = 256; cfg->nb = 1; cfg->stages = 2; cfg->smem_bytes = Traits<256, 1, 2>::SMEM_BYTES;
-        } else {
-            cfg->bn = 128; cfg->nb = 1; cfg->stages = 4; cfg->smem_bytes = Traits<128, 1, 4>::SMEM_BYTES;
-        }
-        return true;
+        cfg->bn = 256; cfg->nb = 1;
+    } else if (V == 64) {
+        cfg->bn = 128; cfg->nb = 2;
+    } else if (V == 32) {
+        cfg->bn = 64; cfg->nb = 4;
+    } else {
+        return false;
     }
-    if (V == 64) {
-        cfg->bn = 128; cfg->nb = 2; cfg->stages = 2; cfg->smem_bytes = Traits<128, 2, 2>::SMEM_BYTES;
-        return true;
-    }
-    if (V == 32) {
-        cfg->bn = 64; cfg->nb = 4; cfg->stages = 2; cfg->smem_bytes = Traits<64, 4, 2>::SMEM_BYTES;
-        return true;
-    }
-    return false;
+    cfg->smem_bytes = Traits<256, 1, kSA, kSB, 8>::SMEM_BYTES;
+    const long long tiles = (long long)mtiles * ((N + cfg->bn - 1) / cfg->bn);
+    const int sms = g_num_sms > 0 ? g_num_sms : 148;
+    cfg->grid = (int)(tiles < sms ? tiles : sms);
+    return true;
 }
 
 cudaError_t spmm_init_kernels()
 {
     cudaError_t e;
-    if ((e = set_attr<256, 1, 2>()) != cudaSuccess) return e;
-    if ((e = set_attr<128, 1, 4>()) != cudaSuccess) return e;
-    if ((e = set_attr<128, 2, 2>()) != cudaSuccess) return e;
-    if ((e = set_attr<64, 4, 2>()) != cudaSuccess) return e;
-    return cudaSuccess;
+    if ((e = set_attr<256, 1, kSA, kSB, 8>()) != cudaSuccess) return e;
+    if ((e = set_attr<128, 2, kSA, kSB, 8>()) != cudaSuccess) return e;
+    if ((e = set_attr<64, 4, kSA, kSB, 8>()) != cudaSuccess) return e;
+    if ((e = set_attr<256, 1, kSA, kSB, 4>()) != cudaSuccess) return e;
+    if ((e = set_attr<128, 2, kSA, kSB, 4>()) != cudaSuccess) return e;
+    if ((e = set_attr<64, 4, kSA, kSB, 4>()) != cudaSuccess) return e;
+    int dev = 0;
+    if ((e = cudaGetDevice(&dev)) != cudaSuccess) return e;
+    return cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
 }
 
-cudaError_t launch_spmm(const SpmmConfig &cfg, const CUtensorMap &tmap_b, const SpmmParams &p, cudaStream_t stream)
+cudaError_t launch_spmm(const SpmmConfig &cfg, const CUtensorMap &tmap_rows, const CUtensorMap &tmap_tile, const SpmmParams &p,
+                        cudaStream_t stream)
 {
-    if (cfg.bn == 256 && cfg.nb == 1) return launch_one<256, 1, 2>(tmap_b, p, stream);
-    if (cfg.bn == 128 && cfg.nb == 1) return launch_one<128, 1, 4>(tmap_b, p, stream);
-    if (cfg.bn == 128 && cfg.nb == 2) return launch_one<128, 2, 2>(tmap_b, p, stream);
-    if (cfg.bn == 64 && cfg.nb == 4) return launch_one<64, 4, 2>(tmap_b, p, stream);
+    if (cfg.stages == 4) {
+        if (cfg.nb == 1) return launch_one<256, 1, kSA, kSB, 4>(cfg, tmap_rows, tmap_tile, p, stream);
+        if (cfg.nb == 2) return launch_one<128, 2, kSA, kSB, 4>(cfg, tmap_rows, tmap_tile, p, stream);
+        if (cfg.nb == 4) return launch_one<64, 4, kSA, kSB, 4>(cfg, tmap_rows, tmap_tile, p, stream);
+    } else {
+        if (cfg.nb == 1) return launch_one<256, 1, kSA, kSB, 8>(cfg, tmap_rows, tmap_tile, p, stream);
+        if (cfg.nb == 2) return launch_one<128, 2, kSA, kSB, 8>(cfg, tmap_rows, tmap_tile, p, stream);
+        if (cfg.nb == 4) return launch_one<64, 4, kSA, kSB, 8>(cfg, tmap_rows, tmap_tile, p, stream);
+    }
     return cudaErrorInvalidValue;
 }
 
