@@ -1,0 +1,66 @@
+"""Two-rank NCCL run of the N-sharded launcher (needs two GPUs; skipped on a single-GPU box)."""
+import os
+import socket
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, q):
+    import torch
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from oracle.oracle import Oracle
+        from venom_b200.sharded import ShardedSpmm, shard_bounds
+        from venom_b200.synth import random_dense_b, random_vnm_dense
+        M, K, V, m, N = 256, 1024, 128, 8, 1024
+        dense, cols, _ = random_vnm_dense(M, K, V, m, seed=1)
+        B = random_dense_b(K, N, seed=2)
+        orc = Oracle()
+        ov, om, _ = orc.compress(dense, cols, V, m)
+        if rank == 0:
+            args = (torch.from_numpy(ov), torch.from_numpy(om.view(np.int32)), torch.from_numpy(cols.view(np.int32)))
+        else:
+            args = (None, None, None)
+        op = ShardedSpmm.from_reference_arrays(*args, M, K, V, m)
+        lo, hi = shard_bounds(N, world, rank)
+        full = op.gathered(torch.from_numpy(B[:, lo:hi].copy()).cuda(), N)
+        torch.cuda.synchronize()
+        want = orc.spmm(ov, om, cols, M, K, V, m, B, layout=1)
+        bad, _, worst = orc.check(full.cpu().numpy(), want, mode=1, tol=1e-2)
+        q.put((rank, bad, worst))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_nccl_sharded_spmm():
+    import torch
+    import torch.multiprocessing as mp
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=300) for _ in range(2)]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert all(bad == 0 for _, bad, _ in res), res

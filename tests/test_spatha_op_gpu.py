@@ -1,0 +1,97 @@
+"""GPU tests of the reference-facing surfaces: the `spatha` torch extension, the SrnmSpmm module that
+replaces torch.nn.Linear, and the benchmark_spmm command line."""
+import os
+import subprocess
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def spatha():
+    import torch
+    assert torch.cuda.is_available()
+    import venom_b200
+    return venom_b200.spatha_module()
+
+
+@pytest.mark.parametrize("cfg", [(768, 768, 128, 8, 512), (1024, 1024, 64, 8, 1024), (512, 1024, 32, 16, 256), (256, 512, 128, 4, 128)])
+def test_spatha_spmm_matches_dense_product_plus_bias(spatha, oracle, cfg):
+    """The reference's only op-level check (end2end/tests.ipynb cells 24-28):
+    spatha.spmm(...).T == dense @ rhs + bias."""
+    import torch
+    from venom_b200.synth import random_dense_b, random_vnm_dense
+    M, K, V, m, N = cfg
+    dense, cols, _ = random_vnm_dense(M, K, V, m, seed=M + N)
+    B = random_dense_b(K, N, seed=3)
+    ov, om, _ = oracle.compress(dense, cols, V, m)
+    values = torch.from_numpy(ov).cuda()
+    meta = torch.from_numpy(om.view(np.int32)).cuda()
+    idx = torch.from_numpy(cols.view(np.int32)).cuda()
+    bias = torch.full((M,), 2.0, dtype=torch.float16, device="cuda")
+    rhs = torch.from_numpy(B).cuda()
+    out = spatha.spmm(meta, idx, values, rhs, bias, M, K, N, V, 2, m, values.numel(), 0, 32, 4)
+    assert tuple(out.shape) == (N, M) and out.dtype == torch.float16
+    want = oracle.spmm(ov, om, cols, M, K, V, m, B, bias=bias.cpu().numpy(), layout=1)
+    bad, first, worst = oracle.check(out.cpu().numpy(), want, mode=1, tol=1e-2)
+    assert bad == 0, (bad, first, worst)
+    ref = torch.from_numpy(dense).cuda().float() @ rhs.float() + 2.0
+    assert torch.allclose(out.T.float(), ref, rtol=1e-2, atol=1e-2)
+    # second call hits the prepared-operand cache and a non-default stream works
+    n0 = spatha.cache_size()
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        out2 = spatha.spmm(meta, idx, values, rhs, bias, M, K, N, V, 2, m, values.numel(), 0, 32, 4)
+    s.synchronize()
+    assert spatha.cache_size() == n0 and torch.equal(out, out2)
+
+
+def test_spatha_spmm_rejects_bad_arguments(spatha):
+    import torch
+    z = torch.zeros(8, dtype=torch.int32, device="cuda")
+    v = torch.zeros(8, dtype=torch.float16, device="cuda")
+    with pytest.raises(RuntimeError):
+        spatha.spmm(z, z, v, torch.zeros((64, 64), dtype=torch.float16, device="cuda"), None, 64, 64, 64, 32, 2, 8, 8, 0, 32, 4)
+
+
+def test_srnm_spmm_module_replaces_linear(spatha):
+    import torch
+    from venom_b200.nmv import SrnmSpmm, linear_to_spmm
+    torch.manual_seed(0)
+    lin = torch.nn.Linear(1024, 512).half().cuda()
+    sp = SrnmSpmm(lin, n=2, m=8, v=64)
+    x = (torch.rand((4, 96, 1024), device="cuda") - 0.5).half()
+    y = sp(x)
+    assert tuple(y.shape) == (4, 96, 512)
+    # fixed pattern of the reference sparsifier: columns 0 and 2 of every group of 8
+    mask = torch.zeros(1024, device="cuda")
+    mask[0::8] = 1
+    mask[2::8] = 1
+    want = torch.nn.functional.linear(x.float(), lin.weight.float() * mask, lin.bias.float())
+    assert torch.allclose(y.float(), want, rtol=2e-2, atol=2e-2)
+    model = torch.nn.Sequential(torch.nn.Linear(256, 512), torch.nn.GELU(), torch.nn.Linear(512, 256)).half().cuda()
+    linear_to_spmm(model, 2, 8, 128)
+    assert isinstance(model[0], SrnmSpmm) and isinstance(model[2], SrnmSpmm)
+    assert tuple(model(x[..., :256]).shape) == (4, 96, 256)
+
+
+@pytest.mark.parametrize("flags", [
+    "--m 1024 --k 4096 --n 4096 --bm 64 --mm_row 8",
+    "--m 1024 --k 1024 --n 2048 --bm 128 --mm_row 4",
+    "--m 512 --k 2000 --n 1024 --bm 32 --mm_row 20",
+])
+def test_benchmark_spmm_cli_check(flags):
+    exe = os.path.join(ROOT, "venom_b200", "benchmark_spmm")
+    assert os.path.exists(exe), "CLI not built: python -m venom_b200.build"
+    cmd = (exe + " --sparsity-type n-to-m --spmm spatha --gemm cuBlas --precision half --meta-block-size 32 --block-size 4 "
+           "--nn_row 2 --d 0.5 --bn 64 --bk 32 --wm 32 --wn 64 --wk 32 --mm 16 --mn 8 --mk 32 --nstage 2 --check " + flags)
+    r = subprocess.run(cmd.split(), capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr
+    cols = r.stdout.strip().splitlines()[-1].split(",")
+    assert len(cols) == 26 and cols[0] == "2" and cols[1] == "sm_100a"
+    assert cols[23] == "0", "check failed: " + r.stdout
+    assert float(cols[20]) > 0 and float(cols[21]) > 0

@@ -1,0 +1,108 @@
+// PyTorch extension `spatha`: the same module name, function name, positional arguments and return
+// shape as the reference's extension (end2end/spatha_mod/block_sparse/api/spatha.cu:41-65 ->
+// spmm_cuda, end2end/spatha_mod/block_sparse/spmm/blockwise_library.cu:294-386), implemented as a
+// thin pybind wrapper over the C ABI of libvenom_b200.  Differences, all deliberate:
+//   * runs on torch's current CUDA stream (the reference launches on the legacy default stream);
+//   * V is a run-time argument (the reference needs a separate -DV_64 build);
+//   * arguments are checked and errors raise RuntimeError (the reference checks nothing);
+//   * `bias` may be an undefined / empty tensor (the reference dereferences it unconditionally);
+//   * the reference-format arrays are re-packed once per distinct (values, metadata, indices) triple
+//     and the prepared operand is cached; call spatha.clear_cache() after modifying them in place.
+#include <torch/extension.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <c10/cuda/CUDAStream.h>
+
+#include <map>
+#include <mutex>
+#include <tuple>
+
+#include "../../include/venom_b200.h"
+
+namespace {
+
+struct Key {
+    const void *values, *meta, *idx;
+    int M, K, V, n, m, device;
+    uint32_t ver_v, ver_m, ver_i;
+    bool operator<(const Key &o) const
+    {
+        return std::tie(values, meta, idx, M, K, V, n, m, device, ver_v, ver_m, ver_i) <
+               std::tie(o.values, o.meta, o.idx, o.M, o.K, o.V, o.n, o.m, o.device, o.ver_v, o.ver_m, o.ver_i);
+    }
+};
+
+std::map<Key, vnm_handle_t> g_cache;
+std::mutex g_mutex;
+
+void check(int rc, const char *what)
+{
+    TORCH_CHECK(rc == 0, what, " failed (", rc, "): ", vnm_last_error_string());
+}
+
+}  // namespace
+
+torch::Tensor spmm(torch::Tensor A_metadata, torch::Tensor A_indices, torch::Tensor A_values, torch::Tensor rhs_matrix,
+                   c10::optional<torch::Tensor> bias, int64_t A_num_rows, int64_t A_num_cols, int64_t B_num_cols,
+                   int64_t vec_length, int64_t n, int64_t m, int64_t nnz, int64_t seed, int64_t mbrow, int64_t brow)
+{
+    (void)seed;
+    TORCH_CHECK(A_values.is_cuda() && A_metadata.is_cuda() && A_indices.is_cuda() && rhs_matrix.is_cuda(), "spatha.spmm: CUDA tensors expected");
+    TORCH_CHECK(A_values.scalar_type() == torch::kFloat16 && rhs_matrix.scalar_type() == torch::kFloat16, "spatha.spmm: fp16 values / rhs expected");
+    TORCH_CHECK(A_metadata.scalar_type() == torch::kInt32 && A_indices.scalar_type() == torch::kInt32, "spatha.spmm: int32 metadata / indices expected");
+    TORCH_CHECK(mbrow == 32 && brow == 4, "spatha.spmm: the storage format is defined for mbrow = 32, brow = 4");
+    TORCH_CHECK(A_values.is_contiguous() && A_metadata.is_contiguous() && A_indices.is_contiguous(), "spatha.spmm: contiguous sparse arrays expected");
+    const int M = (int)A_num_rows, K = (int)A_num_cols, N = (int)B_num_cols, V = (int)vec_length;
+    int64_t ksp = 0, nv = 0, nm = 0, nc = 0;
+    check(vnm_sizes(M, K, V, (int)n, (int)m, &ksp, &nv, &nm, &nc), "vnm_sizes");
+    TORCH_CHECK(A_values.numel() == nv && A_metadata.numel() == nm && A_indices.numel() == nc, "spatha.spmm: array sizes do not match the format (values ",
+                nv, ", metadata ", nm, ", indices ", nc, ")");
+    TORCH_CHECK(nnz == nv, "spatha.spmm: nnz must be A_num_rows * padded compressed columns (", nv, ")");
+    TORCH_CHECK(rhs_matrix.dim() == 2 && rhs_matrix.size(0) == K && rhs_matrix.size(1) == N && rhs_matrix.stride(1) == 1,
+                "spatha.spmm: rhs_matrix must be [A_num_cols, B_num_cols] with unit inner stride");
+    const bool has_bias = bias.has_value() && bias->defined() && bias->numel() > 0;
+    if (has_bias) TORCH_CHECK(bias->is_cuda() && bias->scalar_type() == torch::kFloat16 && bias->numel() == M && bias->is_contiguous(), "spatha.spmm: bias must be fp16 [A_num_rows]");
+
+    c10::cuda::CUDAGuard guard(rhs_matrix.device());
+    cudaStream_t stream = c10::cuda::getCurrentCUDAStream().stream();
+    Key key{A_values.data_ptr(), A_metadata.data_ptr(), A_indices.data_ptr(), M, K, V, (int)n, (int)m, (int)rhs_matrix.device().index(),
+            (uint32_t)A_values._version(), (uint32_t)A_metadata._version(), (uint32_t)A_indices._version()};
+    vnm_handle_t h = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_mutex);
+        auto it = g_cache.find(key);
+        if (it == g_cache.end()) {
+            check(vnm_prepare(A_values.data_ptr(), (const uint32_t *)A_metadata.data_ptr(), (const uint32_t *)A_indices.data_ptr(), M, K, V,
+                              (int)n, (int)m, &h, stream), "vnm_prepare");
+            g_cache.emplace(key, h);
+        } else {
+            h = it->second;
+        }
+    }
+    auto out = torch::empty({N, M}, rhs_matrix.options());
+    check(vnm_spmm_f16(h, rhs_matrix.data_ptr(), rhs_matrix.stride(0), N, has_bias ? bias->data_ptr() : nullptr, out.data_ptr(), M,
+                       VNM_LAYOUT_NM, stream), "vnm_spmm_f16");
+    return out;
+}
+
+void clear_cache()
+{
+    std::lock_guard<std::mutex> lock(g_mutex);
+    for (auto &kv : g_cache) vnm_destroy(kv.second);
+    g_cache.clear();
+}
+
+int64_t cache_size()
+{
+    std::lock_guard<std::mutex> lock(g_mutex);
+    return (int64_t)g_cache.size();
+}
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, mod)
+{
+    mod.def("spmm", &spmm, "V:N:M sparse x dense product (returns [B_num_cols, A_num_rows])", pybind11::arg("A_metadata"), pybind11::arg("A_indices"),
+            pybind11::arg("A_values"), pybind11::arg("rhs_matrix"), pybind11::arg("bias"), pybind11::arg("A_num_rows"), pybind11::arg("A_num_cols"),
+            pybind11::arg("B_num_cols"), pybind11::arg("vec_length"), pybind11::arg("n"), pybind11::arg("m"), pybind11::arg("nnz"),
+            pybind11::arg("seed"), pybind11::arg("mbrow"), pybind11::arg("brow"));
+    mod.def("clear_cache", &clear_cache, "Drop every cached prepared operand");
+    mod.def("cache_size", &cache_size);
+}
