@@ -192,6 +192,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--e2e-steps", type=int, default=3)
+    ap.add_argument("--kernel-only", action="store_true", help="skip the e2e, cuBLAS and CPU legs (used for ncu captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -275,6 +276,14 @@ def main():
     flops_step = sum(useful_flops(M, K, m, N) for (M, K, V, m, N) in points)
     bytes_step = sum(algorithmic_bytes(M, K, V, m, N) for (M, K, V, m, N) in points)
     value = world * flops_step / (ms_step * 1e-3) / 1e12
+
+    if args.kernel_only:
+        if rank == 0:
+            print(json.dumps({"metric": METRIC, "value": value, "unit": UNIT, "ms_per_step": ms_step, "kernel_only": True,
+                              "per_launch_ms": [round(t, 5) for t in per_launch]}), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return
 
     # ---- end to end through the host-buffer C-ABI entry point (pinned host memory) ----
     hB = {K: torch.empty((K, N_COLS), dtype=torch.float16).pin_memory() for K in Bs}
