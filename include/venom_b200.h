@@ -93,6 +93,29 @@ int vnm_spmm_f16(vnm_handle_t handle, const void *B, int64_t ldb, int N,
 int vnm_spmm_f16_host(vnm_handle_t handle, const void *B_host, int N, const void *bias_host,
                       void *out_host, int layout, void *stream);
 
+/* The same product for callers that cannot allocate device memory (no counterpart in the reference, whose
+ * device format always comes from cudaMalloc).  Think of a serving process whose framework already owns
+ * the whole device, a plug-in living inside another component's memory budget, or a loop that cannot take
+ * the device-wide synchronisation of cudaMalloc / cudaFree.  The re-packed copy of the sparse operand,
+ * which vnm_prepare would allocate, is written into an array built into the library instead
+ * (VNM_NOALLOC_SCRATCH_BYTES per GPU that loads the library, held until the process exits), then the
+ * product runs from it.  The call performs no cudaMalloc / cudaFree and uses no allocating library routine.
+ *   - takes the reference-format arrays directly (same meaning as in vnm_prepare) plus the arguments of
+ *     vnm_spmm_f16; re-packs on every call, so it suits small operands and occasional calls;
+ *   - operands whose re-packed form (about 1.13 x 2*M*Ksp bytes) exceeds the limit are rejected with
+ *     VNM_ERR_UNSUPPORTED and a message naming both sizes;
+ *   - the first call on a device also looks up the array's device address and sets kernel attributes: make
+ *     that first call before starting any stream capture;
+ *   - all calls on a device share the one array and it keeps the previous call's contents (the call clears
+ *     what has to start at zero itself): two calls whose GPU work overlaps -- different streams or host
+ *     threads -- race on it, so serialise them;
+ *   - returns after the product has finished on `stream` (it synchronises the stream to read the device
+ *     status word back); failures also print one line to stderr. */
+#define VNM_NOALLOC_SCRATCH_BYTES (8 * 1024 * 1024)
+int vnm_spmm_f16_noalloc(const void *values, const uint32_t *meta, const uint32_t *colloc,
+                         int M, int K, int V, int n, int m,
+                         const void *B, int64_t ldb, int N, const void *bias, void *out, int64_t ldo, int layout, void *stream);
+
 /* Reads and clears the sticky device-side status word of the handle (0 = no bounded wait ever gave
  * up).  Synchronises `stream`. */
 int vnm_device_status(vnm_handle_t handle, int *status, void *stream);
