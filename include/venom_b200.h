@@ -129,6 +129,15 @@ int vnm_device_status(vnm_handle_t handle, int *status, void *stream);
  * 2 = B is not loaded at all (timing floor; results are meaningless).
  * Producer warps: 4 or 8 warps issue the gather loads (default 8). */
 int vnm_set_gather_mode(vnm_handle_t handle, int mode);
+
+/* How vnm_prepare lays the sparse operand out for the kernel (process-wide, applies to later calls):
+ *   AUTO     pick per (V, m) from measurements on B200 (default);
+ *   GATHER   the V:N:M form: only the four selected rows of B per group are gathered per vector block;
+ *   DENSE_B  the pattern re-expressed as plain 2:4 over all K columns (needs m % 4 == 0 and K % m == 0):
+ *            B is read as ordinary tiles shared by all vector blocks, at m/4 times the MMA work.
+ * Both forms give the same result up to fp32 summation order. */
+enum { VNM_STRATEGY_AUTO = 0, VNM_STRATEGY_GATHER = 1, VNM_STRATEGY_DENSE_B = 2 };
+int vnm_set_strategy(int strategy);
 int vnm_set_producer_warps(vnm_handle_t handle, int warps);
 
 /* Kernel configuration that vnm_spmm_f16 would launch for this handle and N (for reporting). */

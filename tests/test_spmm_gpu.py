@@ -159,3 +159,28 @@ def test_gather_modes_agree_when_every_row_is_selected(capi, oracle):
     c = prep.spmm(Bd)
     assert prep.device_status() == 0
     assert torch.equal(a, b) and torch.equal(a, c)
+
+
+@pytest.mark.parametrize("shape", [(128, 512, 128, 4, 256), (256, 1024, 128, 8, 512), (192, 768, 64, 8, 200), (128, 1024, 32, 16, 64),
+                                   (96, 512, 32, 32, 72), (256, 2048, 64, 16, 384)])
+@pytest.mark.parametrize("strategy", ["gather", "dense_b"])
+def test_both_operand_forms_match_oracle(capi, oracle, shape, strategy):
+    """The V:N:M gather form and the dense-B form (2:4 over all K columns) are interchangeable."""
+    M, K, V, m, N = shape
+    capi.set_strategy(capi.STRATEGY_GATHER if strategy == "gather" else capi.STRATEGY_DENSE_B)
+    try:
+        for ints in (True, False):
+            prep, Bd, (ov, om, cols, B) = _setup(capi, oracle, M, K, V, m, N, seed=3 * M + K, ints=ints)
+            out = prep.spmm(Bd)
+            assert prep.device_status() == 0
+            want = oracle.spmm(ov, om, cols, M, K, V, m, B)
+            if ints:
+                assert np.array_equal(out.cpu().numpy().view(np.uint16), want.view(np.uint16))
+            else:
+                _check(oracle, out.cpu().numpy(), want)
+            import torch
+            bias = np.random.default_rng(7).uniform(-1, 1, M).astype(np.float16)
+            outT = prep.spmm(Bd, bias=torch.from_numpy(bias).cuda(), layout=capi.VNM_LAYOUT_NM)
+            _check(oracle, outT.cpu().numpy(), oracle.spmm(ov, om, cols, M, K, V, m, B, bias=bias, layout=1))
+    finally:
+        capi.set_strategy(capi.STRATEGY_AUTO)

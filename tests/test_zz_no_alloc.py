@@ -46,7 +46,13 @@ def test_noalloc_matches_regular_path_on_two_calls_in_a_row(oracle):
     for (M, K, V, m, N, layout) in cases:
         values, meta, cols, B = _operands(oracle, M, K, V, m, N, seed=M + N)
         bias = (torch.rand(M, device="cuda") - 0.5).half() if layout == 1 else None
-        want = capi.Prepared(values, meta, cols, M, K, V, m).spmm(B, bias=bias, layout=layout)
+        # the built-in-scratch entry point always uses the gather form of the operand; ask the regular
+        # path for the same form so that the two results can be compared bit for bit
+        capi.set_strategy(capi.STRATEGY_GATHER)
+        try:
+            want = capi.Prepared(values, meta, cols, M, K, V, m).spmm(B, bias=bias, layout=layout)
+        finally:
+            capi.set_strategy(capi.STRATEGY_AUTO)
         got = torch.full_like(want, float("nan"))
         rc = _call_noalloc(lib, values, meta, cols, M, K, V, m, B, got, bias=bias, layout=layout)
         assert rc == 0

@@ -46,6 +46,8 @@ def lib():
         L.vnm_spmm_config.argtypes = [C.c_void_p, C.c_int] + [C.POINTER(C.c_int)] * 5
         L.vnm_set_gather_mode.argtypes = [C.c_void_p, C.c_int]
         L.vnm_set_gather_mode.restype = C.c_int
+        L.vnm_set_strategy.argtypes = [C.c_int]
+        L.vnm_set_strategy.restype = C.c_int
         L.vnm_set_producer_warps.argtypes = [C.c_void_p, C.c_int]
         L.vnm_set_producer_warps.restype = C.c_int
         for name in ("vnm_sizes", "vnm_compress_f16", "vnm_decompress_f16", "vnm_prepare", "vnm_prepared_bytes",
@@ -53,6 +55,14 @@ def lib():
             getattr(L, name).restype = C.c_int
         _lib = L
     return _lib
+
+
+STRATEGY_AUTO, STRATEGY_GATHER, STRATEGY_DENSE_B = 0, 1, 2
+
+
+def set_strategy(strategy):
+    """Layout chosen by later Prepared(...) constructions: auto / gather (V:N:M form) / dense-B (2:4 over all K)."""
+    _check(lib().vnm_set_strategy(strategy))
 
 
 def _check(rc):

@@ -68,6 +68,20 @@ EncodeTiledFn get_encode_fn()
 }
 
 bool g_kernels_ready = false;
+int g_strategy = 0;  // VNM_STRATEGY_*
+
+// Gather form vs dense-B form (see vnm_set_strategy in the header).  Measured on B200: the gather path is
+// bound by the TMA gather rate and pays NB = 128/V times for small vector lengths, the dense-B form costs
+// m/4 times the MMA work but shares B between all vector blocks.
+bool choose_dense_b(int K, int V, int m)
+{
+    const bool possible = (m % 4 == 0) && (K % m == 0);
+    if (!possible || g_strategy == VNM_STRATEGY_GATHER) return false;
+    if (g_strategy == VNM_STRATEGY_DENSE_B) return true;
+    if (V == 128) return false;
+    if (V == 64) return m <= 8;
+    return m <= 16;  // V == 32
+}
 
 }  // namespace
 
@@ -95,6 +109,7 @@ struct vnm_prepared_s {
     void *stage_bias;
     int gather_mode;
     long long *trace;  // debug builds only
+    int dense_b;       // 1: A re-expressed as 2:4 over all K columns, B read as plain tiles
 };
 
 extern "C" {
@@ -144,8 +159,9 @@ int vnm_prepared_bytes(int M, int K, int V, int n, int m, int64_t *bytes)
     if (rc) return rc;
     if (V != 32 && V != 64 && V != 128) return fail(VNM_ERR_UNSUPPORTED, "SpMM supports V in {32, 64, 128} (got %d)", V);
     const int64_t Ksp = ksp_of(K, m);
-    const int64_t mtiles = (M + TILE_M - 1) / TILE_M, ktiles = (Ksp + KT_COMP - 1) / KT_COMP;
-    const int64_t nb = TILE_M / V;
+    const bool dense_b = choose_dense_b(K, V, m);
+    const int64_t mtiles = (M + TILE_M - 1) / TILE_M, ktiles = dense_b ? (K + 127) / 128 : (Ksp + KT_COMP - 1) / KT_COMP;
+    const int64_t nb = dense_b ? 1 : TILE_M / V;
     if (bytes) *bytes = mtiles * ktiles * AM_BLOCK_BYTES + mtiles * nb * ktiles * KT_GROUPS * 16 + 256;
     return VNM_OK;
 }
@@ -168,18 +184,29 @@ int vnm_prepare(const void *values, const uint32_t *meta, const uint32_t *colloc
     h->M = M; h->K = K; h->V = V; h->n = n; h->m = m;
     h->Ksp = ksp_of(K, m);
     h->mtiles = (M + TILE_M - 1) / TILE_M;
-    h->ktiles = (int)((h->Ksp + KT_COMP - 1) / KT_COMP);
-    h->nb = TILE_M / V;
+    h->dense_b = choose_dense_b(K, V, m) ? 1 : 0;
+    if (h->dense_b) {
+        h->ktiles = (K + 127) / 128;  // a k-tile covers 128 original columns
+        h->nb = 1;
+        h->gather_mode = GATHER_CONTIG;
+    } else {
+        h->ktiles = (int)((h->Ksp + KT_COMP - 1) / KT_COMP);
+        h->nb = TILE_M / V;
+        h->gather_mode = (m == 4) ? GATHER_CONTIG : GATHER_TMA4;  // with m == 4 every row of B is selected
+    }
     h->vblocks_padded = h->mtiles * h->nb;
-    h->gather_mode = (m == 4) ? GATHER_CONTIG : GATHER_TMA4;  // with m == 4 every row of B is selected
     h->producer_warps = 8;
     cudaError_t e = cudaGetDevice(&h->device);
     if (e == cudaSuccess) e = cudaMalloc(&h->am, (size_t)h->mtiles * h->ktiles * AM_BLOCK_BYTES);
     if (e == cudaSuccess) e = cudaMalloc(&h->rows, (size_t)h->vblocks_padded * h->ktiles * KT_GROUPS * sizeof(int4));
     if (e == cudaSuccess) e = cudaMalloc((void **)&h->status, sizeof(int));
     if (e == cudaSuccess) e = cudaMemsetAsync(h->status, 0, sizeof(int), (cudaStream_t)stream);
-    if (e == cudaSuccess)
-        e = launch_prepare(values, meta, colloc, M, K, V, m, h->am, h->rows, h->mtiles, h->ktiles, h->vblocks_padded, (cudaStream_t)stream);
+    if (e == cudaSuccess) {
+        if (h->dense_b)
+            e = launch_prepare_dense_b(values, meta, colloc, M, K, V, m, h->am, h->rows, h->mtiles, h->ktiles, (cudaStream_t)stream);
+        else
+            e = launch_prepare(values, meta, colloc, M, K, V, m, h->am, h->rows, h->mtiles, h->ktiles, h->vblocks_padded, (cudaStream_t)stream);
+    }
     if (e != cudaSuccess) {
         vnm_destroy(h);
         return fail_cuda(e, "vnm_prepare");
@@ -205,6 +232,7 @@ int vnm_set_gather_mode(vnm_handle_t h, int mode)
 {
     if (!h) return fail(VNM_ERR_BAD_ARG, "null handle");
     if (mode != GATHER_TMA4 && mode != GATHER_CONTIG && mode != GATHER_NONE) return fail(VNM_ERR_BAD_ARG, "unknown gather mode %d", mode);
+    if (h->dense_b && mode == GATHER_TMA4) return fail(VNM_ERR_BAD_ARG, "this operand was prepared in dense-B form: it has no gather");
     h->gather_mode = mode;
     return VNM_OK;
 }
@@ -219,6 +247,14 @@ int vnm_debug_set_trace(vnm_handle_t h, long long *device_buffer)
 }
 #endif
 
+int vnm_set_strategy(int strategy)
+{
+    if (strategy != VNM_STRATEGY_AUTO && strategy != VNM_STRATEGY_GATHER && strategy != VNM_STRATEGY_DENSE_B)
+        return fail(VNM_ERR_BAD_ARG, "unknown strategy %d", strategy);
+    g_strategy = strategy;
+    return VNM_OK;
+}
+
 int vnm_set_producer_warps(vnm_handle_t h, int warps)
 {
     if (!h) return fail(VNM_ERR_BAD_ARG, "null handle");
@@ -231,7 +267,7 @@ int vnm_spmm_config(vnm_handle_t h, int N, int *tile_m, int *tile_n, int *stages
 {
     if (!h) return fail(VNM_ERR_BAD_ARG, "null handle");
     SpmmConfig cfg;
-    if (!spmm_select_config(h->V, N, h->M, h->producer_warps, &cfg)) return fail(VNM_ERR_UNSUPPORTED, "unsupported V");
+    if (!spmm_select_config(h->dense_b ? 128 : h->V, N, h->M, h->producer_warps, &cfg)) return fail(VNM_ERR_UNSUPPORTED, "unsupported V");
     if (tile_m) *tile_m = TILE_M;
     if (tile_n) *tile_n = cfg.bn;
     if (stages) *stages = cfg.stages;
@@ -256,7 +292,7 @@ int vnm_spmm_f16(vnm_handle_t h, const void *B, int64_t ldb, int N, const void *
         return fail(VNM_ERR_BAD_ARG, "vnm_spmm_f16: unknown layout %d", layout);
     }
     SpmmConfig cfg;
-    if (!spmm_select_config(h->V, N, h->M, h->producer_warps, &cfg)) return fail(VNM_ERR_UNSUPPORTED, "unsupported V");
+    if (!spmm_select_config(h->dense_b ? 128 : h->V, N, h->M, h->producer_warps, &cfg)) return fail(VNM_ERR_UNSUPPORTED, "unsupported V");
 
     if (!h->tm_valid || h->tm_B != B || h->tm_ldb != ldb || h->tm_N != N) {
         EncodeTiledFn enc = get_encode_fn();

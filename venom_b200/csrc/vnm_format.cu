@@ -199,6 +199,117 @@ __global__ void __launch_bounds__(256) prepare_rows_kernel(const uint32_t *__res
     }
 }
 
+// ------------------------------------------------------------------------------------------------
+// "Dense-B" re-pack: the V:2:m pattern re-expressed as plain 2:4 over ALL K columns.
+// A row keeps two entries per group of m columns, so any aligned chunk of four original columns
+// (m % 4 == 0: chunks never straddle groups) holds at most two of them -- a valid 2:4 pattern once the
+// missing slots are filled with explicit zeros.  The product can then read B as ordinary 64-row tiles
+// that every vector block shares (no per-block gather, no lane masks), at the price of m/4 times the MMA
+// work.  Same block format as prepare_am_kernel, but a k-tile now covers 128 ORIGINAL columns.
+// One thread handles one (row pair, 16 original columns): two 16-byte value chunks and one metadata word.
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) prepare_dense_b_kernel(const __half *__restrict__ values, const uint32_t *__restrict__ meta,
+                                                              const uint32_t *__restrict__ colloc, int M, int K, int V, int m, int64_t Ksp,
+                                                              int mtiles, int ktiles, uint8_t *__restrict__ am)
+{
+    const int64_t total = (int64_t)mtiles * ktiles * 64 * 8;
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+        const int q = (int)(idx & 7);          // 16-column slab of the 128-column k-tile
+        const int pr = (int)((idx >> 3) & 63);  // row pair inside the 128-row tile
+        const int64_t blk = idx >> 9;
+        const int mt = (int)(blk / ktiles);
+        const int kt = (int)(blk - (int64_t)mt * ktiles);
+        uint8_t *block = am + blk * AM_BLOCK_BYTES;
+        uint32_t word = 0;
+        const int i0 = actual_to_mma_row(2 * pr);  // MMA row of the even row; the odd row sits 8 rows further
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const int64_t r = (int64_t)mt * TILE_M + 2 * pr + h;
+            unsigned short v8[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            uint32_t nib16 = 0;
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+                const int64_t cb = (int64_t)kt * 128 + q * 16 + c * 4;  // first original column of the chunk
+                int npos = 0;
+                uint32_t pos[2] = {0, 1};
+                unsigned short val[2] = {0, 0};
+                if (r < M && cb < K) {
+                    const int64_t g = cb / m;
+                    const int o0 = (int)(cb - g * m);
+                    const uint32_t w = meta[meta_index(r, g, Ksp)];
+                    const uint32_t *c4 = colloc + (r / V) * (Ksp / 2) * 4 + g * 4;
+#pragma unroll
+                    for (int sl = 0; sl < 2; sl++) {
+                        const uint32_t sel = (w >> meta_shift(r, g, sl)) & 3u;
+                        const int off = (int)c4[sel] - o0;
+                        if (off >= 0 && off < 4 && npos < 2 && cb + off < K) {
+                            pos[npos] = (uint32_t)off;
+                            val[npos] = __half_as_ushort(values[values_index(r, g, sl, Ksp)]);
+                            npos++;
+                        }
+                    }
+                }
+                if (npos == 1) {  // partner slot with an explicit zero, positions kept ascending
+                    if (pos[0] == 3) { pos[1] = 3; pos[0] = 2; val[1] = val[0]; val[0] = 0; }
+                    else { pos[1] = pos[0] + 1; val[1] = 0; }
+                } else if (npos == 0) {
+                    pos[0] = 0; pos[1] = 1;
+                } else if (pos[0] == pos[1]) {  // duplicate offsets only arise from padded slots (zero values)
+                    if (pos[0] == 3) pos[0] = 2; else pos[1] = pos[0] + 1;
+                }
+                v8[2 * c] = val[0];
+                v8[2 * c + 1] = val[1];
+                nib16 |= (pos[0] | (pos[1] << 2)) << (4 * c);
+            }
+            word |= nib16 << (16 * h);
+            const int i = i0 + 8 * h;
+            uint4 o;
+            o.x = (uint32_t)v8[0] | ((uint32_t)v8[1] << 16);
+            o.y = (uint32_t)v8[2] | ((uint32_t)v8[3] << 16);
+            o.z = (uint32_t)v8[4] | ((uint32_t)v8[5] << 16);
+            o.w = (uint32_t)v8[6] | ((uint32_t)v8[7] << 16);
+            *reinterpret_cast<uint4 *>(block + i * 128 + ((q ^ (i & 7)) << 4)) = o;
+        }
+        const int lane = (i0 & 7) + 8 * (q & 1) + 16 * (i0 >> 4);
+        *reinterpret_cast<uint32_t *>(block + A_IMG_BYTES + (lane * 4 + (q >> 1)) * 4) = word;
+    }
+}
+
+// Row table of the dense-B form: stage j of a tile starts at original row 64*j.
+__global__ void __launch_bounds__(256) prepare_dense_b_rows_kernel(int K, int mtiles, int ktiles, int4 *__restrict__ rows)
+{
+    const int64_t per_tile = (int64_t)ktiles * KT_GROUPS;
+    const int64_t total = (int64_t)mtiles * per_tile;
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t g = idx % per_tile;
+        const int64_t k = g * 4;
+        rows[idx] = k < K ? make_int4((int)k, (int)k + 1, (int)k + 2, (int)k + 3) : make_int4(K, K, K, K);
+    }
+}
+
+cudaError_t launch_prepare_dense_b(const void *values, const uint32_t *meta, const uint32_t *colloc, int M, int K, int V, int m,
+                                   void *am, void *rows, int mtiles, int ktiles, cudaStream_t stream)
+{
+    const int64_t Ksp = ksp_of(K, m);
+    const int64_t cap = (int64_t)148 * 64;
+    {
+        const int64_t total = (int64_t)mtiles * ktiles * 512;
+        int64_t blocks = (total + 255) / 256;
+        if (blocks > cap) blocks = cap;
+        prepare_dense_b_kernel<<<(unsigned)blocks, 256, 0, stream>>>((const __half *)values, meta, colloc, M, K, V, m, Ksp, mtiles, ktiles,
+                                                                   (uint8_t *)am);
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return e;
+    }
+    {
+        const int64_t total = (int64_t)mtiles * ktiles * KT_GROUPS;
+        int64_t blocks = (total + 255) / 256;
+        if (blocks > cap) blocks = cap;
+        prepare_dense_b_rows_kernel<<<(unsigned)blocks, 256, 0, stream>>>(K, mtiles, ktiles, (int4 *)rows);
+        return cudaGetLastError();
+    }
+}
+
 cudaError_t launch_prepare(const void *values, const uint32_t *meta, const uint32_t *colloc, int M, int K, int V, int m,
                            void *am, void *rows, int mtiles, int ktiles, int vblocks_padded, cudaStream_t stream)
 {

@@ -16,9 +16,11 @@
 //                     (four absolute row numbers per instruction, precomputed by the prepare step);
 //                     spreading the loads over many warps matters because a warp issues them one lane
 //                     after the other.
-//   warp PB+1         tensor-memory allocation and MMA issue: metadata image -> tensor memory
-//                     (tcgen05.cp), tcgen05.mma.sp; for NB > 1 each MMA runs on all 128 rows of the
-//                     value tile with the output lanes of the other blocks disabled.
+//   warp PB+1         sequencer: per k-tile waits for the A block, copies the metadata image to tensor
+//                     memory (tcgen05.cp) and waits for both B stages, then flips one "ready" barrier.
+//   warp PB+2         tensor-memory allocation and MMA issue: one wait, 4 * NB tcgen05.mma.sp and one
+//                     tcgen05.commit per k-tile; for NB > 1 each MMA runs on all 128 rows of the value
+//                     tile with the output lanes of the other blocks disabled.
 //   last four warps   epilogue: tcgen05.ld -> packed fp16 registers, release the accumulator, store
 //                     ([M,N], or [N,M] with fused bias).
 // Producers run ahead into the next tile while the epilogue drains.  Every wait is bounded: on expiry
@@ -59,11 +61,14 @@ struct Traits {
     static constexpr int B_RING_BYTES = SB * B_STAGE_BYTES;
     static constexpr int BAR_BYTES = 256;
     static constexpr int SMEM_BYTES = A_RING_BYTES + B_RING_BYTES + BAR_BYTES + 1024;  // + alignment slack
-    static constexpr int MMA_WARP = 1 + PB;
-    static constexpr int NUM_WARPS = 1 + PB + 1 + 4;
+    static constexpr int SEQ_WARP = 1 + PB;      // sequencer: waits for the operands of a k-tile, copies its metadata
+    static constexpr int MMA_WARP = 2 + PB;      // MMA issuer (and tensor-memory owner)
+    static constexpr int NUM_WARPS = 3 + PB + 4;
     static constexpr int NUM_THREADS = NUM_WARPS * 32;
-    static_assert(2 * (SA + SB) * 8 + 32 <= BAR_BYTES, "barrier area too small");
-    static_assert(SB >= 2 * SA - 1, "the A producer reuses the B-stage barriers: see the A producer");
+    static constexpr int SR = 4;                 // "k-tile ready" barriers (sequencer -> MMA issuer)
+    static_assert((2 * (SA + SB) + 8) * 8 + 32 <= BAR_BYTES - 16, "barrier area too small");
+    static constexpr int SP = 4;  // "k-tile done" barriers (one tcgen05.commit per k-tile releases its A stage and both B stages)
+    static_assert(SP >= SA && 2 * SP >= SB + 1, "too few k-tile barriers: a waiter could miss a phase");
 };
 
 // Whole-warp bounded wait on an mbarrier phase; lane 0 polls.  Returns false if the wait expired or
@@ -135,7 +140,9 @@ __global__ void __launch_bounds__(Traits<BN, NB, SA, SB, PB>::NUM_THREADS, 1)
     uint64_t *a_empty = a_full + SA;
     uint64_t *b_full = a_empty + SA;
     uint64_t *b_empty = b_full + SB;
-    uint64_t *acc_full_bar = b_empty + SB;
+    uint64_t *kdone = b_empty + SB;
+    uint64_t *kready = kdone + T::SP;
+    uint64_t *acc_full_bar = kready + T::SR;
     uint64_t *acc_empty_bar = acc_full_bar + 1;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty_bar + 1);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
@@ -148,6 +155,8 @@ __global__ void __launch_bounds__(Traits<BN, NB, SA, SB, PB>::NUM_THREADS, 1)
     if (threadIdx.x == 0) {
         for (int s = 0; s < SA; s++) { mbar_init(&a_full[s], 1); mbar_init(&a_empty[s], 1); }
         for (int s = 0; s < SB; s++) { mbar_init(&b_full[s], 1); mbar_init(&b_empty[s], 1); }
+        for (int s = 0; s < T::SP; s++) mbar_init(&kdone[s], 1);
+        for (int s = 0; s < T::SR; s++) mbar_init(&kready[s], 2);  // metadata copy done + operands landed
         mbar_init(acc_full_bar, 1);
         mbar_init(acc_empty_bar, 4);
         *abort_flag = 0;
@@ -172,12 +181,9 @@ __global__ void __launch_bounds__(Traits<BN, NB, SA, SB, PB>::NUM_THREADS, 1)
                 for (int kt = 0; kt < p.ktiles; ++kt, ++it) {
                     const int s = it % SA;
                     if (it >= SA) {
-                        // slot s was last used by k-tile it - SA; it is free once the MMAs of that k-tile's
-                        // second B stage (ring position jb) have completed.  That barrier cannot advance a
-                        // further phase before this k-tile is loaded, because B stage jb + SB belongs to
-                        // k-tile it - SA + SB/2 + ... >= it (SB >= 2 * SA - 1), which needs this slot.
-                        const int jb = 2 * (it - SA) + 1;
-                        if (!wait_one(&b_empty[jb % SB], (uint32_t)(jb / SB) & 1u, abort_flag, p.status, DEV_TIMEOUT_PRODUCER)) { alive = false; break; }
+                        // slot s was last used by k-tile it - SA: free once that k-tile's MMAs have completed
+                        const int kd = it - SA;
+                        if (!wait_one(&kdone[kd % T::SP], (uint32_t)(kd / T::SP) & 1u, abort_flag, p.status, DEV_TIMEOUT_PRODUCER)) { alive = false; break; }
                     }
                     TRACE(0, it);
                     mbar_arrive_expect_tx(&a_full[s], AM_BLOCK_BYTES);
@@ -224,7 +230,11 @@ __global__ void __launch_bounds__(Traits<BN, NB, SA, SB, PB>::NUM_THREADS, 1)
                 int4 r_nxt = make_int4(0, 0, 0, 0);
                 if (nvalid && (gather_lane || tile_lane)) r_nxt = __ldg(rows_of(ntile, njl));
                 const int s = j % SB;
-                if (!wait_one(&b_empty[s], ((uint32_t)(j / SB) & 1u) ^ 1u, abort_flag, p.status, DEV_TIMEOUT_PRODUCER)) break;
+                if (j >= SB) {
+                    // slot s was last used by stage j - SB, the half of k-tile (j - SB) / 2
+                    const int kd = (j - SB) >> 1;
+                    if (!wait_one(&kdone[kd % T::SP], (uint32_t)(kd / T::SP) & 1u, abort_flag, p.status, DEV_TIMEOUT_PRODUCER)) break;
+                }
                 uint8_t *st = b_ring + s * T::B_STAGE_BYTES;
                 const int n0 = (tile / p.mtiles) * BN;
                 if (leader) {
@@ -243,11 +253,39 @@ __global__ void __launch_bounds__(Traits<BN, NB, SA, SB, PB>::NUM_THREADS, 1)
             }
         }
         __syncwarp();
+    } else if (warp == T::SEQ_WARP) {
+        // ---------------- sequencer (one thread) ----------------
+        // Takes every wait except one off the MMA issuer: per k-tile it waits for the value/metadata block,
+        // copies the metadata image to tensor memory (its own tcgen05.cp, tracked by a tcgen05.commit that
+        // arrives on the k-tile's "ready" barrier), waits for both B stages and arrives on the same barrier.
+        if (lane == 0) {
+            const uint32_t meta0 = tmem_base + T::ACC_COLS;
+            const uint64_t mdesc0 = make_smem_desc(smem_u32(a_ring) + A_IMG_BYTES, 0, 128, 0);
+            const int my_tiles = (p.total_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+            const int total_it = my_tiles * p.ktiles;
+            bool alive = true;
+            for (int it = 0; alive && it < total_it; ++it) {
+                const int sa = it % SA;
+                // the column set it & 1 was last read by the MMAs of k-tile it - 2
+                if (it >= 2 && !wait_one(&kdone[(it - 2) % T::SP], (uint32_t)((it - 2) / T::SP) & 1u, abort_flag, p.status, DEV_TIMEOUT_MMA)) break;
+                if (!wait_one(&a_full[sa], (uint32_t)(it / SA) & 1u, abort_flag, p.status, DEV_TIMEOUT_MMA)) break;
+                tc_fence_after();
+                // metadata image: 128 rows x 16 bytes, 8-row core matrices stored back to back
+                tc_cp_128x128b(meta0 + (uint32_t)(it & 1) * 4u, mdesc0 + ((uint32_t)(sa * AM_BLOCK_BYTES) >> 4));
+                tc_commit(&kready[it % T::SR]);
+                for (int h = 0; h < 2; ++h) {
+                    const int j = 2 * it + h;
+                    if (!wait_one(&b_full[j % SB], (uint32_t)(j / SB) & 1u, abort_flag, p.status, DEV_TIMEOUT_MMA)) { alive = false; break; }
+                }
+                if (alive) mbar_arrive(&kready[it % T::SR]);
+            }
+        }
+        __syncwarp();
     } else if (warp == T::MMA_WARP) {
         // ---------------- MMA issuer (one thread) ----------------
-        // The metadata image of k-tile it+1 is copied to tensor memory before the MMAs of k-tile it are
-        // issued, so that the copy never sits on the critical path.  One commit per B stage: the commit of
-        // the second half of a k-tile also releases the A stage (the A producer waits on that barrier).
+        // One wait per k-tile (its "ready" barrier), 4 * NB MMAs, one tcgen05.commit that releases the
+        // k-tile's A stage and both of its B stages.  Anything else on this thread would sit between two
+        // MMAs: the tensor pipe accepts them nearly one at a time, so issue-side work is not hidden.
         if (lane == 0) {
             const uint32_t acc = tmem_base;
             const uint32_t meta0 = tmem_base + T::ACC_COLS;
@@ -255,41 +293,25 @@ __global__ void __launch_bounds__(Traits<BN, NB, SA, SB, PB>::NUM_THREADS, 1)
             // descriptor templates: only the start-address field (low 14 bits, in 16-byte units) varies
             const uint64_t adesc0 = make_smem_desc(smem_u32(a_ring), 16, 1024, 2);
             const uint64_t bdesc0 = make_smem_desc(smem_u32(b_ring), T::B_CHUNK_BYTES, 1024, 2);
-            const uint64_t mdesc0 = make_smem_desc(smem_u32(a_ring) + A_IMG_BYTES, 0, 128, 0);
             const int my_tiles = (p.total_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
-            const int total_it = my_tiles * p.ktiles;
-            int it = 0, j = 0;
-            bool alive = total_it > 0;
-            if (alive) {
-                alive = wait_one(&a_full[0], 0u, abort_flag, p.status, DEV_TIMEOUT_MMA);
-                if (alive) { tc_fence_after(); tc_cp_128x128b(meta0, mdesc0); }
-            }
+            int it = 0;
+            bool alive = true;
             for (int ti = 0; alive && ti < my_tiles; ++ti) {
                 // the epilogue must have read the previous tile's accumulator
                 TRACE(7, ti * 2);
                 if (!wait_one(acc_empty_bar, ((uint32_t)ti & 1u) ^ 1u, abort_flag, p.status, DEV_TIMEOUT_MMA)) break;
                 tc_fence_after();
                 TRACE(7, ti * 2 + 1);
-                for (int kt = 0; alive && kt < p.ktiles; ++kt, ++it) {
-                    const int sa = it % SA;
-                    const uint32_t aoff = (uint32_t)(sa * AM_BLOCK_BYTES) >> 4;
-                    const uint32_t mcol = meta0 + (uint32_t)(it & 1) * 4u;
+                for (int kt = 0; kt < p.ktiles; ++kt, ++it) {
                     TRACE(2, it);
-                    if (it + 1 < total_it) {
-                        // metadata of the next k-tile -> the other column set (last read by k-tile it-1)
-                        const int sn = (it + 1) % SA;
-                        if (!wait_one(&a_full[sn], (uint32_t)((it + 1) / SA) & 1u, abort_flag, p.status, DEV_TIMEOUT_MMA)) { alive = false; break; }
-                        tc_fence_after();
-                        tc_cp_128x128b(meta0 + (uint32_t)((it + 1) & 1) * 4u, mdesc0 + ((uint32_t)(sn * AM_BLOCK_BYTES) >> 4));
-                    }
+                    if (!wait_one(&kready[it % T::SR], (uint32_t)(it / T::SR) & 1u, abort_flag, p.status, DEV_TIMEOUT_MMA)) { alive = false; break; }
+                    tc_fence_after();
                     TRACE(3, it);
+                    const uint32_t aoff = (uint32_t)((it % SA) * AM_BLOCK_BYTES) >> 4;
+                    const uint32_t mcol = meta0 + (uint32_t)(it & 1) * 4u;
 #pragma unroll
-                    for (int h = 0; h < 2; ++h, ++j) {
-                        const int sb = j % SB;
-                        if (!wait_one(&b_full[sb], (uint32_t)(j / SB) & 1u, abort_flag, p.status, DEV_TIMEOUT_MMA)) { alive = false; break; }
-                        tc_fence_after();
-                        TRACE(4, j);
-                        const uint32_t boff = (uint32_t)(sb * T::B_STAGE_BYTES) >> 4;
+                    for (int h = 0; h < 2; ++h) {
+                        const uint32_t boff = (uint32_t)(((2 * it + h) % SB) * T::B_STAGE_BYTES) >> 4;
 #pragma unroll
                         for (int b = 0; b < NB; b++) {
                             uint32_t mk[4] = {0u, 0u, 0u, 0u};  // bit set = output lane NOT written
@@ -313,10 +335,10 @@ __global__ void __launch_bounds__(Traits<BN, NB, SA, SB, PB>::NUM_THREADS, 1)
                                               (kt | kb) != 0 ? 1u : 0u, mk[0], mk[1], mk[2], mk[3]);
                             }
                         }
-                        tc_commit(&b_empty[sb]);
-                        if (h == 1 && kt == p.ktiles - 1) tc_commit(acc_full_bar);
-                        TRACE(5, j);
                     }
+                    tc_commit(&kdone[it % T::SP]);
+                    if (kt == p.ktiles - 1) tc_commit(acc_full_bar);
+                    TRACE(5, 2 * it + 1);
                 }
             }
         }
@@ -343,15 +365,18 @@ __global__ void __launch_bounds__(Traits<BN, NB, SA, SB, PB>::NUM_THREADS, 1)
 #pragma unroll
             for (int part = 0; part < BN / PART; part++) {
                 uint32_t pk[PART / 2];  // packed fp16 pairs: pk[c] = columns 2c, 2c+1 of this part
-#pragma unroll
-                for (int c0 = 0; c0 < PART; c0 += 32) {
-                    uint32_t v[32];
-                    tc_ld_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(part * PART + c0), v);
+                {
+                    uint32_t v0[32], v1[32];  // both loads in flight before the single wait
+                    const uint32_t tcol = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(part * PART);
+                    tc_ld_32x32b_x32(tcol, v0);
+                    tc_ld_32x32b_x32(tcol + 32u, v1);
                     tc_wait_ld();
 #pragma unroll
                     for (int jj = 0; jj < 16; jj++) {
-                        __half2 h = __floats2half2_rn(__uint_as_float(v[2 * jj]), __uint_as_float(v[2 * jj + 1]));
-                        pk[c0 / 2 + jj] = *reinterpret_cast<uint32_t *>(&h);
+                        __half2 h0 = __floats2half2_rn(__uint_as_float(v0[2 * jj]), __uint_as_float(v0[2 * jj + 1]));
+                        __half2 h1 = __floats2half2_rn(__uint_as_float(v1[2 * jj]), __uint_as_float(v1[2 * jj + 1]));
+                        pk[jj] = *reinterpret_cast<uint32_t *>(&h0);
+                        pk[16 + jj] = *reinterpret_cast<uint32_t *>(&h1);
                     }
                 }
                 if (part == BN / PART - 1) {
@@ -427,7 +452,7 @@ bool spmm_select_config(int V, int N, int M, int producer_warps, SpmmConfig *cfg
     const int mtiles = (M + TILE_M - 1) / TILE_M;
     const int pb = (producer_warps == 4) ? 4 : 8;
     cfg->stages = pb;
-    cfg->threads = (1 + pb + 1 + 4) * 32;
+    cfg->threads = (3 + pb + 4) * 32;
     if (V == 128) {
         cfg->bn = 256; cfg->nb = 1;
     } else if (V == 64) {
