@@ -151,7 +151,11 @@ def test_gather_modes_agree_when_every_row_is_selected(capi, oracle):
     producer-warp counts too."""
     import torch
     M, K, V, m, N = 256, 1024, 128, 4, 512
-    prep, Bd, _ = _setup(capi, oracle, M, K, V, m, N, seed=5, ints=False)
+    capi.set_strategy(capi.STRATEGY_GATHER)          # the gather-mode switch belongs to the V:N:M form
+    try:
+        prep, Bd, _ = _setup(capi, oracle, M, K, V, m, N, seed=5, ints=False)
+    finally:
+        capi.set_strategy(capi.STRATEGY_AUTO)
     a = prep.spmm(Bd)
     prep.set_gather_mode(0)
     b = prep.spmm(Bd)

@@ -78,9 +78,10 @@ bool choose_dense_b(int K, int V, int m)
     const bool possible = (m % 4 == 0) && (K % m == 0);
     if (!possible || g_strategy == VNM_STRATEGY_GATHER) return false;
     if (g_strategy == VNM_STRATEGY_DENSE_B) return true;
-    if (V == 128) return false;
-    if (V == 64) return m <= 8;
-    return m <= 16;  // V == 32
+    // measured on B200 (N = 16384): the dense-B kernel wins for every V at m <= 8, and at m = 16 only for
+    // V = 32 (where the gather kernel pays four masked MMAs per stage)
+    if (m <= 8) return true;
+    return V == 32 && m <= 16;
 }
 
 }  // namespace
@@ -176,6 +177,7 @@ int vnm_prepare(const void *values, const uint32_t *meta, const uint32_t *colloc
     if (((uintptr_t)colloc & 15) || ((uintptr_t)values & 3)) return fail(VNM_ERR_BAD_ARG, "vnm_prepare: colloc must be 16-byte and values 4-byte aligned");
     if (!g_kernels_ready) {
         VNM_CUDA(spmm_init_kernels(), "cudaFuncSetAttribute(max dynamic shared memory)");
+        VNM_CUDA(spmm_dense_b_init(), "cudaFuncSetAttribute(max dynamic shared memory)");
         g_kernels_ready = true;
     }
     vnm_prepared_s *h = new (std::nothrow) vnm_prepared_s();
@@ -267,8 +269,9 @@ int vnm_spmm_config(vnm_handle_t h, int N, int *tile_m, int *tile_n, int *stages
 {
     if (!h) return fail(VNM_ERR_BAD_ARG, "null handle");
     SpmmConfig cfg;
-    if (!spmm_select_config(h->dense_b ? 128 : h->V, N, h->M, h->producer_warps, &cfg)) return fail(VNM_ERR_UNSUPPORTED, "unsupported V");
-    if (tile_m) *tile_m = TILE_M;
+    if (h->dense_b) spmm_dense_b_config(h->M, N, &cfg);
+    else if (!spmm_select_config(h->V, N, h->M, h->producer_warps, &cfg)) return fail(VNM_ERR_UNSUPPORTED, "unsupported V");
+    if (tile_m) *tile_m = h->dense_b ? 2 * TILE_M : TILE_M;
     if (tile_n) *tile_n = cfg.bn;
     if (stages) *stages = cfg.stages;
     if (grid) *grid = cfg.grid;
@@ -292,7 +295,8 @@ int vnm_spmm_f16(vnm_handle_t h, const void *B, int64_t ldb, int N, const void *
         return fail(VNM_ERR_BAD_ARG, "vnm_spmm_f16: unknown layout %d", layout);
     }
     SpmmConfig cfg;
-    if (!spmm_select_config(h->dense_b ? 128 : h->V, N, h->M, h->producer_warps, &cfg)) return fail(VNM_ERR_UNSUPPORTED, "unsupported V");
+    if (h->dense_b) spmm_dense_b_config(h->M, N, &cfg);
+    else if (!spmm_select_config(h->V, N, h->M, h->producer_warps, &cfg)) return fail(VNM_ERR_UNSUPPORTED, "unsupported V");
 
     if (!h->tm_valid || h->tm_B != B || h->tm_ldb != ldb || h->tm_N != N) {
         EncodeTiledFn enc = get_encode_fn();
@@ -329,7 +333,24 @@ int vnm_spmm_f16(vnm_handle_t h, const void *B, int64_t ldb, int N, const void *
     p.gather_mode = h->gather_mode;
     p.total_tiles = p.mtiles * p.ntiles;
     p.trace = h->trace;
-    VNM_CUDA(launch_spmm(cfg, h->tmap_rows, h->tmap_tile, p, (cudaStream_t)stream), "spmm launch");
+    if (h->dense_b) {
+        // [M,N] output goes out through TMA stores of 128 rows x 64 columns (128-byte swizzled staging)
+        CUtensorMap tmap_out;
+        memset(&tmap_out, 0, sizeof(tmap_out));
+        if (layout == VNM_LAYOUT_MN) {
+            EncodeTiledFn enc = get_encode_fn();
+            if (!enc) return fail(VNM_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+            cuuint64_t odims[2] = {(cuuint64_t)N, (cuuint64_t)h->M};
+            cuuint64_t ostrides[1] = {(cuuint64_t)ldo * 2};
+            cuuint32_t obox[2] = {64, 128};
+            cuuint32_t oestr[2] = {1, 1};
+            CUresult r = enc(&tmap_out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, out, odims, ostrides, obox, oestr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (r != CUDA_SUCCESS) return fail(VNM_ERR_CUDA, "cuTensorMapEncodeTiled (output) failed with CUresult %d", (int)r);
+        }
+        VNM_CUDA(launch_spmm_dense_b(cfg, h->tmap_tile, tmap_out, p, (cudaStream_t)stream), "spmm launch");
+    }
+    else VNM_CUDA(launch_spmm(cfg, h->tmap_rows, h->tmap_tile, p, (cudaStream_t)stream), "spmm launch");
     return VNM_OK;
 }
 

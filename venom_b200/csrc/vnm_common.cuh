@@ -88,6 +88,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity)
         : "memory");
     return ok != 0;
 }
+// Non-blocking probe of a barrier phase (try_wait may park the thread for a while before it reports
+// completion; the single-thread pipeline roles spin on this instead to keep hand-offs short).
+__device__ __forceinline__ bool mbar_test_wait(uint64_t *bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
 __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
@@ -114,6 +128,32 @@ __device__ __forceinline__ void tma_load_2d(void *smem_dst, const void *tmap, in
                      smem_u32(smem_dst)),
                  "l"(tmap), "r"(col), "r"(row), "r"(smem_u32(bar))
                  : "memory");
+}
+// TMA tile store shared -> global of a 2-D box at (col, row); completion is tracked by bulk groups.
+__device__ __forceinline__ void tma_store_2d(const void *tmap, const void *smem_src, int col, int row)
+{
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];" ::"l"(tmap), "r"(col), "r"(row),
+                 "r"(smem_u32(smem_src))
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Waits until the bulk groups of this thread have finished READING shared memory (the source may be reused).
+__device__ __forceinline__ void bulk_wait_group_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_group0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void named_barrier_sync(uint32_t id, uint32_t threads) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory"); }
+// Named barrier that also returns the AND of `pred` over its participants.
+__device__ __forceinline__ bool named_barrier_and(uint32_t id, uint32_t threads, bool pred)
+{
+    uint32_t r;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.u32 q, %3, 0;\n\t"
+        "bar.red.and.pred p, %1, %2, q;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(r)
+        : "r"(id), "r"(threads), "r"((uint32_t)pred)
+        : "memory");
+    return r != 0;
 }
 // 16-byte asynchronous copy global -> shared; src_bytes < 16 zero-fills the remainder (0 = all zeros).
 __device__ __forceinline__ void cp_async_16(uint32_t saddr, const void *gsrc, uint32_t src_bytes)

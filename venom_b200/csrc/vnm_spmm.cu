@@ -102,11 +102,11 @@ __device__ __forceinline__ bool wait_bounded(uint64_t *bar, uint32_t parity, vol
 // Single-thread bounded wait (no warp convergence needed): the fast path is one try_wait.
 __device__ __forceinline__ bool wait_one(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int *status, int code)
 {
-    if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_test_wait(bar, parity)) return true;
     const long long t0 = clock64();
     for (uint32_t it = 0;; ++it) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((it & 63u) == 63u) {
+        if (mbar_test_wait(bar, parity)) return true;
+        if ((it & 1023u) == 1023u) {
             if (*abort_flag) return false;
             if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
                 *abort_flag = 1;
