@@ -61,6 +61,18 @@ int vnm_compress_f16(const void *dense, int64_t ldd, const int32_t *mask, const 
                      int M, int K, int V, int n, int m,
                      void *values, uint32_t *meta, unsigned long long *violations, void *stream);
 
+/* Magnitude pruner (CUDA): picks, per V x m block, the four columns and, per row, the two entries that
+ * maximise the kept |w| exactly as the reference's exhaustive search does.
+ * Replaces: group_n_m2 / nm_vector_mask_sparsify, end2end/grouped_nmv_tensor.py:81-343,746-779.
+ *   w       fp32 [M, K] weights (magnitudes are taken inside), leading dimension ldw
+ *   mask    out, int32 [M, K] (leading dimension ldm): 1 = kept
+ *   colloc  out, column-loc array of the format (padding groups are zeroed)
+ * Needs K % m == 0 and V * m * 4 <= 48 KiB.  Bit-identical to the reference except when the second and third
+ * largest |w| of a row of the winning column quadruple are exactly equal (the reference's pick then depends on
+ * scratch state carried over from earlier blocks); the chosen columns never differ. */
+int vnm_prune_magnitude_f32(const float *w, int64_t ldw, int M, int K, int V, int n, int m,
+                            int32_t *mask, int64_t ldm, uint32_t *colloc, void *stream);
+
 /* V:N:M -> dense decompressor (CUDA).  dense [M, K] fp16, leading dimension ldd, fully overwritten.
  * Replaces: Format_sr_nm<T>::to_dense, src/format/format_sr_nm.cpp:327-417. */
 int vnm_decompress_f16(const void *values, const uint32_t *meta, const uint32_t *colloc,

@@ -36,6 +36,8 @@ def lib():
         L.vnm_sizes.argtypes = [C.c_int] * 5 + [i64p] * 4
         L.vnm_compress_f16.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p] + [C.c_int] * 5 + [C.c_void_p] * 4
         L.vnm_decompress_f16.argtypes = [C.c_void_p] * 3 + [C.c_int] * 5 + [C.c_void_p, C.c_int64, C.c_void_p]
+        L.vnm_prune_magnitude_f32.argtypes = [C.c_void_p, C.c_int64] + [C.c_int] * 5 + [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p]
+        L.vnm_prune_magnitude_f32.restype = C.c_int
         L.vnm_prepare.argtypes = [C.c_void_p] * 3 + [C.c_int] * 5 + [C.POINTER(C.c_void_p), C.c_void_p]
         L.vnm_prepared_bytes.argtypes = [C.c_int] * 5 + [i64p]
         L.vnm_destroy.argtypes = [C.c_void_p]
@@ -106,6 +108,19 @@ def compress(dense, colloc, V, m, n=2, mask=None, count_violations=True):
                                   colloc.data_ptr(), M, K, V, n, m, values.data_ptr(), meta.data_ptr(),
                                   None if viol is None else viol.data_ptr(), _stream()))
     return values, meta, (int(viol.item()) if viol is not None else None)
+
+
+def prune_magnitude(w, V, m, n=2):
+    """w: [M,K] CUDA tensor (any float dtype; converted to fp32 like the reference does).  Returns
+    (mask int32 [M,K], colloc int32) -- the outputs of the reference's nm_vector_mask_sparsify."""
+    _need_cuda(w)
+    M, K = w.shape
+    ksp, nv, nm, nc = sizes(M, K, V, m, n)
+    wf = w.detach().to(torch.float32).contiguous()
+    mask = torch.empty((M, K), dtype=torch.int32, device=w.device)
+    colloc = torch.empty(nc, dtype=torch.int32, device=w.device)
+    _check(lib().vnm_prune_magnitude_f32(wf.data_ptr(), K, M, K, V, n, m, mask.data_ptr(), K, colloc.data_ptr(), _stream()))
+    return mask, colloc
 
 
 def decompress(values, meta, colloc, M, K, V, m, n=2):

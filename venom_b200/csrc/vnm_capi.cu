@@ -143,6 +143,19 @@ int vnm_compress_f16(const void *dense, int64_t ldd, const int32_t *mask, const 
     return VNM_OK;
 }
 
+int vnm_prune_magnitude_f32(const float *w, int64_t ldw, int M, int K, int V, int n, int m, int32_t *mask, int64_t ldm, uint32_t *colloc,
+                            void *stream)
+{
+    int rc = check_format(M, K, V, n, m);
+    if (rc) return rc;
+    if (!w || !mask || !colloc) return fail(VNM_ERR_BAD_ARG, "vnm_prune_magnitude_f32: null pointer");
+    if (ldw < K || ldm < K) return fail(VNM_ERR_BAD_ARG, "vnm_prune_magnitude_f32: leading dimensions must be >= K");
+    if (K % m != 0) return fail(VNM_ERR_UNSUPPORTED, "vnm_prune_magnitude_f32: K (%d) must be a multiple of m (%d)", K, m);
+    if ((size_t)V * m * sizeof(float) > 48 * 1024) return fail(VNM_ERR_UNSUPPORTED, "vnm_prune_magnitude_f32: V * m too large (%d x %d)", V, m);
+    VNM_CUDA(launch_prune(w, ldw, M, K, V, m, mask, ldm, colloc, (cudaStream_t)stream), "prune launch");
+    return VNM_OK;
+}
+
 int vnm_decompress_f16(const void *values, const uint32_t *meta, const uint32_t *colloc, int M, int K, int V, int n, int m,
                        void *dense, int64_t ldd, void *stream)
 {

@@ -58,6 +58,9 @@ cudaError_t launch_prepare(const void *values, const uint32_t *meta, const uint3
 cudaError_t launch_prepare_dense_b(const void *values, const uint32_t *meta, const uint32_t *colloc, int M, int K, int V, int m,
                                    void *am, void *rows, int mtiles, int ktiles, cudaStream_t stream);
 
+cudaError_t launch_prune(const float *w, int64_t ldw, int M, int K, int V, int m, int32_t *mask, int64_t ldm, uint32_t *colloc,
+                         cudaStream_t stream);
+
 // Chooses the tile configuration for (V, N).  Returns false for an unsupported V.
 bool spmm_select_config(int V, int N, int M, int producer_warps, SpmmConfig *cfg);
 // One-time per-process opt-in to large dynamic shared memory for every kernel instance.

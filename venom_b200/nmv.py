@@ -48,6 +48,25 @@ class SrNMTensor:
         return capi.decompress(self.values, self.metadata, self.columns, self.nrows, self.ncols, self.tileM, self.m, self.n)
 
 
+def nm_vector_mask_sparsify(tensor, n, m, tileM):
+    """Magnitude pruning to V:n:m on the GPU; same return value as the reference function of this name
+    (end2end/grouped_nmv_tensor.py:746-779): (masks int32 [nrows, ncols], columns int32)."""
+    return capi.prune_magnitude(tensor, tileM, m, n)
+
+
+class MagnitudeSparsifier:
+    """The magnitude path the reference keeps commented out in its scripts (end2end/bert_pytorch.py:63-64)."""
+
+    def __init__(self, n, m, tileM):
+        self.n, self.m, self.tileM = n, m, tileM
+
+    def __call__(self, tensor, device=None):
+        device = tensor.device if device is None else device
+        mask, columns = nm_vector_mask_sparsify(tensor.to(device), self.n, self.m, self.tileM)
+        dense = tensor.detach().to(device=device, dtype=torch.float16) * mask.to(torch.float16)
+        return SrNMTensor(self.n, self.m, self.tileM, dense, mask, columns, device)
+
+
 class NMVectorSparsifier:
     """The sparsifier the reference's end-to-end scripts ship with: a fixed pattern that keeps columns
     0 and 2 of every group of m and uses column-loc {0,1,2,3} (end2end/bert_pytorch.py:66-75)."""
