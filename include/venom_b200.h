@@ -99,6 +99,14 @@ int vnm_destroy(vnm_handle_t handle);
 int vnm_spmm_f16(vnm_handle_t handle, const void *B, int64_t ldb, int N,
                  const void *bias, void *out, int64_t ldo, int layout, void *stream);
 
+/* Same product with the dense operand given as Bt = B^T, i.e. [N, K] row-major with leading dimension ldbt
+ * (the activation in its natural [tokens, features] layout), so the caller does not have to materialise the
+ * transpose the reference's scripts make before every call (end2end/bert_pytorch.py:85-87,133).
+ * Only for operands prepared in dense-B form (vnm_operand_form reports it); otherwise VNM_ERR_UNSUPPORTED. */
+int vnm_spmm_f16_nk(vnm_handle_t handle, const void *Bt, int64_t ldbt, int N,
+                    const void *bias, void *out, int64_t ldo, int layout, void *stream);
+int vnm_operand_form(vnm_handle_t handle, int *dense_b);
+
 /* Same product with HOST buffers: copies B (and bias) to the device, runs vnm_spmm_f16 and copies the
  * result back, all on `stream`, then synchronises it.  Device staging buffers are owned by the handle
  * and grown on demand.  B_host [K, N] and out_host are dense row-major ([M,N] or [N,M]). */

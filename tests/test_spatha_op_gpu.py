@@ -48,6 +48,11 @@ def test_spatha_spmm_matches_dense_product_plus_bias(spatha, oracle, cfg):
         out2 = spatha.spmm(meta, idx, values, rhs, bias, M, K, N, V, 2, m, values.numel(), 0, 32, 4)
     s.synchronize()
     assert spatha.cache_size() == n0 and torch.equal(out, out2)
+    # the end-to-end scripts pass `flattened_input.T` (end2end/bert_pytorch.py:133): a transposed view of a
+    # [tokens, features] activation must give the same result whether or not the op has to copy it
+    act = rhs.t().contiguous()
+    out3 = spatha.spmm(meta, idx, values, act.t(), bias, M, K, N, V, 2, m, values.numel(), 0, 32, 4)
+    assert torch.equal(out, out3)
 
 
 def test_spatha_spmm_rejects_bad_arguments(spatha):
@@ -95,3 +100,27 @@ def test_benchmark_spmm_cli_check(flags):
     assert len(cols) == 26 and cols[0] == "2" and cols[1] == "sm_100a"
     assert cols[23] == "0", "check failed: " + r.stdout
     assert float(cols[20]) > 0 and float(cols[21]) > 0
+
+
+def test_bert_encoder_harness_small(spatha):
+    """Two BERT-large-shaped encoder layers, magnitude-pruned to 64:2:8: the sparse model must agree with a
+    dense model whose linear weights were masked the same way."""
+    import torch
+    from venom_b200 import e2e_bert
+    from venom_b200.nmv import SrnmSpmm
+    torch.manual_seed(0)
+    dense = e2e_bert.build_model(2).half().cuda()
+    sparse = e2e_bert.build_model(2).half().cuda()
+    sparse.load_state_dict(dense.state_dict())
+    assert e2e_bert.sparsify_encoder(sparse, 2, 8, 64) == 12
+    # mask the dense twin's weights with what the sparse modules kept
+    for (name, mod) in sparse.named_modules():
+        if isinstance(mod, SrnmSpmm):
+            from venom_b200 import capi
+            kept = capi.decompress(mod.values, mod.metadata, mod.columns, mod.nrows_sp, mod.ncols_sp, mod.v, mod.m)
+            dict(dense.named_modules())[name].weight.data.copy_(kept)
+    ids = torch.randint(0, 30522, (2, 128), device="cuda")
+    with torch.no_grad():
+        a = dense(ids).last_hidden_state.float()
+        b = sparse(ids).last_hidden_state.float()
+    assert torch.allclose(a, b, rtol=3e-2, atol=3e-2), (a - b).abs().max()

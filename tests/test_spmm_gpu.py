@@ -188,3 +188,23 @@ def test_both_operand_forms_match_oracle(capi, oracle, shape, strategy):
             _check(oracle, outT.cpu().numpy(), oracle.spmm(ov, om, cols, M, K, V, m, B, bias=bias, layout=1))
     finally:
         capi.set_strategy(capi.STRATEGY_AUTO)
+
+
+@pytest.mark.parametrize("shape", [(256, 1024, 64, 8, 384), (384, 512, 128, 4, 200), (128, 2048, 32, 16, 72)])
+def test_transposed_dense_operand_and_tma_store_layouts(capi, oracle, shape):
+    """Dense-B form: B given as [N,K] (no transpose copy) must equal the [K,N] call, in both output layouts."""
+    import torch
+    M, K, V, m, N = shape
+    prep, Bd, (ov, om, cols, B) = _setup(capi, oracle, M, K, V, m, N, seed=11 * M + N, ints=False)
+    assert prep.dense_b_form()
+    bias = np.random.default_rng(3).uniform(-1, 1, M).astype(np.float16)
+    bt = Bd.t().contiguous()
+    a = prep.spmm(Bd, bias=torch.from_numpy(bias).cuda(), layout=capi.VNM_LAYOUT_NM)
+    b = prep.spmm_nk(bt, bias=torch.from_numpy(bias).cuda(), layout=capi.VNM_LAYOUT_NM)
+    assert torch.equal(a, b)
+    _check(oracle, b.cpu().numpy(), oracle.spmm(ov, om, cols, M, K, V, m, B, bias=bias, layout=1))
+    c = prep.spmm_nk(bt, layout=capi.VNM_LAYOUT_MN)
+    assert torch.equal(c, prep.spmm(Bd))
+    wide = torch.full((N, M + 8), 3.0, dtype=torch.float16, device="cuda")
+    prep.spmm_nk(bt, layout=capi.VNM_LAYOUT_NM, out=wide[:, :M])
+    assert torch.equal(wide[:, :M], prep.spmm(Bd, layout=capi.VNM_LAYOUT_NM)) and bool((wide[:, M:] == 3.0).all())

@@ -43,6 +43,10 @@ def lib():
         L.vnm_destroy.argtypes = [C.c_void_p]
         L.vnm_spmm_f16.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_void_p, C.c_void_p, C.c_int64,
                                    C.c_int, C.c_void_p]
+        L.vnm_spmm_f16_nk.argtypes = L.vnm_spmm_f16.argtypes
+        L.vnm_spmm_f16_nk.restype = C.c_int
+        L.vnm_operand_form.argtypes = [C.c_void_p, C.POINTER(C.c_int)]
+        L.vnm_operand_form.restype = C.c_int
         L.vnm_spmm_f16_host.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]
         L.vnm_device_status.argtypes = [C.c_void_p, C.POINTER(C.c_int), C.c_void_p]
         L.vnm_spmm_config.argtypes = [C.c_void_p, C.c_int] + [C.POINTER(C.c_int)] * 5
@@ -171,6 +175,24 @@ class Prepared:
             raise VenomError("bias must be a contiguous fp16 vector of M elements")
         _check(lib().vnm_spmm_f16(self._h, B.data_ptr(), B.stride(0), N, None if bias is None else bias.data_ptr(),
                                   out.data_ptr(), out.stride(0), layout, _stream()))
+        return out
+
+    def dense_b_form(self):
+        v = C.c_int(0)
+        _check(lib().vnm_operand_form(self._h, C.byref(v)))
+        return bool(v.value)
+
+    def spmm_nk(self, Bt, bias=None, layout=VNM_LAYOUT_NM, out=None):
+        """Bt: [N,K] fp16 CUDA (unit inner stride), the transpose of B.  Same result as spmm(Bt.T)."""
+        _need_cuda(Bt, bias, out)
+        if Bt.dtype != torch.float16 or Bt.dim() != 2 or Bt.shape[1] != self.K or Bt.stride(1) != 1:
+            raise VenomError("Bt must be a [N,K] fp16 tensor with unit inner stride (K=%d)" % self.K)
+        N = Bt.shape[0]
+        if out is None:
+            shape = (self.M, N) if layout == VNM_LAYOUT_MN else (N, self.M)
+            out = torch.empty(shape, dtype=torch.float16, device=Bt.device)
+        _check(lib().vnm_spmm_f16_nk(self._h, Bt.data_ptr(), Bt.stride(0), N, None if bias is None else bias.data_ptr(),
+                                     out.data_ptr(), out.stride(0), layout, _stream()))
         return out
 
     def spmm_host(self, B_host, out_host, bias_host=None, layout=VNM_LAYOUT_MN):

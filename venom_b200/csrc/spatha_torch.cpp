@@ -57,8 +57,10 @@ torch::Tensor spmm(torch::Tensor A_metadata, torch::Tensor A_indices, torch::Ten
     TORCH_CHECK(A_values.numel() == nv && A_metadata.numel() == nm && A_indices.numel() == nc, "spatha.spmm: array sizes do not match the format (values ",
                 nv, ", metadata ", nm, ", indices ", nc, ")");
     TORCH_CHECK(nnz == nv, "spatha.spmm: nnz must be A_num_rows * padded compressed columns (", nv, ")");
-    TORCH_CHECK(rhs_matrix.dim() == 2 && rhs_matrix.size(0) == K && rhs_matrix.size(1) == N && rhs_matrix.stride(1) == 1,
-                "spatha.spmm: rhs_matrix must be [A_num_cols, B_num_cols] with unit inner stride");
+    TORCH_CHECK(rhs_matrix.dim() == 2 && rhs_matrix.size(0) == K && rhs_matrix.size(1) == N, "spatha.spmm: rhs_matrix must be [A_num_cols, B_num_cols]");
+    // A transposed view of a [B_num_cols, A_num_cols] activation (what `flattened_input.T` is) can be consumed
+    // in place when the operand is held in dense-B form; any other non-contiguous rhs is copied like the reference does.
+    const bool rhs_is_t_view = rhs_matrix.stride(0) == 1 && rhs_matrix.stride(1) >= K && N > 1;
     const bool has_bias = bias.has_value() && bias->defined() && bias->numel() > 0;
     if (has_bias) TORCH_CHECK(bias->is_cuda() && bias->scalar_type() == torch::kFloat16 && bias->numel() == M && bias->is_contiguous(), "spatha.spmm: bias must be fp16 [A_num_rows]");
 
@@ -79,8 +81,16 @@ torch::Tensor spmm(torch::Tensor A_metadata, torch::Tensor A_indices, torch::Ten
         }
     }
     auto out = torch::empty({N, M}, rhs_matrix.options());
-    check(vnm_spmm_f16(h, rhs_matrix.data_ptr(), rhs_matrix.stride(0), N, has_bias ? bias->data_ptr() : nullptr, out.data_ptr(), M,
-                       VNM_LAYOUT_NM, stream), "vnm_spmm_f16");
+    int dense_b = 0;
+    check(vnm_operand_form(h, &dense_b), "vnm_operand_form");
+    if (rhs_is_t_view && dense_b && rhs_matrix.stride(1) % 8 == 0 && (reinterpret_cast<uintptr_t>(rhs_matrix.data_ptr()) & 15) == 0) {
+        check(vnm_spmm_f16_nk(h, rhs_matrix.data_ptr(), rhs_matrix.stride(1), N, has_bias ? bias->data_ptr() : nullptr, out.data_ptr(), M,
+                              VNM_LAYOUT_NM, stream), "vnm_spmm_f16_nk");
+        return out;
+    }
+    torch::Tensor rhs = rhs_matrix.stride(1) == 1 ? rhs_matrix : rhs_matrix.contiguous();
+    check(vnm_spmm_f16(h, rhs.data_ptr(), rhs.stride(0), N, has_bias ? bias->data_ptr() : nullptr, out.data_ptr(), M, VNM_LAYOUT_NM, stream),
+          "vnm_spmm_f16");
     return out;
 }
 

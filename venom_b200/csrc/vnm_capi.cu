@@ -98,6 +98,7 @@ struct vnm_prepared_s {
     const void *tm_B;
     int64_t tm_ldb;
     int tm_N;
+    int tm_nk;
     bool tm_valid;
     CUtensorMap tmap_rows;
     CUtensorMap tmap_tile;
@@ -292,11 +293,17 @@ int vnm_spmm_config(vnm_handle_t h, int N, int *tile_m, int *tile_n, int *stages
     return VNM_OK;
 }
 
-int vnm_spmm_f16(vnm_handle_t h, const void *B, int64_t ldb, int N, const void *bias, void *out, int64_t ldo, int layout, void *stream)
+static int spmm_impl(vnm_handle_t h, const void *B, int64_t ldb, int N, int b_nk, const void *bias, void *out, int64_t ldo, int layout,
+                     void *stream)
 {
     if (!h || !B || !out) return fail(VNM_ERR_BAD_ARG, "vnm_spmm_f16: null pointer");
     if (N <= 0 || N % 8 != 0) return fail(VNM_ERR_BAD_ARG, "vnm_spmm_f16: N (%d) must be a positive multiple of 8", N);
-    if (ldb < N || ldb % 8 != 0) return fail(VNM_ERR_BAD_ARG, "vnm_spmm_f16: ldb (%lld) must be >= N and a multiple of 8", (long long)ldb);
+    if (b_nk) {
+        if (!h->dense_b) return fail(VNM_ERR_UNSUPPORTED, "a [N,K] dense operand needs an operand prepared in dense-B form (see vnm_operand_form)");
+        if (ldb < h->K || ldb % 8 != 0) return fail(VNM_ERR_BAD_ARG, "vnm_spmm_f16_nk: ldb (%lld) must be >= K and a multiple of 8", (long long)ldb);
+    } else if (ldb < N || ldb % 8 != 0) {
+        return fail(VNM_ERR_BAD_ARG, "vnm_spmm_f16: ldb (%lld) must be >= N and a multiple of 8", (long long)ldb);
+    }
     if ((uintptr_t)B & 15) return fail(VNM_ERR_BAD_ARG, "vnm_spmm_f16: B must be 16-byte aligned");
     if (layout == VNM_LAYOUT_MN) {
         if (bias) return fail(VNM_ERR_BAD_ARG, "vnm_spmm_f16: bias is only supported with layout NM");
@@ -310,27 +317,39 @@ int vnm_spmm_f16(vnm_handle_t h, const void *B, int64_t ldb, int N, const void *
     SpmmConfig cfg;
     if (h->dense_b) spmm_dense_b_config(h->M, N, &cfg);
     else if (!spmm_select_config(h->V, N, h->M, h->producer_warps, &cfg)) return fail(VNM_ERR_UNSUPPORTED, "unsupported V");
+    EncodeTiledFn enc = get_encode_fn();
+    if (!enc) return fail(VNM_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
 
-    if (!h->tm_valid || h->tm_B != B || h->tm_ldb != ldb || h->tm_N != N) {
-        EncodeTiledFn enc = get_encode_fn();
-        if (!enc) return fail(VNM_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
-        // B viewed as a 2-D tensor {N (contiguous), K}; one box = 64 columns (128 bytes) of one row
-        // (gather4 picks four such rows) or of 64 consecutive rows, written with the 128-byte swizzle
-        // the MMA's N-major operand layout expects.  Rows >= K and columns >= N read as zeros.
-        cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)h->K};
-        cuuint64_t strides[1] = {(cuuint64_t)ldb * 2};
-        cuuint32_t box_rows[2] = {64, 1};
-        cuuint32_t box_tile[2] = {64, 64};
+    if (!h->tm_valid || h->tm_B != B || h->tm_ldb != ldb || h->tm_N != N || h->tm_nk != b_nk) {
         cuuint32_t estr[2] = {1, 1};
-        CUresult r = enc(&h->tmap_rows, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(B), dims, strides, box_rows, estr,
-                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-        if (r == CUDA_SUCCESS)
-            r = enc(&h->tmap_tile, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(B), dims, strides, box_tile, estr,
+        CUresult r;
+        if (b_nk) {
+            // B given as [N, K] (K contiguous): boxes of 64 k x 128 rows (n) form the K-major operand tile.
+            cuuint64_t dims[2] = {(cuuint64_t)h->K, (cuuint64_t)N};
+            cuuint64_t strides[1] = {(cuuint64_t)ldb * 2};
+            cuuint32_t box[2] = {64, 128};
+            r = enc(&h->tmap_tile, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(B), dims, strides, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            h->tmap_rows = h->tmap_tile;
+        } else {
+            // B viewed as a 2-D tensor {N (contiguous), K}; one box = 64 columns (128 bytes) of one row
+            // (gather4 picks four such rows) or of 64 consecutive rows, written with the 128-byte swizzle
+            // the MMA's N-major operand layout expects.  Rows >= K and columns >= N read as zeros.
+            cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)h->K};
+            cuuint64_t strides[1] = {(cuuint64_t)ldb * 2};
+            cuuint32_t box_rows[2] = {64, 1};
+            cuuint32_t box_tile[2] = {64, 64};
+            r = enc(&h->tmap_rows, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(B), dims, strides, box_rows, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (r == CUDA_SUCCESS)
+                r = enc(&h->tmap_tile, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(B), dims, strides, box_tile, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        }
         if (r != CUDA_SUCCESS) return fail(VNM_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
-        h->tm_B = B; h->tm_ldb = ldb; h->tm_N = N; h->tm_valid = true;
+        h->tm_B = B; h->tm_ldb = ldb; h->tm_N = N; h->tm_nk = b_nk; h->tm_valid = true;
     }
 
     SpmmParams p;
@@ -346,24 +365,49 @@ int vnm_spmm_f16(vnm_handle_t h, const void *B, int64_t ldb, int N, const void *
     p.gather_mode = h->gather_mode;
     p.total_tiles = p.mtiles * p.ntiles;
     p.trace = h->trace;
+    p.b_nk = b_nk;
     if (h->dense_b) {
-        // [M,N] output goes out through TMA stores of 128 rows x 64 columns (128-byte swizzled staging)
+        // The result leaves through TMA stores: [M,N] as boxes of 64 columns x 128 rows (128-byte swizzled
+        // staging), [N,M] as boxes of 128 columns (m) x 64 rows (n).
+        if (layout == VNM_LAYOUT_NM && (ldo % 8 != 0 || ((uintptr_t)out & 15)))
+            return fail(VNM_ERR_BAD_ARG, "vnm_spmm_f16: layout NM needs ldo %% 8 == 0 and a 16-byte aligned out for this operand");
         CUtensorMap tmap_out;
-        memset(&tmap_out, 0, sizeof(tmap_out));
+        cuuint32_t oestr[2] = {1, 1};
+        cuuint64_t ostrides[1] = {(cuuint64_t)ldo * 2};
+        CUresult r;
         if (layout == VNM_LAYOUT_MN) {
-            EncodeTiledFn enc = get_encode_fn();
-            if (!enc) return fail(VNM_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
             cuuint64_t odims[2] = {(cuuint64_t)N, (cuuint64_t)h->M};
-            cuuint64_t ostrides[1] = {(cuuint64_t)ldo * 2};
             cuuint32_t obox[2] = {64, 128};
-            cuuint32_t oestr[2] = {1, 1};
-            CUresult r = enc(&tmap_out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, out, odims, ostrides, obox, oestr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-            if (r != CUDA_SUCCESS) return fail(VNM_ERR_CUDA, "cuTensorMapEncodeTiled (output) failed with CUresult %d", (int)r);
+            r = enc(&tmap_out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, out, odims, ostrides, obox, oestr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        } else {
+            cuuint64_t odims[2] = {(cuuint64_t)h->M, (cuuint64_t)N};
+            cuuint32_t obox[2] = {128, 64};
+            r = enc(&tmap_out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, out, odims, ostrides, obox, oestr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         }
+        if (r != CUDA_SUCCESS) return fail(VNM_ERR_CUDA, "cuTensorMapEncodeTiled (output) failed with CUresult %d", (int)r);
         VNM_CUDA(launch_spmm_dense_b(cfg, h->tmap_tile, tmap_out, p, (cudaStream_t)stream), "spmm launch");
+    } else {
+        VNM_CUDA(launch_spmm(cfg, h->tmap_rows, h->tmap_tile, p, (cudaStream_t)stream), "spmm launch");
     }
-    else VNM_CUDA(launch_spmm(cfg, h->tmap_rows, h->tmap_tile, p, (cudaStream_t)stream), "spmm launch");
+    return VNM_OK;
+}
+
+int vnm_spmm_f16(vnm_handle_t h, const void *B, int64_t ldb, int N, const void *bias, void *out, int64_t ldo, int layout, void *stream)
+{
+    return spmm_impl(h, B, ldb, N, 0, bias, out, ldo, layout, stream);
+}
+
+int vnm_spmm_f16_nk(vnm_handle_t h, const void *Bt, int64_t ldbt, int N, const void *bias, void *out, int64_t ldo, int layout, void *stream)
+{
+    return spmm_impl(h, Bt, ldbt, N, 1, bias, out, ldo, layout, stream);
+}
+
+int vnm_operand_form(vnm_handle_t h, int *dense_b)
+{
+    if (!h || !dense_b) return fail(VNM_ERR_BAD_ARG, "vnm_operand_form: null pointer");
+    *dense_b = h->dense_b;
     return VNM_OK;
 }
 

@@ -29,6 +29,7 @@ struct SpmmParams {
     int gather_mode;      // GATHER_* below
     int total_tiles;      // mtiles * ntiles
     long long *trace;     // debug builds (-DVNM_TRACE) only: clock stamps of CTA 0, else null
+    int b_nk;             // dense-B kernel only: the dense operand is given as [N, K] row-major (K contiguous)
 };
 
 // How the producer warps bring the selected rows of B into shared memory.

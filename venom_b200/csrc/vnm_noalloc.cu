@@ -160,6 +160,7 @@ extern "C" int vnm_spmm_f16_noalloc(const void *values, const uint32_t *meta, co
     p.gather_mode = (m == 4) ? GATHER_CONTIG : GATHER_TMA4;
     p.total_tiles = p.mtiles * p.ntiles;
     p.trace = nullptr;
+    p.b_nk = 0;
     e = launch_spmm(cfg, tmap_rows, tmap_tile, p, s);
     if (e != cudaSuccess) return nfail(VNM_ERR_CUDA, "product launch: %s", cudaGetErrorString(e));
 

@@ -178,9 +178,14 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_kernel(const __gr
                     TRACE(1, j);
                     if (p.gather_mode != GATHER_NONE) {
                         mbar_arrive_expect_tx(&b_full[s], B_STAGE_BYTES);
+                        if (p.b_nk) {
+                            // B given as [N, K]: one box of 128 rows (n) x 64 k, i.e. a K-major operand tile
+                            tma_load_2d(b_ring + s * B_STAGE_BYTES, &tmap_tile, jl * 64, n0, &b_full[s]);
+                        } else {
 #pragma unroll
-                        for (int c = 0; c < BN / 64; c++)
-                            tma_load_2d(b_ring + s * B_STAGE_BYTES + c * B_CHUNK_BYTES, &tmap_tile, n0 + c * 64, jl * 64, &b_full[s]);
+                            for (int c = 0; c < BN / 64; c++)
+                                tma_load_2d(b_ring + s * B_STAGE_BYTES + c * B_CHUNK_BYTES, &tmap_tile, n0 + c * 64, jl * 64, &b_full[s]);
+                        }
                     } else {
                         mbar_arrive(&b_full[s]);
                     }
@@ -223,9 +228,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_kernel(const __gr
     } else if (warp == 3) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
-            const uint32_t idesc0 = make_idesc_f16(TILE_M, BN, true, 0u, true);
+            const bool b_nk = p.b_nk != 0;
+            const uint32_t idesc0 = make_idesc_f16(TILE_M, BN, true, 0u, !b_nk);
             const uint64_t adesc0 = make_smem_desc(smem_u32(a_ring), 16, 1024, 2);
-            const uint64_t bdesc0 = make_smem_desc(smem_u32(b_ring), B_CHUNK_BYTES, 1024, 2);
+            // B stage: N-major (two 64-column slices, 64 k-rows of 128 B each) or K-major (128 n-rows of 128 B = 64 k)
+            const uint64_t bdesc0 = b_nk ? make_smem_desc(smem_u32(b_ring), 16, 1024, 2) : make_smem_desc(smem_u32(b_ring), B_CHUNK_BYTES, 1024, 2);
+            const uint32_t bstep = b_nk ? (64u >> 4) : (4096u >> 4);  // next K=32 block: 32 k = 64 B along a row, or 32 rows further
             int it = 0;
             bool alive = true;
             for (int ti = 0; alive && ti < my_tiles; ++ti) {
@@ -248,7 +256,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_kernel(const __gr
 #pragma unroll
                             for (int k2 = 0; k2 < 2; k2++) {
                                 const int kb = h * 2 + k2;  // K=32 block inside the k-tile
-                                tc_mma_sp_f16(tmem_base + rt * BN, adesc0 + aoff + (uint32_t)(kb * 32 >> 4), bdesc0 + boff + (uint32_t)(k2 * 4096 >> 4),
+                                tc_mma_sp_f16(tmem_base + rt * BN, adesc0 + aoff + (uint32_t)(kb * 32 >> 4), bdesc0 + boff + (uint32_t)k2 * bstep,
                                               mcol + rt * 4 + (uint32_t)(kb & ~1), idesc0 | (uint32_t)(kb & 1), (kt | kb) != 0 ? 1u : 0u, 0u, 0u, 0u, 0u);
                             }
                         }
@@ -323,21 +331,28 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_kernel(const __gr
                             tma_store_2d(&tmap_out, stg, n0 + part * PART, mt * TILE_M);
                             bulk_commit_group();
                         }
-                    } else if (row_ok) {
-                        const int nbase = n0 + part * PART;
-                        {
-                            __half *dst = p.out + (int64_t)nbase * p.ldo + row;
-                            const int64_t step = p.ldo;
+                    } else {
+                        // [N,M] output (+ bias): stage the transposed part, 64 rows (n) x 128 columns (m) without
+                        // swizzle -- the 32 lanes of a warp write 32 consecutive m of one n -- and store it with
+                        // one TMA store, which clips at N and M.
+                        uint8_t *stg = out_ring + rt * OUT_STAGE_BYTES;
+                        const bool leader = (warp == 4 + 4 * rt) && lane == 0;
+                        if (leader) bulk_wait_group_read0();
+                        named_barrier_sync(1 + rt, 128);
+                        __half *col = reinterpret_cast<__half *>(stg) + arow;
 #pragma unroll
-                            for (int jj = 0; jj < PART / 2; jj++) {
-                                __half2 h = *reinterpret_cast<__half2 *>(&pk[jj]);
-                                __half lo = __low2half(h), hi = __high2half(h);
-                                if (has_bias) { lo = __hadd(lo, bias); hi = __hadd(hi, bias); }
-                                if (nbase + 2 * jj < p.N) *dst = lo;
-                                dst += step;
-                                if (nbase + 2 * jj + 1 < p.N) *dst = hi;
-                                dst += step;
-                            }
+                        for (int jj = 0; jj < PART / 2; jj++) {
+                            __half2 h = *reinterpret_cast<__half2 *>(&pk[jj]);
+                            __half lo = __low2half(h), hi = __high2half(h);
+                            if (has_bias) { lo = __hadd(lo, bias); hi = __hadd(hi, bias); }
+                            col[(2 * jj) * TILE_M] = lo;
+                            col[(2 * jj + 1) * TILE_M] = hi;
+                        }
+                        fence_proxy_async();
+                        named_barrier_sync(1 + rt, 128);
+                        if (leader && mt < p.mtiles) {
+                            tma_store_2d(&tmap_out, stg, mt * TILE_M, n0 + part * PART);
+                            bulk_commit_group();
                         }
                     }
                 }

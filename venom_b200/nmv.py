@@ -91,7 +91,9 @@ class NMVectorSparsifier:
 def sparse_dense_mul_dispatch(sparse_values, sparse_indices, sparse_metadata, dense, nrows_sp, ncols_sp, ncols_d, m, n, v, nnz, bias):
     """Same call as the reference helper: returns [ncols_d, nrows_sp] = (A @ dense).T + bias."""
     from . import spatha_module
-    dense_ = dense.contiguous()
+    # the reference materialises `dense.contiguous()` here; the op accepts the transposed view itself and
+    # copies only when it has to
+    dense_ = dense
     return spatha_module().spmm(sparse_metadata, sparse_indices, sparse_values, dense_, bias, nrows_sp, ncols_sp, ncols_d, v, n, m, nnz, 0, 32, 4)
 
 
