@@ -110,6 +110,25 @@ def test_spmm_host_buffers_end_to_end(capi, oracle):
     assert np.array_equal(oh.numpy().view(np.uint16), want.view(np.uint16))
 
 
+@pytest.mark.parametrize("cfg", [(256, 512, 64, 8, 2568, True), (128, 256, 128, 16, 1536, False)])
+def test_spmm_host_buffers_in_slices(capi, oracle, cfg):
+    """Host-buffer call whose columns go through in several slices (the last one ragged), both layouts, with
+    bias, from pinned and from pageable memory: equal to the device-buffer call bit for bit."""
+    import torch
+    M, K, V, m, N, pinned = cfg
+    prep, Bd, (ov, om, cols, B) = _setup(capi, oracle, M, K, V, m, N, seed=5, ints=False)
+    bias = np.random.default_rng(9).uniform(-1, 1, M).astype(np.float16)
+    Bh = torch.from_numpy(B)
+    o_mn, o_nm = torch.empty((M, N), dtype=torch.float16), torch.empty((N, M), dtype=torch.float16)
+    if pinned:
+        Bh, o_mn, o_nm = Bh.pin_memory(), o_mn.pin_memory(), o_nm.pin_memory()
+    prep.spmm_host(Bh, o_mn)
+    prep.spmm_host(Bh, o_nm, bias_host=torch.from_numpy(bias), layout=capi.VNM_LAYOUT_NM)
+    assert torch.equal(o_mn, prep.spmm(Bd).cpu())
+    assert torch.equal(o_nm, prep.spmm(Bd, bias=torch.from_numpy(bias).cuda(), layout=capi.VNM_LAYOUT_NM).cpu())
+    _check(oracle, o_nm.numpy(), oracle.spmm(ov, om, cols, M, K, V, m, B, bias=bias, layout=1))
+
+
 def test_bad_arguments_raise(capi, oracle):
     import torch
     M, K, V, m, N = 128, 256, 128, 8, 64

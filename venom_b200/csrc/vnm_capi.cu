@@ -86,6 +86,8 @@ bool choose_dense_b(int K, int V, int m)
 
 }  // namespace
 
+constexpr int HOST_CHUNKS_MAX = 8;
+
 struct vnm_prepared_s {
     int M, K, V, n, m;
     int64_t Ksp;
@@ -109,6 +111,9 @@ struct vnm_prepared_s {
     void *stage_out;
     size_t stage_out_bytes;
     void *stage_bias;
+    cudaStream_t copy_in, copy_out;   // host-buffer entry point: copy engines run beside the kernels
+    cudaEvent_t ev[2 * HOST_CHUNKS_MAX + 2];
+    bool host_pipe_ready;
     int gather_mode;
     long long *trace;  // debug builds only
     int dense_b;       // 1: A re-expressed as 2:4 over all K columns, B read as plain tiles
@@ -240,6 +245,11 @@ int vnm_destroy(vnm_handle_t h)
     cudaFree(h->stage_B);
     cudaFree(h->stage_out);
     cudaFree(h->stage_bias);
+    if (h->host_pipe_ready) {
+        cudaStreamDestroy(h->copy_in);
+        cudaStreamDestroy(h->copy_out);
+        for (cudaEvent_t e : h->ev) cudaEventDestroy(e);
+    }
     delete h;
     return VNM_OK;
 }
@@ -426,20 +436,60 @@ int vnm_spmm_f16_host(vnm_handle_t h, const void *B_host, int N, const void *bia
 {
     if (!h || !B_host || !out_host) return fail(VNM_ERR_BAD_ARG, "vnm_spmm_f16_host: null pointer");
     if (N <= 0 || N % 8 != 0) return fail(VNM_ERR_BAD_ARG, "vnm_spmm_f16_host: N (%d) must be a positive multiple of 8", N);
+    if (layout != VNM_LAYOUT_MN && layout != VNM_LAYOUT_NM) return fail(VNM_ERR_BAD_ARG, "vnm_spmm_f16_host: unknown layout %d", layout);
     cudaStream_t s = (cudaStream_t)stream;
     const size_t b_bytes = (size_t)h->K * N * 2, o_bytes = (size_t)h->M * N * 2;
     int rc;
     if ((rc = grow(&h->stage_B, &h->stage_B_bytes, b_bytes))) return rc;
     if ((rc = grow(&h->stage_out, &h->stage_out_bytes, o_bytes))) return rc;
-    VNM_CUDA(cudaMemcpyAsync(h->stage_B, B_host, b_bytes, cudaMemcpyHostToDevice, s), "H2D copy of B");
+    if (!h->host_pipe_ready) {
+        VNM_CUDA(cudaStreamCreateWithFlags(&h->copy_in, cudaStreamNonBlocking), "cudaStreamCreate");
+        VNM_CUDA(cudaStreamCreateWithFlags(&h->copy_out, cudaStreamNonBlocking), "cudaStreamCreate");
+        for (cudaEvent_t &e : h->ev) VNM_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming), "cudaEventCreate");
+        h->host_pipe_ready = true;
+    }
+    // The columns are cut into up to HOST_CHUNKS_MAX slices of a multiple of 256 columns.  Slice c+1 goes up
+    // (copy engine 1) while slice c is multiplied and slice c-1 comes down (copy engine 2), so the call costs
+    // about the larger of the two transfers instead of their sum.  On the device every slice is its own
+    // compact matrix, [K, nc] in and [M, nc] or [nc, M] out.
+    int nc = ((N + HOST_CHUNKS_MAX - 1) / HOST_CHUNKS_MAX + 255) / 256 * 256;
+    if (nc < 1024) nc = 1024;
+    const int chunks = (N + nc - 1) / nc;
+    cudaEvent_t ev_start = h->ev[2 * HOST_CHUNKS_MAX], ev_done = h->ev[2 * HOST_CHUNKS_MAX + 1];
+    VNM_CUDA(cudaEventRecord(ev_start, s), "event record");
+    VNM_CUDA(cudaStreamWaitEvent(h->copy_in, ev_start, 0), "stream wait");
+    VNM_CUDA(cudaStreamWaitEvent(h->copy_out, ev_start, 0), "stream wait");
     if (bias_host) {
         if (!h->stage_bias) VNM_CUDA(cudaMalloc(&h->stage_bias, (size_t)h->M * 2), "bias cudaMalloc");
-        VNM_CUDA(cudaMemcpyAsync(h->stage_bias, bias_host, (size_t)h->M * 2, cudaMemcpyHostToDevice, s), "H2D copy of bias");
+        VNM_CUDA(cudaMemcpyAsync(h->stage_bias, bias_host, (size_t)h->M * 2, cudaMemcpyHostToDevice, h->copy_in), "H2D copy of bias");
     }
-    rc = vnm_spmm_f16(h, h->stage_B, N, N, bias_host ? h->stage_bias : nullptr, h->stage_out, layout == VNM_LAYOUT_MN ? N : h->M, layout, stream);
+    for (int c = 0; c < chunks; ++c) {
+        const int n0 = c * nc, w = N - n0 < nc ? N - n0 : nc;
+        uint8_t *dB = (uint8_t *)h->stage_B + (size_t)h->K * n0 * 2;
+        uint8_t *dO = (uint8_t *)h->stage_out + (size_t)h->M * n0 * 2;
+        VNM_CUDA(cudaMemcpy2DAsync(dB, (size_t)w * 2, (const uint8_t *)B_host + (size_t)n0 * 2, (size_t)N * 2, (size_t)w * 2, h->K,
+                                   cudaMemcpyHostToDevice, h->copy_in), "H2D copy of B");
+        VNM_CUDA(cudaEventRecord(h->ev[2 * c], h->copy_in), "event record");
+        VNM_CUDA(cudaStreamWaitEvent(s, h->ev[2 * c], 0), "stream wait");
+        rc = vnm_spmm_f16(h, dB, w, w, bias_host ? h->stage_bias : nullptr, dO, layout == VNM_LAYOUT_MN ? w : h->M, layout, stream);
+        if (rc) break;
+        VNM_CUDA(cudaEventRecord(h->ev[2 * c + 1], s), "event record");
+        VNM_CUDA(cudaStreamWaitEvent(h->copy_out, h->ev[2 * c + 1], 0), "stream wait");
+        if (layout == VNM_LAYOUT_MN)
+            VNM_CUDA(cudaMemcpy2DAsync((uint8_t *)out_host + (size_t)n0 * 2, (size_t)N * 2, dO, (size_t)w * 2, (size_t)w * 2, h->M,
+                                       cudaMemcpyDeviceToHost, h->copy_out), "D2H copy of the result");
+        else
+            VNM_CUDA(cudaMemcpyAsync((uint8_t *)out_host + (size_t)h->M * n0 * 2, dO, (size_t)h->M * w * 2, cudaMemcpyDeviceToHost, h->copy_out),
+                     "D2H copy of the result");
+    }
+    // join both copy streams back into the caller's stream, also on the error path, before returning
+    cudaEventRecord(ev_done, h->copy_out);
+    cudaStreamWaitEvent(s, ev_done, 0);
+    cudaEventRecord(ev_start, h->copy_in);
+    cudaStreamWaitEvent(s, ev_start, 0);
+    cudaError_t e = cudaStreamSynchronize(s);
     if (rc) return rc;
-    VNM_CUDA(cudaMemcpyAsync(out_host, h->stage_out, o_bytes, cudaMemcpyDeviceToHost, s), "D2H copy of the result");
-    VNM_CUDA(cudaStreamSynchronize(s), "stream synchronize");
+    VNM_CUDA(e, "stream synchronize");
     return VNM_OK;
 }
 

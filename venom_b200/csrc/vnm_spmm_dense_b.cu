@@ -50,10 +50,11 @@ constexpr int SMEM_BYTES = A_RING_BYTES + B_RING_BYTES + OUT_RING_BYTES + BAR_BY
 static_assert(A_RING_BYTES % 1024 == 0 && B_RING_BYTES % 1024 == 0, "swizzled staging needs 1024-byte alignment");
 constexpr int NUM_THREADS = 384;  // 4 single-thread roles + 2 x 4 epilogue warps
 constexpr int TMEM_COLS = 512;
-constexpr int META_COL0 = RT * BN;  // first metadata column
+constexpr int ACC_SLOTS = RT + 1;  // accumulator (tile ti, row tile rt) lives in slot (RT * ti + rt) % ACC_SLOTS
+constexpr int META_COL0 = ACC_SLOTS * BN;  // first metadata column
 static_assert(SP >= SA && 2 * SP >= SB + 1, "too few k-tile barriers: a waiter could miss a phase");
 static_assert(META_COL0 + META_SETS * RT * 4 <= TMEM_COLS, "tensor memory overflow");
-static_assert((SA + SB + SP + SR + 2) * 8 + 16 <= BAR_BYTES, "barrier area too small");
+static_assert((SA + SB + SP + SR + 2 * ACC_SLOTS) * 8 + 16 <= BAR_BYTES, "barrier area too small");
 
 __device__ __forceinline__ bool wait_one(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int *status, int code)
 {
@@ -101,8 +102,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_kernel(const __gr
     uint64_t *kdone = b_full + SB;
     uint64_t *kready = kdone + SP;
     uint64_t *acc_full_bar = kready + SR;
-    uint64_t *acc_empty_bar = acc_full_bar + 1;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty_bar + 1);
+    uint64_t *acc_empty_bar = acc_full_bar + ACC_SLOTS;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty_bar + ACC_SLOTS);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5;
@@ -118,8 +119,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_kernel(const __gr
         for (int s = 0; s < SB; s++) mbar_init(&b_full[s], 1);
         for (int s = 0; s < SP; s++) mbar_init(&kdone[s], 1);
         for (int s = 0; s < SR; s++) mbar_init(&kready[s], 2);  // metadata copies done + operands landed
-        mbar_init(acc_full_bar, 1);
-        mbar_init(acc_empty_bar, 4 * RT);
+        for (int s = 0; s < ACC_SLOTS; s++) {
+            mbar_init(&acc_full_bar[s], 1);
+            mbar_init(&acc_empty_bar[s], 4);  // the four warps that drain it
+        }
         *abort_flag = 0;
         fence_barrier_init();
     }
@@ -237,32 +240,35 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_kernel(const __gr
             int it = 0;
             bool alive = true;
             for (int ti = 0; alive && ti < my_tiles; ++ti) {
-                TRACE(7, ti * 2);
-                if (!wait_one(acc_empty_bar, ((uint32_t)ti & 1u) ^ 1u, abort_flag, p.status, DEV_TIMEOUT_MMA)) break;
-                tc_fence_after();
-                TRACE(7, ti * 2 + 1);
-                for (int kt = 0; kt < p.ktiles; ++kt, ++it) {
+                // Accumulator slots rotate: row tile 0 of this tile has a slot nobody is draining, row tile 1
+                // takes over the slot row tile 0 of the previous tile is being drained from.  Inside a k-tile
+                // all MMAs of row tile 0 come first, so its drain also starts half a k-tile early.
+                for (int kt = 0; alive && kt < p.ktiles; ++kt, ++it) {
                     TRACE(2, it);
                     if (!wait_one(&kready[it % SR], (uint32_t)(it / SR) & 1u, abort_flag, p.status, DEV_TIMEOUT_MMA)) { alive = false; break; }
                     tc_fence_after();
                     TRACE(3, it);
                     const uint32_t mcol = tmem_base + META_COL0 + (uint32_t)(it % META_SETS) * (RT * 4);
 #pragma unroll
-                    for (int h = 0; h < 2; ++h) {
-                        const uint32_t boff = (uint32_t)(((2 * it + h) % SB) * B_STAGE_BYTES) >> 4;
-#pragma unroll
-                        for (int rt = 0; rt < RT; rt++) {
-                            const uint32_t aoff = (uint32_t)((it % SA) * A_STAGE_BYTES + rt * AM_BLOCK_BYTES) >> 4;
-#pragma unroll
-                            for (int k2 = 0; k2 < 2; k2++) {
-                                const int kb = h * 2 + k2;  // K=32 block inside the k-tile
-                                tc_mma_sp_f16(tmem_base + rt * BN, adesc0 + aoff + (uint32_t)(kb * 32 >> 4), bdesc0 + boff + (uint32_t)k2 * bstep,
-                                              mcol + rt * 4 + (uint32_t)(kb & ~1), idesc0 | (uint32_t)(kb & 1), (kt | kb) != 0 ? 1u : 0u, 0u, 0u, 0u, 0u);
-                            }
+                    for (int rt = 0; rt < RT; rt++) {
+                        const int use = RT * ti + rt, slot = use % ACC_SLOTS;
+                        if (kt == 0) {
+                            if (rt == 0) TRACE(7, ti * 2);
+                            if (!wait_one(&acc_empty_bar[slot], ((uint32_t)(use / ACC_SLOTS) & 1u) ^ 1u, abort_flag, p.status, DEV_TIMEOUT_MMA)) { alive = false; break; }
+                            tc_fence_after();
+                            if (rt == 0) TRACE(7, ti * 2 + 1);
                         }
+                        const uint32_t aoff = (uint32_t)((it % SA) * A_STAGE_BYTES + rt * AM_BLOCK_BYTES) >> 4;
+#pragma unroll
+                        for (int kb = 0; kb < 4; kb++) {  // K=32 blocks of the k-tile; two per B stage
+                            const uint32_t boff = (uint32_t)(((2 * it + (kb >> 1)) % SB) * B_STAGE_BYTES) >> 4;
+                            tc_mma_sp_f16(tmem_base + slot * BN, adesc0 + aoff + (uint32_t)(kb * 32 >> 4), bdesc0 + boff + (uint32_t)(kb & 1) * bstep,
+                                          mcol + rt * 4 + (uint32_t)(kb & ~1), idesc0 | (uint32_t)(kb & 1), (kt | kb) != 0 ? 1u : 0u, 0u, 0u, 0u, 0u);
+                        }
+                        if (kt == p.ktiles - 1) tc_commit(&acc_full_bar[slot]);
                     }
+                    if (!alive) break;
                     tc_commit(&kdone[it % SP]);
-                    if (kt == p.ktiles - 1) tc_commit(acc_full_bar);
                     TRACE(5, it);
                 }
             }
@@ -278,7 +284,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_kernel(const __gr
             const int mp = tile % mpairs;
             const int n0 = (tile / mpairs) * BN;
             // the four warps of a group leave the loop together (they meet at named barriers below)
-            const bool got = wait_warp(acc_full_bar, (uint32_t)ti & 1u, abort_flag, p.status, DEV_TIMEOUT_EPILOGUE);
+            const int use = RT * ti + ((warp - 4) >> 2), slot = use % ACC_SLOTS;
+            const bool got = wait_warp(&acc_full_bar[slot], (uint32_t)(use / ACC_SLOTS) & 1u, abort_flag, p.status, DEV_TIMEOUT_EPILOGUE);
             if (!named_barrier_and(1 + ((warp - 4) >> 2), 128, got)) break;
             tc_fence_after();
             if (warp == 4 && lane == 0) TRACE(6, ti * 3);
@@ -290,30 +297,31 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_kernel(const __gr
                 const bool row_ok = mt < p.mtiles && row < p.M;
                 const bool has_bias = p.layout == 1 && p.bias != nullptr;
                 const __half bias = (has_bias && row_ok) ? p.bias[row] : __ushort_as_half((unsigned short)0);
+                // The whole 128-column row of the accumulator goes into registers as packed halves first, so
+                // that the MMA issuer gets the accumulator back before any staging or store work starts.
+                uint32_t pk_all[BN / 2];
 #pragma unroll
                 for (int part = 0; part < BN / PART; part++) {
-                    uint32_t pk[PART / 2];
-                    {
-                        uint32_t v0[32], v1[32];
-                        const uint32_t tcol = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(rt * BN + part * PART);
-                        tc_ld_32x32b_x32(tcol, v0);
-                        tc_ld_32x32b_x32(tcol + 32u, v1);
-                        tc_wait_ld();
+                    uint32_t v0[32], v1[32];
+                    const uint32_t tcol = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(slot * BN + part * PART);
+                    tc_ld_32x32b_x32(tcol, v0);
+                    tc_ld_32x32b_x32(tcol + 32u, v1);
+                    tc_wait_ld();
 #pragma unroll
-                        for (int jj = 0; jj < 16; jj++) {
-                            __half2 h0 = __floats2half2_rn(__uint_as_float(v0[2 * jj]), __uint_as_float(v0[2 * jj + 1]));
-                            __half2 h1 = __floats2half2_rn(__uint_as_float(v1[2 * jj]), __uint_as_float(v1[2 * jj + 1]));
-                            pk[jj] = *reinterpret_cast<uint32_t *>(&h0);
-                            pk[16 + jj] = *reinterpret_cast<uint32_t *>(&h1);
-                        }
+                    for (int jj = 0; jj < 16; jj++) {
+                        __half2 h0 = __floats2half2_rn(__uint_as_float(v0[2 * jj]), __uint_as_float(v0[2 * jj + 1]));
+                        __half2 h1 = __floats2half2_rn(__uint_as_float(v1[2 * jj]), __uint_as_float(v1[2 * jj + 1]));
+                        pk_all[part * (PART / 2) + jj] = *reinterpret_cast<uint32_t *>(&h0);
+                        pk_all[part * (PART / 2) + 16 + jj] = *reinterpret_cast<uint32_t *>(&h1);
                     }
-                    if (part == BN / PART - 1) {
-                        // this warp's share of the accumulators is in registers: hand it back to the MMA issuer
-                        tc_fence_before();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(acc_empty_bar);
-                        if (warp == 4 && lane == 0) TRACE(6, ti * 3 + 1);
-                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&acc_empty_bar[slot]);
+                if (warp == 4 && lane == 0) TRACE(6, ti * 3 + 1);
+#pragma unroll
+                for (int part = 0; part < BN / PART; part++) {
+                    const uint32_t *pk = pk_all + part * (PART / 2);
                     if (p.layout == 0) {
                         // [M,N] output: stage 128 rows x 64 columns in shared memory (128-byte swizzle, rows at
                         // their actual position) and let one TMA store write full lines; it clips at M and N.
@@ -342,7 +350,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_kernel(const __gr
                         __half *col = reinterpret_cast<__half *>(stg) + arow;
 #pragma unroll
                         for (int jj = 0; jj < PART / 2; jj++) {
-                            __half2 h = *reinterpret_cast<__half2 *>(&pk[jj]);
+                            uint32_t pw = pk[jj];
+                            __half2 h = *reinterpret_cast<__half2 *>(&pw);
                             __half lo = __low2half(h), hi = __high2half(h);
                             if (has_bias) { lo = __hadd(lo, bias); hi = __hadd(hi, bias); }
                             col[(2 * jj) * TILE_M] = lo;
