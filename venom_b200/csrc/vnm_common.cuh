@@ -160,6 +160,21 @@ __device__ __forceinline__ void cp_async_16(uint32_t saddr, const void *gsrc, ui
 {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(saddr), "l"(gsrc), "r"(src_bytes) : "memory");
 }
+// 4-byte asynchronous copy global -> shared (any 4-byte aligned destination), grouped with commit / wait.
+__device__ __forceinline__ void cp_async_4(uint32_t saddr, const void *gsrc)
+{
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(saddr), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_8(uint32_t saddr, const void *gsrc)
+{
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(saddr), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int kPending>
+__device__ __forceinline__ void cp_async_wait()
+{
+    asm volatile("cp.async.wait_group %0;" ::"n"(kPending) : "memory");
+}
 // The barrier receives one arrival from this thread once all its earlier cp.async copies have landed
 // (the arrival must be part of the barrier's expected count).
 __device__ __forceinline__ void cp_async_mbar_arrive_noinc(uint64_t *bar)

@@ -5,7 +5,7 @@
 namespace vnm {
 
 // ------------------------------------------------------------------------------------------------
-// Compressor.  One thread owns one metadata word = (row pair 2p,2p+1) x (tile t of four groups):
+// Compressor, general form (any alignment, any m).  One thread owns one metadata word = (row pair 2p,2p+1) x (tile t of four groups):
 // it scans 2 x 4 groups x 4 column-loc candidates of the pruned dense matrix in ascending order,
 // emits the first two kept entries of every (row, group) as values + 2-bit positions, and writes one
 // 32-bit metadata word plus four 8-byte value pieces.  Threads of a warp walk consecutive tiles of
@@ -73,12 +73,198 @@ __global__ void __launch_bounds__(256) compress_kernel(const __half *__restrict_
     }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Tiled compressor (the one normally used).  A CTA takes 32 rows (inside one V-block, so one column-loc
+// row) x TS tiles of four groups = TS*4*m consecutive columns:
+//   1. the 32 dense row segments come in with coalesced 8-byte asynchronous copies into one of two
+//      shared-memory buffers (row pitch an odd number of words, so 32 lanes reading one column of 32 rows
+//      hit 32 banks), one chunk ahead of the work; in mask mode the int32 mask is folded into one bit per
+//      element;
+//   2. lane = row, warp = tile: the same selection as compress_kernel, results staged in shared memory in
+//      the reference's value order (128 halves per 16 rows x tile) and metadata order (16 words per
+//      32 rows x tile);
+//   3. both stagings are contiguous in global memory (TS*256 bytes per 16 rows, TS*64 bytes of metadata)
+//      and leave with 16-byte stores.
+// Needs 8-byte aligned dense and mask rows and an even m; launch_compress falls back to compress_kernel
+// otherwise.
+// ------------------------------------------------------------------------------------------------
+template <bool kHasMask>
+__global__ void __launch_bounds__(256) compress_tiled_kernel(const __half *__restrict__ dense, int64_t ldd, const int32_t *__restrict__ mask,
+                                                             const uint32_t *__restrict__ colloc, int M, int K, int V, int m, int64_t Ksp, int TS,
+                                                             uint32_t *__restrict__ values, uint32_t *__restrict__ meta,
+                                                             unsigned long long *violations)
+{
+    extern __shared__ __align__(16) uint8_t csm[];
+    const int span = TS * 4 * m;                 // columns per chunk, even
+    const int pitch = span + 4;                  // halves; 8-byte aligned rows, pitch / 2 = 2 mod 32: rows r and r+16 share banks
+    const int mpitch = ((span / 2 + 7) & ~7) + 4;  // mask bytes per row (two bits per byte); mpitch / 4 is odd
+    uint32_t *val_s = reinterpret_cast<uint32_t *>(csm);                 // [2][TS][64]
+    uint32_t *meta_s = val_s + 2 * TS * 64;                              // [TS][16]
+    unsigned short *in_s = reinterpret_cast<unsigned short *>(meta_s + TS * 16);  // [2 buffers][32][pitch]
+    uint8_t *mk_s = reinterpret_cast<uint8_t *>(in_s + 2 * 32 * pitch);  // [32][mpitch]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t tiles = Ksp / 8;
+    const int spans = (int)((tiles + TS - 1) / TS);
+    const int64_t chunks = (int64_t)(M / 32) * spans;
+    unsigned int bad = 0;
+
+    // Asynchronous 8-byte copies bring the 32 row segments of a chunk into one of two buffers: a warp takes
+    // rows warp, warp+8, ..., its lanes consecutive pieces, so global reads are coalesced and shared-memory
+    // writes hit consecutive banks.  The chunk after the current one is in flight while this one is worked on.
+    auto fetch = [&](int64_t ch, int buf) {
+        const int64_t rc = ch / spans;
+        const int64_t c0 = (ch - rc * spans) * TS * 4 * m;
+        const int valid = (int)(c0 >= K ? 0 : (K - c0 < span ? K - c0 : span));
+        const int nq = (valid + 3) / 4;  // 8-byte pieces per row holding existing columns
+        for (int r = warp; r < 32; r += 8) {
+            const __half *drow = dense + (rc * 32 + r) * ldd + c0;
+            unsigned short *srow = in_s + (buf * 32 + r) * pitch;
+            const uint32_t sbase = smem_u32(srow);
+#pragma unroll 4
+            for (int q = lane; q < nq; q += 32) {
+                if (4 * q + 4 <= valid) {
+                    cp_async_8(sbase + q * 8, reinterpret_cast<const uint2 *>(drow) + q);
+                } else {  // ragged end of the matrix
+                    for (int c = 4 * q; c < valid; c++) srow[c] = __half_as_ushort(drow[c]);
+                }
+            }
+        }
+        cp_async_commit();
+    };
+
+    int buf = 0;
+    if ((int64_t)blockIdx.x < chunks) fetch(blockIdx.x, 0);
+    for (int64_t ch = blockIdx.x; ch < chunks; ch += gridDim.x, buf ^= 1) {
+        const int64_t rc = ch / spans;
+        const int sp = (int)(ch - rc * spans);
+        const int64_t R0 = rc * 32;
+        const int64_t t0 = (int64_t)sp * TS;
+        const int tcount = (int)(tiles - t0 < TS ? tiles - t0 : TS);
+        const int64_t c0 = t0 * 4 * m;
+        if (ch + gridDim.x < chunks) {
+            fetch(ch + gridDim.x, buf ^ 1);
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        if (kHasMask) {  // the int32 mask, folded into one bit per element
+            const int valid = (int)(c0 >= K ? 0 : (K - c0 < span ? K - c0 : span));
+            const int nw = (valid + 1) / 2;
+            for (int r = warp; r < 32; r += 8) {
+                const int32_t *mrow = mask + (R0 + r) * ldd + c0;
+                for (int w = lane; w < nw; w += 32) {
+                    uint32_t mb;
+                    if (2 * w + 1 < valid) {
+                        const int2 mm = __ldg(reinterpret_cast<const int2 *>(mrow) + w);
+                        mb = (mm.x != 0) | ((mm.y != 0) << 1);
+                    } else {
+                        mb = mrow[2 * w] != 0;
+                    }
+                    mk_s[r * mpitch + w] = (uint8_t)mb;
+                }
+            }
+        }
+        __syncthreads();
+        // ---- lane = row, warp = tile
+        const uint32_t *crow = colloc + (R0 / V) * (Ksp / 2) * 4;
+        const unsigned short *my_in = in_s + (buf * 32 + lane) * pitch;
+        const uint8_t *my_mk = mk_s + lane * mpitch;
+        const int validc = (int)(c0 >= K ? 0 : (K - c0 < span ? K - c0 : span));
+        for (int tl = warp; tl < tcount; tl += 8) {
+            uint32_t hw = 0;
+            uint32_t *vdst = val_s + ((lane >> 4) * TS + tl) * 64 + ((lane & 15) >> 2) * 16 + (lane & 3);
+            const uint4 *c4p = reinterpret_cast<const uint4 *>(crow + (t0 + tl) * 16);
+#pragma unroll
+            for (int gi = 0; gi < 4; gi++) {
+                const uint4 c4 = __ldg(c4p + gi);
+                const int cand[4] = {(int)c4.x, (int)c4.y, (int)c4.z, (int)c4.w};
+                const int lg = (tl * 4 + gi) * m;  // first column of the group, relative to the chunk
+                uint32_t out = 0;
+                int pos = 0;
+                if (lg + m <= validc) {  // the whole group exists (same for every lane)
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        const int lc = lg + cand[j];
+                        const uint32_t bits = my_in[lc];
+                        const bool keep = kHasMask ? ((my_mk[lc >> 1] >> (lc & 1)) & 1) != 0 : (bits & 0x7FFFu) != 0;
+                        if (keep) {
+                            if (pos < 2) {
+                                out |= bits << (16 * pos);
+                                hw |= (uint32_t)j << (gi * 4 + pos * 2);
+                            }
+                            pos++;
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        const int lc = lg + cand[j];
+                        if (lc < validc) {
+                            const uint32_t bits = my_in[lc];
+                            const bool keep = kHasMask ? ((my_mk[lc >> 1] >> (lc & 1)) & 1) != 0 : (bits & 0x7FFFu) != 0;
+                            if (keep) {
+                                if (pos < 2) {
+                                    out |= bits << (16 * pos);
+                                    hw |= (uint32_t)j << (gi * 4 + pos * 2);
+                                }
+                                pos++;
+                            }
+                        } else if (j < 2) {
+                            pos++;  // slot (position 0, value 0) of a column past K
+                        }
+                    }
+                }
+                bad += (pos != 2);
+                vdst[gi * 4] = out;
+            }
+            const uint32_t other = __shfl_xor_sync(0xffffffffu, hw, 1);
+            if ((lane & 1) == 0) meta_s[tl * 16 + (lane >> 1)] = hw | (other << 16);
+        }
+        __syncthreads();
+        // ---- staged values and metadata -> global memory
+        const int vq = tcount * 16;  // 16-byte pieces per 16-row group
+        for (int i = threadIdx.x; i < 2 * vq; i += 256) {
+            const int rg = i >= vq ? 1 : 0;
+            const int k = i - rg * vq;
+            uint4 *dst = reinterpret_cast<uint4 *>(values + ((R0 / 16 + rg) * 16 * Ksp + t0 * 128) / 2);
+            dst[k] = reinterpret_cast<const uint4 *>(val_s + rg * TS * 64)[k];
+        }
+        uint4 *mdst = reinterpret_cast<uint4 *>(meta + (R0 / 32) * 16 * tiles + t0 * 16);
+        for (int i = threadIdx.x; i < tcount * 4; i += 256) mdst[i] = reinterpret_cast<const uint4 *>(meta_s)[i];
+    }
+    if (violations != nullptr) {
+        for (int o = 16; o > 0; o >>= 1) bad += __shfl_xor_sync(0xffffffffu, bad, o);
+        if (lane == 0 && bad) atomicAdd(violations, (unsigned long long)bad);
+    }
+}
+
 cudaError_t launch_compress(const void *dense, int64_t ldd, const int32_t *mask, const uint32_t *colloc, int M, int K, int V, int m,
                             void *values, uint32_t *meta, unsigned long long *violations, cudaStream_t stream)
 {
     const int64_t Ksp = ksp_of(K, m);
-    const int64_t total = (int64_t)(M / 2) * (Ksp / 8);
     const int threads = 256;
+    const bool aligned = ldd % 4 == 0 && ((uintptr_t)dense & 7) == 0 && ((uintptr_t)mask & 7) == 0 && ((uintptr_t)meta & 15) == 0 &&
+                         m <= 128 && M % 32 == 0 && V % 32 == 0;
+    if (aligned) {
+        const int TS = m >= 128 ? 1 : (m <= 8 ? 16 : 128 / m);  // at most 512 columns per chunk
+        const int span = TS * 4 * m;
+        const size_t smem = (size_t)(2 * TS * 64 + TS * 16) * 4 + (size_t)2 * 32 * (span + 4) * 2 + (mask ? (size_t)32 * (((span / 2 + 7) & ~7) + 4) : 0);
+        const int64_t chunks = (int64_t)(M / 32) * ((Ksp / 8 + TS - 1) / TS);
+        int64_t blocks = chunks < (int64_t)148 * 3 ? chunks : (int64_t)148 * 3;
+        // up to ~83 KiB: two input buffers, the output staging and the mask bits
+        cudaError_t e = mask ? cudaFuncSetAttribute(compress_tiled_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024)
+                             : cudaFuncSetAttribute(compress_tiled_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+        if (e != cudaSuccess) return e;
+        if (blocks < 1) blocks = 1;
+        if (mask)
+            compress_tiled_kernel<true><<<(unsigned)blocks, threads, smem, stream>>>((const __half *)dense, ldd, mask, colloc, M, K, V, m, Ksp, TS,
+                                                                                   (uint32_t *)values, meta, violations);
+        else
+            compress_tiled_kernel<false><<<(unsigned)blocks, threads, smem, stream>>>((const __half *)dense, ldd, mask, colloc, M, K, V, m, Ksp, TS,
+                                                                                    (uint32_t *)values, meta, violations);
+        return cudaGetLastError();
+    }
+    const int64_t total = (int64_t)(M / 2) * (Ksp / 8);
     int64_t blocks = (total + threads - 1) / threads;
     const int64_t cap = (int64_t)148 * 64;
     if (blocks > cap) blocks = cap;
