@@ -334,22 +334,23 @@ static int spmm_impl(vnm_handle_t h, const void *B, int64_t ldb, int N, int b_nk
         cuuint32_t estr[2] = {1, 1};
         CUresult r;
         if (b_nk) {
-            // B given as [N, K] (K contiguous): boxes of 64 k x 128 rows (n) form the K-major operand tile.
+            // B given as [N, K] (K contiguous): boxes of 32 k x 64 rows (n), written with the 64-byte swizzle,
+            // form the K-major operand tile of one MMA.
             cuuint64_t dims[2] = {(cuuint64_t)h->K, (cuuint64_t)N};
             cuuint64_t strides[1] = {(cuuint64_t)ldb * 2};
-            cuuint32_t box[2] = {64, 128};
+            cuuint32_t box[2] = {32, 64};
             r = enc(&h->tmap_tile, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(B), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
             h->tmap_rows = h->tmap_tile;
         } else {
             // B viewed as a 2-D tensor {N (contiguous), K}; one box = 64 columns (128 bytes) of one row
-            // (gather4 picks four such rows) or of 64 consecutive rows, written with the 128-byte swizzle
-            // the MMA's N-major operand layout expects.  Rows >= K and columns >= N read as zeros.
+            // (gather4 picks four such rows) or of 64 consecutive rows (32 for the dense-B kernel), written with
+            // the 128-byte swizzle the MMA's N-major operand layout expects.  Rows >= K and columns >= N read as zeros.
             cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)h->K};
             cuuint64_t strides[1] = {(cuuint64_t)ldb * 2};
             cuuint32_t box_rows[2] = {64, 1};
-            cuuint32_t box_tile[2] = {64, 64};
+            cuuint32_t box_tile[2] = {64, h->dense_b ? 32u : 64u};
             r = enc(&h->tmap_rows, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(B), dims, strides, box_rows, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -377,8 +378,8 @@ static int spmm_impl(vnm_handle_t h, const void *B, int64_t ldb, int N, int b_nk
     p.trace = h->trace;
     p.b_nk = b_nk;
     if (h->dense_b) {
-        // The result leaves through TMA stores: [M,N] as boxes of 64 columns x 128 rows (128-byte swizzled
-        // staging), [N,M] as boxes of 128 columns (m) x 64 rows (n).
+        // The result leaves through TMA stores: [M,N] as boxes of 40 columns x 128 rows, [N,M] as boxes of 128
+        // columns (m) x 40 rows (n).
         if (layout == VNM_LAYOUT_NM && (ldo % 8 != 0 || ((uintptr_t)out & 15)))
             return fail(VNM_ERR_BAD_ARG, "vnm_spmm_f16: layout NM needs ldo %% 8 == 0 and a 16-byte aligned out for this operand");
         CUtensorMap tmap_out;
@@ -387,12 +388,12 @@ static int spmm_impl(vnm_handle_t h, const void *B, int64_t ldb, int N, int b_nk
         CUresult r;
         if (layout == VNM_LAYOUT_MN) {
             cuuint64_t odims[2] = {(cuuint64_t)N, (cuuint64_t)h->M};
-            cuuint32_t obox[2] = {64, 128};
+            cuuint32_t obox[2] = {40, 128};
             r = enc(&tmap_out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, out, odims, ostrides, obox, oestr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                    CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         } else {
             cuuint64_t odims[2] = {(cuuint64_t)h->M, (cuuint64_t)N};
-            cuuint32_t obox[2] = {128, 64};
+            cuuint32_t obox[2] = {128, 40};
             r = enc(&tmap_out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, out, odims, ostrides, obox, oestr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                     CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         }

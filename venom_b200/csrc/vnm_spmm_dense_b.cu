@@ -1,20 +1,24 @@
 // SpMM kernel for the dense-B operand form (the V:2:m pattern re-expressed as 2:4 over all K columns).
 //
-// Here B is read as ordinary tiles that every row of A shares, so one CTA can reuse a B stage for two
-// 128-row tiles of A: a 256 x 128 output tile with two accumulators (128 tensor-memory columns each).
-// Per k-tile (128 original columns of A = 128 rows of B) the CTA streams
-//     2 x 18 KiB value + metadata blocks   and   2 x 16 KiB stages of B (64 rows x 128 columns)
-// = 68 KiB for eight 128 x 128 x 32 MMAs, against 82 KiB for four 128 x 256 x 32 MMAs in the gather
-// kernel.  Fewer bytes per MMA clock means more k-tiles of MMA work buffered in the same shared memory,
-// which is what hides the load latency.
+// Here B is read as ordinary tiles that every row of A shares, so one CTA reuses a B stage for two
+// 128-row tiles of A: a 256 x 240 output tile with two accumulators of 240 tensor-memory columns (240 is
+// the widest N that leaves room for the metadata columns).  The mainloop runs at the rate at which an SM
+// takes in data from L2 (about 64 bytes per clock), so the tile is as large as tensor memory allows: per
+// k-tile (128 original columns of A = 128 rows of B) the CTA streams
+//     2 x 18 KiB value + metadata blocks   and   2 x 32 KiB stages of B (64 rows x 256 columns, 240 used)
+// = 100 KiB for eight 128 x 240 x 32 MMAs (152 clocks each), i.e. 53 KiB per 256 x 128 outputs.
 //
-// Warp roles (384 threads):
+// Warp roles (512 threads; the first two warpgroups give registers to the last two):
 //   warp 0      A producer (one thread): two bulk copies per k-tile.
-//   warp 1      B producer (one thread): two TMA tile loads (64 rows x 64 columns) per stage.
-//   warp 2      sequencer (one thread): waits for the A blocks, copies both metadata images to tensor
-//               memory, waits for the B stages, flips the k-tile's "ready" barrier.
-//   warp 3      MMA issuer (one thread) and tensor-memory owner: one wait, eight MMAs, one commit per k-tile.
-//   warps 4..11 epilogue: four warps per accumulator drain it, hand it back, store.
+//   warp 1      sequencer (one thread): waits for the A blocks, copies both metadata images to tensor memory
+//               and flips the k-tile's "ready" barrier.
+//   warp 3      MMA issuer (one thread) and tensor-memory owner: per K=32 block one wait for its B stage, two
+//               MMAs (one per row tile) and one commit that frees the stage.
+//   warps 4..7  B producers (one thread each): warp 4+c loads the c-th 64-column slice (32 rows x 128 bytes; or,
+//               for B given as [N, K], 64 rows of 32 k) of every stage.  Issued from one thread the TMA tile
+//               loads reach about 15 bytes per clock, from four threads about twice that.
+//   warps 8..15 epilogue: four warps per accumulator read their rows into registers, hand the accumulator
+//               back, and store six parts of 40 columns through shared memory with one TMA store each.
 // Every wait is bounded: on expiry the kernel records a status bit, drains and returns.
 #include "vnm_internal.h"
 
@@ -32,29 +36,33 @@ constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;  // ~2 s at B200 clocks
 #endif
 
 constexpr int RT = 2;            // row tiles per CTA tile
-constexpr int BN = 128;          // output columns per CTA tile
+constexpr int BN = 240;          // output columns per CTA tile
+constexpr int PART = 40;         // columns per epilogue part / TMA store
 constexpr int SA = 3;            // A ring: k-tiles (each RT blocks)
-constexpr int SB = 5;            // B ring: stages of 64 rows x BN columns
-constexpr int SP = 4;            // k-tile "done" barriers
+constexpr int SB = 6;            // B ring: stages of 32 rows x 256 columns (one K=32 block of the MMAs)
+constexpr int SF = 12;           // stage "free" barriers (more than stages, so that a late waiter never sees a wrapped phase)
 constexpr int SR = 4;            // k-tile "ready" barriers
 constexpr int META_SETS = 3;     // metadata column sets in tensor memory (4 columns per row tile each)
-constexpr int B_CHUNK_BYTES = 64 * 128;            // 64 rows x 64 columns
-constexpr int B_STAGE_BYTES = (BN / 64) * B_CHUNK_BYTES;  // 16 KiB
+constexpr int B_CHUNK_BYTES = 32 * 128;            // 32 rows x 64 columns
+constexpr int B_STAGE_BYTES = 4 * B_CHUNK_BYTES;    // 16 KiB: four 64-column slices, the last one used up to column 240 (or 240 rows of 32 k)
 constexpr int A_STAGE_BYTES = RT * AM_BLOCK_BYTES;  // 36 KiB
 constexpr int A_RING_BYTES = SA * A_STAGE_BYTES;
 constexpr int B_RING_BYTES = SB * B_STAGE_BYTES;
-constexpr int OUT_STAGE_BYTES = TILE_M * 128;       // 128 rows x 64 fp16 columns, staging of one TMA store
+constexpr int OUT_STAGE_BYTES = TILE_M * PART * 2;  // 128 rows x 40 fp16 columns, staging of one TMA store
 constexpr int OUT_RING_BYTES = RT * OUT_STAGE_BYTES;  // one staging buffer per accumulator
 constexpr int BAR_BYTES = 256;
 constexpr int SMEM_BYTES = A_RING_BYTES + B_RING_BYTES + OUT_RING_BYTES + BAR_BYTES + 1024;
 static_assert(A_RING_BYTES % 1024 == 0 && B_RING_BYTES % 1024 == 0, "swizzled staging needs 1024-byte alignment");
-constexpr int NUM_THREADS = 384;  // 4 single-thread roles + 2 x 4 epilogue warps
+static_assert(SMEM_BYTES <= 227 * 1024, "shared memory per CTA");
+constexpr int NUM_THREADS = 512;  // warps 0-3 single-thread roles, 4-7 B producers, 8-15 epilogue (2 x 4 warps)
+constexpr int EPI_WARP0 = 8;
 constexpr int TMEM_COLS = 512;
-constexpr int ACC_SLOTS = RT + 1;  // accumulator (tile ti, row tile rt) lives in slot (RT * ti + rt) % ACC_SLOTS
-constexpr int META_COL0 = ACC_SLOTS * BN;  // first metadata column
-static_assert(SP >= SA && 2 * SP >= SB + 1, "too few k-tile barriers: a waiter could miss a phase");
-static_assert(META_COL0 + META_SETS * RT * 4 <= TMEM_COLS, "tensor memory overflow");
-static_assert((SA + SB + SP + SR + 2 * ACC_SLOTS) * 8 + 16 <= BAR_BYTES, "barrier area too small");
+// tensor-memory columns: accumulator 0 at 0..239, metadata sets at 240 and 248, accumulator 1 at 256..495, metadata set at 496
+__device__ __forceinline__ uint32_t acc_col(int rt) { return (uint32_t)rt * 256u; }
+__device__ __forceinline__ uint32_t meta_col(int set) { return set == 0 ? 240u : (set == 1 ? 248u : 496u); }
+static_assert(SF >= 4 * SA && SF >= 4 * META_SETS && SF >= 2 * SB && SF % SB == 0, "too few stage barriers: a waiter could miss a phase");
+static_assert(BN <= 240 && META_SETS == 3 && RT == 2 && BN % 16 == 0 && BN == 6 * PART, "tensor-memory column plan");
+static_assert((SA + SB + SF + SR + 2) * 8 + 16 <= BAR_BYTES, "barrier area too small");
 
 __device__ __forceinline__ bool wait_one(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int *status, int code)
 {
@@ -99,11 +107,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_kernel(const __gr
     uint8_t *out_ring = smem + A_RING_BYTES + B_RING_BYTES;
     uint64_t *a_full = reinterpret_cast<uint64_t *>(smem + A_RING_BYTES + B_RING_BYTES + OUT_RING_BYTES);
     uint64_t *b_full = a_full + SA;
-    uint64_t *kdone = b_full + SB;
-    uint64_t *kready = kdone + SP;
+    uint64_t *b_free = b_full + SB;   // b_free[j % SF]: the MMAs that read B stage j (k-tile j / 4, K=32 block j % 4) have completed
+    uint64_t *kready = b_free + SF;
     uint64_t *acc_full_bar = kready + SR;
-    uint64_t *acc_empty_bar = acc_full_bar + ACC_SLOTS;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty_bar + ACC_SLOTS);
+    uint64_t *acc_empty_bar = acc_full_bar + 1;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty_bar + 1);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5;
@@ -116,13 +124,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_kernel(const __gr
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < SA; s++) mbar_init(&a_full[s], 1);
-        for (int s = 0; s < SB; s++) mbar_init(&b_full[s], 1);
-        for (int s = 0; s < SP; s++) mbar_init(&kdone[s], 1);
-        for (int s = 0; s < SR; s++) mbar_init(&kready[s], 2);  // metadata copies done + operands landed
-        for (int s = 0; s < ACC_SLOTS; s++) {
-            mbar_init(&acc_full_bar[s], 1);
-            mbar_init(&acc_empty_bar[s], 4);  // the four warps that drain it
-        }
+        for (int s = 0; s < SB; s++) mbar_init(&b_full[s], 4);  // one arrival (+ 4 KiB) per B producer warp
+        for (int s = 0; s < SF; s++) mbar_init(&b_free[s], 1);
+        for (int s = 0; s < SR; s++) mbar_init(&kready[s], 1);  // A block landed and its metadata copied to tensor memory
+        mbar_init(acc_full_bar, 1);
+        mbar_init(acc_empty_bar, 4 * RT);
         *abort_flag = 0;
         fence_barrier_init();
     }
@@ -135,8 +141,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_kernel(const __gr
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
+    // Register re-allocation, first statement of every role: the eight epilogue warps hold a whole accumulator
+    // row in registers (192 each), the other eight need few (64 each).
     if (warp == 0) {
         // ---------------- A producer ----------------
+        setmaxnreg_dec<64>();
         if (lane == 0) {
             int it = 0;
             bool alive = true;
@@ -145,8 +154,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_kernel(const __gr
                 for (int kt = 0; kt < p.ktiles; ++kt, ++it) {
                     const int s = it % SA;
                     if (it >= SA) {
-                        const int kd = it - SA;
-                        if (!wait_one(&kdone[kd % SP], (uint32_t)(kd / SP) & 1u, abort_flag, p.status, DEV_TIMEOUT_PRODUCER)) { alive = false; break; }
+                        const int jd = 4 * (it - SA) + 3;  // last B stage of the k-tile that used this slot
+                        if (!wait_one(&b_free[jd % SF], (uint32_t)(jd / SF) & 1u, abort_flag, p.status, DEV_TIMEOUT_PRODUCER)) { alive = false; break; }
                     }
                     TRACE(0, it);
                     mbar_arrive_expect_tx(&a_full[s], A_STAGE_BYTES);
@@ -164,31 +173,29 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_kernel(const __gr
             }
         }
         __syncwarp();
-    } else if (warp == 1) {
-        // ---------------- B producer ----------------
+    } else if (warp >= 4 && warp < EPI_WARP0) {
+        // ---------------- B producers: warp 4 + c loads the c-th 64-column (or 64-row) slice of every stage ----------------
+        // (one thread issuing all TMA tile loads cannot keep the copy engine busy; four in parallel can)
+        setmaxnreg_dec<64>();
         if (lane == 0) {
+            const int c = warp - 4;
             tma_prefetch_desc(&tmap_tile);
             int j = 0;
             bool alive = true;
             for (int tile = blockIdx.x; alive && tile < total_tiles; tile += gridDim.x) {
                 const int n0 = (tile / mpairs) * BN;
-                for (int jl = 0; jl < 2 * p.ktiles; ++jl, ++j) {
+                for (int jl = 0; jl < 4 * p.ktiles; ++jl, ++j) {
                     const int s = j % SB;
                     if (j >= SB) {
-                        const int kd = (j - SB) >> 1;
-                        if (!wait_one(&kdone[kd % SP], (uint32_t)(kd / SP) & 1u, abort_flag, p.status, DEV_TIMEOUT_PRODUCER)) { alive = false; break; }
+                        const int jd = j - SB;
+                        if (!wait_one(&b_free[jd % SF], (uint32_t)(jd / SF) & 1u, abort_flag, p.status, DEV_TIMEOUT_PRODUCER)) { alive = false; break; }
                     }
-                    TRACE(1, j);
+                    if (c == 0) TRACE(1, j);
                     if (p.gather_mode != GATHER_NONE) {
-                        mbar_arrive_expect_tx(&b_full[s], B_STAGE_BYTES);
-                        if (p.b_nk) {
-                            // B given as [N, K]: one box of 128 rows (n) x 64 k, i.e. a K-major operand tile
-                            tma_load_2d(b_ring + s * B_STAGE_BYTES, &tmap_tile, jl * 64, n0, &b_full[s]);
-                        } else {
-#pragma unroll
-                            for (int c = 0; c < BN / 64; c++)
-                                tma_load_2d(b_ring + s * B_STAGE_BYTES + c * B_CHUNK_BYTES, &tmap_tile, n0 + c * 64, jl * 64, &b_full[s]);
-                        }
+                        mbar_arrive_expect_tx(&b_full[s], B_CHUNK_BYTES);
+                        // the last slice carries 16 columns of the next tile along (never read by the MMAs)
+                        if (p.b_nk) tma_load_2d(b_ring + s * B_STAGE_BYTES + c * B_CHUNK_BYTES, &tmap_tile, jl * 32, n0 + c * 64, &b_full[s]);
+                        else tma_load_2d(b_ring + s * B_STAGE_BYTES + c * B_CHUNK_BYTES, &tmap_tile, n0 + c * 64, jl * 32, &b_full[s]);
                     } else {
                         mbar_arrive(&b_full[s]);
                     }
@@ -199,8 +206,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_kernel(const __gr
             }
         }
         __syncwarp();
-    } else if (warp == 2) {
+    } else if (warp == 1) {
         // ---------------- sequencer ----------------
+        setmaxnreg_dec<64>();
         if (lane == 0) {
             const uint64_t mdesc0 = make_smem_desc(smem_u32(a_ring) + A_IMG_BYTES, 0, 128, 0);
             bool alive = true;
@@ -208,74 +216,70 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_kernel(const __gr
                 const int sa = it % SA;
                 // column set it % META_SETS was last read by the MMAs of k-tile it - META_SETS
                 if (it >= META_SETS) {
-                    const int kd = it - META_SETS;
-                    if (!wait_one(&kdone[kd % SP], (uint32_t)(kd / SP) & 1u, abort_flag, p.status, DEV_TIMEOUT_MMA)) break;
+                    const int jd = 4 * (it - META_SETS) + 3;
+                    if (!wait_one(&b_free[jd % SF], (uint32_t)(jd / SF) & 1u, abort_flag, p.status, DEV_TIMEOUT_MMA)) break;
                 }
                 if (!wait_one(&a_full[sa], (uint32_t)(it / SA) & 1u, abort_flag, p.status, DEV_TIMEOUT_MMA)) break;
                 tc_fence_after();
-                TRACE(4, 2 * it);
-                const uint32_t mcol = tmem_base + META_COL0 + (uint32_t)(it % META_SETS) * (RT * 4);
+                const uint32_t mcol = tmem_base + meta_col(it % META_SETS);
 #pragma unroll
                 for (int rt = 0; rt < RT; rt++)
                     tc_cp_128x128b(mcol + rt * 4, mdesc0 + ((uint32_t)(sa * A_STAGE_BYTES + rt * AM_BLOCK_BYTES) >> 4));
                 tc_commit(&kready[it % SR]);
-                for (int h = 0; h < 2; ++h) {
-                    const int j = 2 * it + h;
-                    if (!wait_one(&b_full[j % SB], (uint32_t)(j / SB) & 1u, abort_flag, p.status, DEV_TIMEOUT_MMA)) { alive = false; break; }
-                }
-                TRACE(4, 2 * it + 1);
-                if (alive) mbar_arrive(&kready[it % SR]);
             }
         }
         __syncwarp();
     } else if (warp == 3) {
         // ---------------- MMA issuer ----------------
+        setmaxnreg_dec<64>();
         if (lane == 0) {
             const bool b_nk = p.b_nk != 0;
             const uint32_t idesc0 = make_idesc_f16(TILE_M, BN, true, 0u, !b_nk);
             const uint64_t adesc0 = make_smem_desc(smem_u32(a_ring), 16, 1024, 2);
-            // B stage: N-major (two 64-column slices, 64 k-rows of 128 B each) or K-major (128 n-rows of 128 B = 64 k)
-            const uint64_t bdesc0 = b_nk ? make_smem_desc(smem_u32(b_ring), 16, 1024, 2) : make_smem_desc(smem_u32(b_ring), B_CHUNK_BYTES, 1024, 2);
-            const uint32_t bstep = b_nk ? (64u >> 4) : (4096u >> 4);  // next K=32 block: 32 k = 64 B along a row, or 32 rows further
+            // B stage = the 32 k of one MMA: N-major (four 64-column slices of 32 rows x 128 bytes, 128-byte swizzle)
+            // or K-major (256 n-rows of 64 bytes of which 240 are used, 64-byte swizzle, 8-row groups 512 bytes apart)
+            const uint64_t bdesc0 = b_nk ? make_smem_desc(smem_u32(b_ring), 16, 512, 4) : make_smem_desc(smem_u32(b_ring), B_CHUNK_BYTES, 1024, 2);
             int it = 0;
             bool alive = true;
             for (int ti = 0; alive && ti < my_tiles; ++ti) {
-                // Accumulator slots rotate: row tile 0 of this tile has a slot nobody is draining, row tile 1
-                // takes over the slot row tile 0 of the previous tile is being drained from.  Inside a k-tile
-                // all MMAs of row tile 0 come first, so its drain also starts half a k-tile early.
                 for (int kt = 0; alive && kt < p.ktiles; ++kt, ++it) {
                     TRACE(2, it);
                     if (!wait_one(&kready[it % SR], (uint32_t)(it / SR) & 1u, abort_flag, p.status, DEV_TIMEOUT_MMA)) { alive = false; break; }
                     tc_fence_after();
                     TRACE(3, it);
-                    const uint32_t mcol = tmem_base + META_COL0 + (uint32_t)(it % META_SETS) * (RT * 4);
+                    if (kt == 0) {
+                        TRACE(7, ti * 2);
+                        if (!wait_one(acc_empty_bar, ((uint32_t)ti & 1u) ^ 1u, abort_flag, p.status, DEV_TIMEOUT_MMA)) { alive = false; break; }
+                        tc_fence_after();
+                        TRACE(7, ti * 2 + 1);
+                    }
+                    const uint32_t mcol = tmem_base + meta_col(it % META_SETS);
+                    const uint32_t aoff = (uint32_t)((it % SA) * A_STAGE_BYTES) >> 4;
 #pragma unroll
-                    for (int rt = 0; rt < RT; rt++) {
-                        const int use = RT * ti + rt, slot = use % ACC_SLOTS;
-                        if (kt == 0) {
-                            if (rt == 0) TRACE(7, ti * 2);
-                            if (!wait_one(&acc_empty_bar[slot], ((uint32_t)(use / ACC_SLOTS) & 1u) ^ 1u, abort_flag, p.status, DEV_TIMEOUT_MMA)) { alive = false; break; }
-                            tc_fence_after();
-                            if (rt == 0) TRACE(7, ti * 2 + 1);
-                        }
-                        const uint32_t aoff = (uint32_t)((it % SA) * A_STAGE_BYTES + rt * AM_BLOCK_BYTES) >> 4;
+                    for (int kb = 0; kb < 4; kb++) {  // K=32 blocks of the k-tile, one B stage each
+                        const int j = 4 * it + kb;
+                        if (!wait_one(&b_full[j % SB], (uint32_t)(j / SB) & 1u, abort_flag, p.status, DEV_TIMEOUT_MMA)) { alive = false; break; }
+                        tc_fence_after();
+                        TRACE(4, j);
+                        const uint32_t boff = (uint32_t)((j % SB) * B_STAGE_BYTES) >> 4;
 #pragma unroll
-                        for (int kb = 0; kb < 4; kb++) {  // K=32 blocks of the k-tile; two per B stage
-                            const uint32_t boff = (uint32_t)(((2 * it + (kb >> 1)) % SB) * B_STAGE_BYTES) >> 4;
-                            tc_mma_sp_f16(tmem_base + slot * BN, adesc0 + aoff + (uint32_t)(kb * 32 >> 4), bdesc0 + boff + (uint32_t)(kb & 1) * bstep,
+                        for (int rt = 0; rt < RT; rt++)
+                            tc_mma_sp_f16(tmem_base + acc_col(rt), adesc0 + aoff + (uint32_t)((rt * AM_BLOCK_BYTES + kb * 32) >> 4), bdesc0 + boff,
                                           mcol + rt * 4 + (uint32_t)(kb & ~1), idesc0 | (uint32_t)(kb & 1), (kt | kb) != 0 ? 1u : 0u, 0u, 0u, 0u, 0u);
-                        }
-                        if (kt == p.ktiles - 1) tc_commit(&acc_full_bar[slot]);
+                        tc_commit(&b_free[j % SF]);  // the stage (and, after the fourth, the A blocks and metadata set) may be refilled
                     }
                     if (!alive) break;
-                    tc_commit(&kdone[it % SP]);
+                    if (kt == p.ktiles - 1) tc_commit(acc_full_bar);
                     TRACE(5, it);
                 }
             }
         }
         __syncwarp();
+    } else if (warp == 2) {
+        setmaxnreg_dec<64>();  // idle warp of the first warpgroup
     } else {
         // ---------------- epilogue ----------------
+        setmaxnreg_inc<192>();
         const int q = warp & 3;
         const int i = q * 32 + lane;
         const int arow = mma_row_to_actual(i);
@@ -284,69 +288,50 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_kernel(const __gr
             const int mp = tile % mpairs;
             const int n0 = (tile / mpairs) * BN;
             // the four warps of a group leave the loop together (they meet at named barriers below)
-            const int use = RT * ti + ((warp - 4) >> 2), slot = use % ACC_SLOTS;
-            const bool got = wait_warp(&acc_full_bar[slot], (uint32_t)(use / ACC_SLOTS) & 1u, abort_flag, p.status, DEV_TIMEOUT_EPILOGUE);
-            if (!named_barrier_and(1 + ((warp - 4) >> 2), 128, got)) break;
+            const bool got = wait_warp(acc_full_bar, (uint32_t)ti & 1u, abort_flag, p.status, DEV_TIMEOUT_EPILOGUE);
+            if (!named_barrier_and(1 + ((warp - EPI_WARP0) >> 2), 128, got)) break;
             tc_fence_after();
-            if (warp == 4 && lane == 0) TRACE(6, ti * 3);
-            constexpr int PART = 64;
+            if (warp == EPI_WARP0 && lane == 0) TRACE(6, ti * 3);
             {
-                const int rt = (warp - 4) >> 2;  // which accumulator this warp drains
+                const int rt = (warp - EPI_WARP0) >> 2;  // which accumulator this warp drains
                 const int mt = mp * RT + rt;
                 const int64_t row = (int64_t)mt * TILE_M + arow;
                 const bool row_ok = mt < p.mtiles && row < p.M;
                 const bool has_bias = p.layout == 1 && p.bias != nullptr;
                 const __half bias = (has_bias && row_ok) ? p.bias[row] : __ushort_as_half((unsigned short)0);
-                // The whole 128-column row of the accumulator goes into registers as packed halves first, so
-                // that the MMA issuer gets the accumulator back before any staging or store work starts.
-                uint32_t pk_all[BN / 2];
-#pragma unroll
-                for (int part = 0; part < BN / PART; part++) {
-                    uint32_t v0[32], v1[32];
-                    const uint32_t tcol = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(slot * BN + part * PART);
-                    tc_ld_32x32b_x32(tcol, v0);
-                    tc_ld_32x32b_x32(tcol + 32u, v1);
+                uint8_t *stg = out_ring + rt * OUT_STAGE_BYTES;
+                const bool leader = (warp == EPI_WARP0 + 4 * rt) && lane == 0;
+                const uint32_t trow = tmem_base + ((uint32_t)(q * 32) << 16) + acc_col(rt);
+                // 40 accumulator columns of this thread's row -> 20 registers of packed halves
+                auto drain = [&](int part, uint32_t *pk) {
+                    uint32_t v0[32], v1[8];
+                    tc_ld_32x32b_x32(trow + (uint32_t)(part * PART), v0);
+                    tc_ld_32x32b_x8(trow + (uint32_t)(part * PART) + 32u, v1);
                     tc_wait_ld();
 #pragma unroll
                     for (int jj = 0; jj < 16; jj++) {
                         __half2 h0 = __floats2half2_rn(__uint_as_float(v0[2 * jj]), __uint_as_float(v0[2 * jj + 1]));
-                        __half2 h1 = __floats2half2_rn(__uint_as_float(v1[2 * jj]), __uint_as_float(v1[2 * jj + 1]));
-                        pk_all[part * (PART / 2) + jj] = *reinterpret_cast<uint32_t *>(&h0);
-                        pk_all[part * (PART / 2) + 16 + jj] = *reinterpret_cast<uint32_t *>(&h1);
+                        pk[jj] = *reinterpret_cast<uint32_t *>(&h0);
                     }
-                }
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&acc_empty_bar[slot]);
-                if (warp == 4 && lane == 0) TRACE(6, ti * 3 + 1);
 #pragma unroll
-                for (int part = 0; part < BN / PART; part++) {
-                    const uint32_t *pk = pk_all + part * (PART / 2);
+                    for (int jj = 0; jj < 4; jj++) {
+                        __half2 h1 = __floats2half2_rn(__uint_as_float(v1[2 * jj]), __uint_as_float(v1[2 * jj + 1]));
+                        pk[16 + jj] = *reinterpret_cast<uint32_t *>(&h1);
+                    }
+                };
+                // one part -> staging buffer -> one TMA store (which clips at M and N)
+                auto store_part = [&](int part, const uint32_t *pk) {
+                    const bool in_range = mt < p.mtiles && n0 + part * PART < p.N;
+                    if (leader) bulk_wait_group_read0();  // the previous store has finished reading the staging buffer
+                    named_barrier_sync(1 + rt, 128);
                     if (p.layout == 0) {
-                        // [M,N] output: stage 128 rows x 64 columns in shared memory (128-byte swizzle, rows at
-                        // their actual position) and let one TMA store write full lines; it clips at M and N.
-                        uint8_t *stg = out_ring + rt * OUT_STAGE_BYTES;
-                        const bool leader = (warp == 4 + 4 * rt) && lane == 0;
-                        if (leader) bulk_wait_group_read0();  // the previous store has finished reading the staging buffer
-                        named_barrier_sync(1 + rt, 128);
+                        // [M,N] output: 128 rows (at their actual position) x 40 columns
 #pragma unroll
-                        for (int c = 0; c < 8; c++)
-                            *reinterpret_cast<uint4 *>(stg + arow * 128 + ((c ^ (arow & 7)) << 4)) =
-                                make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
-                        fence_proxy_async();
-                        named_barrier_sync(1 + rt, 128);
-                        if (leader && mt < p.mtiles) {
-                            tma_store_2d(&tmap_out, stg, n0 + part * PART, mt * TILE_M);
-                            bulk_commit_group();
-                        }
+                        for (int c = 0; c < PART / 8; c++)
+                            *reinterpret_cast<uint4 *>(stg + arow * (PART * 2) + c * 16) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
                     } else {
-                        // [N,M] output (+ bias): stage the transposed part, 64 rows (n) x 128 columns (m) without
-                        // swizzle -- the 32 lanes of a warp write 32 consecutive m of one n -- and store it with
-                        // one TMA store, which clips at N and M.
-                        uint8_t *stg = out_ring + rt * OUT_STAGE_BYTES;
-                        const bool leader = (warp == 4 + 4 * rt) && lane == 0;
-                        if (leader) bulk_wait_group_read0();
-                        named_barrier_sync(1 + rt, 128);
+                        // [N,M] output (+ bias): the transposed part, 40 rows (n) x 128 columns (m); the 32 lanes
+                        // of a warp write 32 m of one n
                         __half *col = reinterpret_cast<__half *>(stg) + arow;
 #pragma unroll
                         for (int jj = 0; jj < PART / 2; jj++) {
@@ -357,19 +342,40 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_kernel(const __gr
                             col[(2 * jj) * TILE_M] = lo;
                             col[(2 * jj + 1) * TILE_M] = hi;
                         }
-                        fence_proxy_async();
-                        named_barrier_sync(1 + rt, 128);
-                        if (leader && mt < p.mtiles) {
-                            tma_store_2d(&tmap_out, stg, mt * TILE_M, n0 + part * PART);
-                            bulk_commit_group();
-                        }
                     }
+                    fence_proxy_async();
+                    named_barrier_sync(1 + rt, 128);
+                    if (leader && in_range) {
+                        if (p.layout == 0) tma_store_2d(&tmap_out, stg, n0 + part * PART, mt * TILE_M);
+                        else tma_store_2d(&tmap_out, stg, mt * TILE_M, n0 + part * PART);
+                        bulk_commit_group();
+                    }
+                };
+                // The first parts go out one by one; the last HELD parts are all read into registers first, so the
+                // MMA issuer gets the accumulator back before their staging and store work (the register file
+                // does not hold the packed halves of all six).
+                constexpr int NPARTS = BN / PART, HELD = 5;
+#pragma unroll
+                for (int part = 0; part < NPARTS - HELD; part++) {
+                    uint32_t pk[PART / 2];
+                    drain(part, pk);
+                    store_part(part, pk);
                 }
+                uint32_t held[HELD * (PART / 2)];
+#pragma unroll
+                for (int h = 0; h < HELD; h++) drain(NPARTS - HELD + h, held + h * (PART / 2));
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(acc_empty_bar);
+                if (warp == EPI_WARP0 && lane == 0) TRACE(6, ti * 3 + 1);
+#pragma unroll
+                for (int h = 0; h < HELD; h++) store_part(NPARTS - HELD + h, held + h * (PART / 2));
+                if (warp == EPI_WARP0 && lane == 0) TRACE(6, ti * 3 + 2);
             }
         }
     }
 
-    if (warp >= 4 && ((warp - 4) & 3) == 0 && lane == 0) bulk_wait_group0();  // this thread's TMA stores are complete
+    if (warp >= EPI_WARP0 && ((warp - EPI_WARP0) & 3) == 0 && lane == 0) bulk_wait_group0();  // this thread's TMA stores are complete
     tc_fence_before();
     __syncthreads();
     if (warp == 3) {
