@@ -113,6 +113,16 @@ int vnm_operand_form(vnm_handle_t handle, int *dense_b);
 int vnm_spmm_f16_host(vnm_handle_t handle, const void *B_host, int N, const void *bias_host,
                       void *out_host, int layout, void *stream);
 
+/* The same call without the final wait: it returns once the copies and launches are queued, so that the
+ * host-to-device copies of one product overlap the device-to-host copies of the one before (different
+ * handles, or the same handle after vnm_host_wait).  out_host is valid after vnm_host_wait(handle); host buffers
+ * should be pinned, otherwise the copies are synchronous anyway.  One outstanding call per handle.
+ * No counterpart in the reference (its harness copies and computes in separate, blocking steps,
+ * src/spmm/spatha_spmm.cpp:24-38,84-90). */
+int vnm_spmm_f16_host_async(vnm_handle_t handle, const void *B_host, int N, const void *bias_host,
+                            void *out_host, int layout, void *stream);
+int vnm_host_wait(vnm_handle_t handle);
+
 /* The same product for callers that cannot allocate device memory (no counterpart in the reference, whose
  * device format always comes from cudaMalloc).  Think of a serving process whose framework already owns
  * the whole device, a plug-in living inside another component's memory budget, or a loop that cannot take

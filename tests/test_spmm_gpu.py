@@ -129,6 +129,22 @@ def test_spmm_host_buffers_in_slices(capi, oracle, cfg):
     _check(oracle, o_nm.numpy(), oracle.spmm(ov, om, cols, M, K, V, m, B, bias=bias, layout=1))
 
 
+def test_spmm_host_async_calls_overlap_and_match(capi, oracle):
+    """Three products queued without waiting (different handles, pinned buffers), collected afterwards."""
+    import torch
+    cases = [(128, 512, 128, 8, 1280), (256, 256, 64, 8, 2048), (128, 1024, 128, 16, 1024)]
+    jobs = []
+    for i, (M, K, V, m, N) in enumerate(cases):
+        prep, Bd, _ = _setup(capi, oracle, M, K, V, m, N, seed=40 + i, ints=False)
+        jobs.append((prep, Bd, Bd.cpu().pin_memory(), torch.empty((M, N), dtype=torch.float16).pin_memory()))
+    for prep, Bd, Bh, oh in jobs:
+        prep.spmm_host_async(Bh, oh)
+    for prep, Bd, Bh, oh in jobs:
+        prep.host_wait()
+    for prep, Bd, Bh, oh in jobs:
+        assert torch.equal(oh, prep.spmm(Bd).cpu())
+
+
 def test_bad_arguments_raise(capi, oracle):
     import torch
     M, K, V, m, N = 128, 256, 128, 8, 64

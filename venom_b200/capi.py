@@ -43,6 +43,10 @@ def lib():
         L.vnm_destroy.argtypes = [C.c_void_p]
         L.vnm_spmm_f16.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_void_p, C.c_void_p, C.c_int64,
                                    C.c_int, C.c_void_p]
+        L.vnm_spmm_f16_host_async.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]
+        L.vnm_spmm_f16_host_async.restype = C.c_int
+        L.vnm_host_wait.argtypes = [C.c_void_p]
+        L.vnm_host_wait.restype = C.c_int
         L.vnm_spmm_f16_nk.argtypes = L.vnm_spmm_f16.argtypes
         L.vnm_spmm_f16_nk.restype = C.c_int
         L.vnm_operand_form.argtypes = [C.c_void_p, C.POINTER(C.c_int)]
@@ -201,6 +205,16 @@ class Prepared:
         _check(lib().vnm_spmm_f16_host(self._h, B_host.data_ptr(), N, None if bias_host is None else bias_host.data_ptr(),
                                        out_host.data_ptr(), layout, _stream()))
         return out_host
+
+    def spmm_host_async(self, B_host, out_host, bias_host=None, layout=VNM_LAYOUT_MN):
+        """spmm_host without the final wait (pinned host tensors); collect with host_wait()."""
+        N = B_host.shape[1]
+        _check(lib().vnm_spmm_f16_host_async(self._h, B_host.data_ptr(), N, None if bias_host is None else bias_host.data_ptr(),
+                                             out_host.data_ptr(), layout, _stream()))
+        return out_host
+
+    def host_wait(self):
+        _check(lib().vnm_host_wait(self._h))
 
     def device_status(self):
         st = C.c_int(0)

@@ -433,7 +433,7 @@ static int grow(void **buf, size_t *cap, size_t need)
     return VNM_OK;
 }
 
-int vnm_spmm_f16_host(vnm_handle_t h, const void *B_host, int N, const void *bias_host, void *out_host, int layout, void *stream)
+static int spmm_host_impl(vnm_handle_t h, const void *B_host, int N, const void *bias_host, void *out_host, int layout, void *stream, bool wait)
 {
     if (!h || !B_host || !out_host) return fail(VNM_ERR_BAD_ARG, "vnm_spmm_f16_host: null pointer");
     if (N <= 0 || N % 8 != 0) return fail(VNM_ERR_BAD_ARG, "vnm_spmm_f16_host: N (%d) must be a positive multiple of 8", N);
@@ -483,6 +483,7 @@ int vnm_spmm_f16_host(vnm_handle_t h, const void *B_host, int N, const void *bia
             VNM_CUDA(cudaMemcpyAsync((uint8_t *)out_host + (size_t)h->M * n0 * 2, dO, (size_t)h->M * w * 2, cudaMemcpyDeviceToHost, h->copy_out),
                      "D2H copy of the result");
     }
+    if (!wait) return rc;  // the caller collects the result with vnm_host_wait
     // join both copy streams back into the caller's stream, also on the error path, before returning
     cudaEventRecord(ev_done, h->copy_out);
     cudaStreamWaitEvent(s, ev_done, 0);
@@ -491,6 +492,25 @@ int vnm_spmm_f16_host(vnm_handle_t h, const void *B_host, int N, const void *bia
     cudaError_t e = cudaStreamSynchronize(s);
     if (rc) return rc;
     VNM_CUDA(e, "stream synchronize");
+    return VNM_OK;
+}
+
+int vnm_spmm_f16_host(vnm_handle_t h, const void *B_host, int N, const void *bias_host, void *out_host, int layout, void *stream)
+{
+    return spmm_host_impl(h, B_host, N, bias_host, out_host, layout, stream, true);
+}
+
+int vnm_spmm_f16_host_async(vnm_handle_t h, const void *B_host, int N, const void *bias_host, void *out_host, int layout, void *stream)
+{
+    return spmm_host_impl(h, B_host, N, bias_host, out_host, layout, stream, false);
+}
+
+int vnm_host_wait(vnm_handle_t h)
+{
+    if (!h) return fail(VNM_ERR_BAD_ARG, "vnm_host_wait: null handle");
+    if (!h->host_pipe_ready) return VNM_OK;
+    VNM_CUDA(cudaStreamSynchronize(h->copy_in), "stream synchronize");
+    VNM_CUDA(cudaStreamSynchronize(h->copy_out), "stream synchronize");
     return VNM_OK;
 }
 
