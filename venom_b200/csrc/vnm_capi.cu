@@ -2,6 +2,7 @@
 // handle, TMA descriptor construction for the dense operand, and kernel dispatch.
 #include "../../include/venom_b200.h"
 #include "vnm_internal.h"
+#include <mutex>
 
 #include <cstdio>
 #include <cstdarg>
@@ -111,7 +112,7 @@ struct vnm_prepared_s {
     void *stage_out;
     size_t stage_out_bytes;
     void *stage_bias;
-    cudaStream_t copy_in, copy_out;   // host-buffer entry point: copy engines run beside the kernels
+    cudaStream_t copy_in, copy_out;   // host-buffer entry point: the device's two copy streams (shared by all handles)
     cudaEvent_t ev[2 * HOST_CHUNKS_MAX + 2];
     bool host_pipe_ready;
     int gather_mode;
@@ -246,8 +247,6 @@ int vnm_destroy(vnm_handle_t h)
     cudaFree(h->stage_out);
     cudaFree(h->stage_bias);
     if (h->host_pipe_ready) {
-        cudaStreamDestroy(h->copy_in);
-        cudaStreamDestroy(h->copy_out);
         for (cudaEvent_t e : h->ev) cudaEventDestroy(e);
     }
     delete h;
@@ -444,8 +443,20 @@ static int spmm_host_impl(vnm_handle_t h, const void *B_host, int N, const void 
     if ((rc = grow(&h->stage_B, &h->stage_B_bytes, b_bytes))) return rc;
     if ((rc = grow(&h->stage_out, &h->stage_out_bytes, o_bytes))) return rc;
     if (!h->host_pipe_ready) {
-        VNM_CUDA(cudaStreamCreateWithFlags(&h->copy_in, cudaStreamNonBlocking), "cudaStreamCreate");
-        VNM_CUDA(cudaStreamCreateWithFlags(&h->copy_out, cudaStreamNonBlocking), "cudaStreamCreate");
+        // One upload and one download stream per device for every handle: with a pair of streams per handle
+        // the driver multiplexes them onto a few hardware queues and unrelated copies end up waiting for each other.
+        static std::mutex mu;
+        static cudaStream_t up[64], down[64];
+        {
+            std::lock_guard<std::mutex> lock(mu);
+            const int dev = h->device >= 0 && h->device < 64 ? h->device : 0;
+            if (!up[dev]) {
+                VNM_CUDA(cudaStreamCreateWithFlags(&up[dev], cudaStreamNonBlocking), "cudaStreamCreate");
+                VNM_CUDA(cudaStreamCreateWithFlags(&down[dev], cudaStreamNonBlocking), "cudaStreamCreate");
+            }
+            h->copy_in = up[dev];
+            h->copy_out = down[dev];
+        }
         for (cudaEvent_t &e : h->ev) VNM_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming), "cudaEventCreate");
         h->host_pipe_ready = true;
     }
