@@ -105,6 +105,8 @@ struct vnm_prepared_s {
     bool tm_valid;
     CUtensorMap tmap_rows;
     CUtensorMap tmap_tile;
+    CUtensorMap tmap_tile2;  // dense-B kernel: 2-D map for the ragged right edge
+    bool tm_wide;            // tmap_tile is the 4-D one-box-per-stage map
     int producer_warps;
     // device staging of the host-buffer entry point
     void *stage_B;
@@ -333,15 +335,17 @@ static int spmm_impl(vnm_handle_t h, const void *B, int64_t ldb, int N, int b_nk
         cuuint32_t estr[2] = {1, 1};
         CUresult r;
         if (b_nk) {
-            // B given as [N, K] (K contiguous): boxes of 32 k x 64 rows (n), written with the 64-byte swizzle,
-            // form the K-major operand tile of one MMA.
+            // B given as [N, K] (K contiguous): one box of 32 k x 256 rows (n), written with the 64-byte swizzle,
+            // is the K-major operand tile of one MMA (the last 16 rows belong to the next tile and are not read).
             cuuint64_t dims[2] = {(cuuint64_t)h->K, (cuuint64_t)N};
             cuuint64_t strides[1] = {(cuuint64_t)ldb * 2};
-            cuuint32_t box[2] = {32, 64};
+            cuuint32_t box[2] = {32, 256};
             r = enc(&h->tmap_tile, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(B), dims, strides, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
             h->tmap_rows = h->tmap_tile;
+            h->tmap_tile2 = h->tmap_tile;
+            h->tm_wide = false;
         } else {
             // B viewed as a 2-D tensor {N (contiguous), K}; one box = 64 columns (128 bytes) of one row
             // (gather4 picks four such rows) or of 64 consecutive rows (32 for the dense-B kernel), written with
@@ -357,6 +361,24 @@ static int spmm_impl(vnm_handle_t h, const void *B, int64_t ldb, int N, int b_nk
                 r = enc(&h->tmap_tile, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(B), dims, strides, box_tile, estr,
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            h->tmap_tile2 = h->tmap_tile;
+            h->tm_wide = false;
+            if (r == CUDA_SUCCESS && h->dense_b && N >= 256) {
+                // dense-B kernel: {64 columns, K rows, 4 slices of 64 columns, start column / 16}.  A box {64, 32, 4, 1}
+                // lands as [slice][row][64 columns], the N-major operand tile of one MMA, with a single instruction.
+                // Only start columns whose 256 columns lie inside N are addressable; the ragged edge uses the 2-D map.
+                cuuint64_t dims4[4] = {64, (cuuint64_t)h->K, 4, (cuuint64_t)((N - 256) / 16 + 1)};
+                cuuint64_t strides4[3] = {(cuuint64_t)ldb * 2, 128, 32};
+                cuuint32_t box4[4] = {64, 32, 4, 1};
+                cuuint32_t estr4[4] = {1, 1, 1, 1};
+                CUtensorMap wide;
+                if (enc(&wide, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void *>(B), dims4, strides4, box4, estr4,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS) {
+                    h->tmap_tile = wide;
+                    h->tm_wide = true;
+                }
+            }
         }
         if (r != CUDA_SUCCESS) return fail(VNM_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
         h->tm_B = B; h->tm_ldb = ldb; h->tm_N = N; h->tm_nk = b_nk; h->tm_valid = true;
@@ -376,6 +398,7 @@ static int spmm_impl(vnm_handle_t h, const void *B, int64_t ldb, int N, int b_nk
     p.total_tiles = p.mtiles * p.ntiles;
     p.trace = h->trace;
     p.b_nk = b_nk;
+    p.b_wide_ok = h->tm_wide ? 1 : 0;
     if (h->dense_b) {
         // The result leaves through TMA stores: [M,N] as boxes of 40 columns x 128 rows, [N,M] as boxes of 128
         // columns (m) x 40 rows (n).
@@ -397,7 +420,7 @@ static int spmm_impl(vnm_handle_t h, const void *B, int64_t ldb, int N, int b_nk
                     CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         }
         if (r != CUDA_SUCCESS) return fail(VNM_ERR_CUDA, "cuTensorMapEncodeTiled (output) failed with CUresult %d", (int)r);
-        VNM_CUDA(launch_spmm_dense_b(cfg, h->tmap_tile, tmap_out, p, (cudaStream_t)stream), "spmm launch");
+        VNM_CUDA(launch_spmm_dense_b(cfg, h->tmap_tile, h->tmap_tile2, tmap_out, p, (cudaStream_t)stream), "spmm launch");
     } else {
         VNM_CUDA(launch_spmm(cfg, h->tmap_rows, h->tmap_tile, p, (cudaStream_t)stream), "spmm launch");
     }

@@ -129,6 +129,22 @@ __device__ __forceinline__ void tma_load_2d(void *smem_dst, const void *tmap, in
                  "l"(tmap), "r"(col), "r"(row), "r"(smem_u32(bar))
                  : "memory");
 }
+// TMA tile load of a 3-D box at (c0, c1, c2), c0 innermost.
+__device__ __forceinline__ void tma_load_3d(void *smem_dst, const void *tmap, int c0, int c1, int c2, uint64_t *bar)
+{
+    asm volatile("cp.async.bulk.tensor.3d.shared::cta.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(
+                     smem_u32(smem_dst)),
+                 "l"(tmap), "r"(c0), "r"(c1), "r"(c2), "r"(smem_u32(bar))
+                 : "memory");
+}
+// TMA tile load of a 4-D box at (c0, c1, c2, c3), c0 innermost.
+__device__ __forceinline__ void tma_load_4d(void *smem_dst, const void *tmap, int c0, int c1, int c2, int c3, uint64_t *bar)
+{
+    asm volatile("cp.async.bulk.tensor.4d.shared::cta.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(
+                     smem_u32(smem_dst)),
+                 "l"(tmap), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(smem_u32(bar))
+                 : "memory");
+}
 // TMA tile store shared -> global of a 2-D box at (col, row); completion is tracked by bulk groups.
 __device__ __forceinline__ void tma_store_2d(const void *tmap, const void *smem_src, int col, int row)
 {

@@ -30,6 +30,7 @@ struct SpmmParams {
     int total_tiles;      // mtiles * ntiles
     long long *trace;     // debug builds (-DVNM_TRACE) only: clock stamps of CTA 0, else null
     int b_nk;             // dense-B kernel only: the dense operand is given as [N, K] row-major (K contiguous)
+    int b_wide_ok;        // dense-B kernel only: the 4-D tensor map exists (column tiles with 256 columns inside N use one box per stage)
 };
 
 // How the producer warps bring the selected rows of B into shared memory.
@@ -72,7 +73,7 @@ cudaError_t launch_spmm(const SpmmConfig &cfg, const CUtensorMap &tmap_rows, con
 // Dense-B form: 256 x 128 tiles, two accumulators sharing every B stage (vnm_spmm_dense_b.cu).
 cudaError_t spmm_dense_b_init();
 void spmm_dense_b_config(int M, int N, SpmmConfig *cfg);
-cudaError_t launch_spmm_dense_b(const SpmmConfig &cfg, const CUtensorMap &tmap_tile, const CUtensorMap &tmap_out, const SpmmParams &p,
-                                cudaStream_t stream);
+cudaError_t launch_spmm_dense_b(const SpmmConfig &cfg, const CUtensorMap &tmap_tile, const CUtensorMap &tmap_tile2, const CUtensorMap &tmap_out,
+                                const SpmmParams &p, cudaStream_t stream);
 
 }  // namespace vnm

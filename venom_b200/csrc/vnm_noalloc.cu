@@ -161,6 +161,7 @@ extern "C" int vnm_spmm_f16_noalloc(const void *values, const uint32_t *meta, co
     p.total_tiles = p.mtiles * p.ntiles;
     p.trace = nullptr;
     p.b_nk = 0;
+    p.b_wide_ok = 0;
     e = launch_spmm(cfg, tmap_rows, tmap_tile, p, s);
     if (e != cudaSuccess) return nfail(VNM_ERR_CUDA, "product launch: %s", cudaGetErrorString(e));
 

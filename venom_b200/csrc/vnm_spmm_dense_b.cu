@@ -14,9 +14,10 @@
 //               and flips the k-tile's "ready" barrier.
 //   warp 3      MMA issuer (one thread) and tensor-memory owner: per K=32 block one wait for its B stage, two
 //               MMAs (one per row tile) and one commit that frees the stage.
-//   warps 4..7  B producers (one thread each): warp 4+c loads the c-th 64-column slice (32 rows x 128 bytes; or,
-//               for B given as [N, K], 64 rows of 32 k) of every stage.  Issued from one thread the TMA tile
-//               loads reach about 15 bytes per clock, from four threads about twice that.
+//   warps 4..6  B producers (one thread each): stages are dealt round-robin; a stage is one 16 KiB TMA box (a 4-D
+//               map {64 columns, K rows, 4 slices of 64 columns, start column / 16} gives the [slice][row][64 columns]
+//               layout in one instruction; for B given as [N, K] a 2-D box of 256 rows x 32 k).  One thread issuing every TMA tile load keeps
+//               the copy engine about a third busy (measured); three do.
 //   warps 8..15 epilogue: four warps per accumulator read their rows into registers, hand the accumulator
 //               back, and store six parts of 40 columns through shared memory with one TMA store each.
 // Every wait is bounded: on expiry the kernel records a status bit, drains and returns.
@@ -56,10 +57,12 @@ static_assert(A_RING_BYTES % 1024 == 0 && B_RING_BYTES % 1024 == 0, "swizzled st
 static_assert(SMEM_BYTES <= 227 * 1024, "shared memory per CTA");
 constexpr int NUM_THREADS = 512;  // warps 0-3 single-thread roles, 4-7 B producers, 8-15 epilogue (2 x 4 warps)
 constexpr int EPI_WARP0 = 8;
+constexpr int NBP = 3;            // B producer warps (SB % NBP == 0: a ring slot always has the same owner)
 constexpr int TMEM_COLS = 512;
 // tensor-memory columns: accumulator 0 at 0..239, metadata sets at 240 and 248, accumulator 1 at 256..495, metadata set at 496
 __device__ __forceinline__ uint32_t acc_col(int rt) { return (uint32_t)rt * 256u; }
 __device__ __forceinline__ uint32_t meta_col(int set) { return set == 0 ? 240u : (set == 1 ? 248u : 496u); }
+static_assert(SB % NBP == 0 && NBP <= 4, "B producers");
 static_assert(SF >= 4 * SA && SF >= 4 * META_SETS && SF >= 2 * SB && SF % SB == 0, "too few stage barriers: a waiter could miss a phase");
 static_assert(BN <= 240 && META_SETS == 3 && RT == 2 && BN % 16 == 0 && BN == 6 * PART, "tensor-memory column plan");
 static_assert((SA + SB + SF + SR + 2) * 8 + 16 <= BAR_BYTES, "barrier area too small");
@@ -97,7 +100,8 @@ __device__ __forceinline__ void drain_slot(uint64_t *bar, uint32_t parity, int *
     atomicOr(status, DEV_TIMEOUT_DRAIN);
 }
 
-__global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_kernel(const __grid_constant__ CUtensorMap tmap_tile, const __grid_constant__ CUtensorMap tmap_out,
+__global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_kernel(const __grid_constant__ CUtensorMap tmap_tile, const __grid_constant__ CUtensorMap tmap_tile2,
+                                                                      const __grid_constant__ CUtensorMap tmap_out,
                                                                       const SpmmParams p)
 {
     extern __shared__ uint8_t smem_raw[];
@@ -124,7 +128,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_kernel(const __gr
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < SA; s++) mbar_init(&a_full[s], 1);
-        for (int s = 0; s < SB; s++) mbar_init(&b_full[s], 4);  // one arrival (+ 4 KiB) per B producer warp
+        for (int s = 0; s < SB; s++) mbar_init(&b_full[s], 1);
         for (int s = 0; s < SF; s++) mbar_init(&b_free[s], 1);
         for (int s = 0; s < SR; s++) mbar_init(&kready[s], 1);  // A block landed and its metadata copied to tensor memory
         mbar_init(acc_full_bar, 1);
@@ -174,35 +178,46 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_kernel(const __gr
         }
         __syncwarp();
     } else if (warp >= 4 && warp < EPI_WARP0) {
-        // ---------------- B producers: warp 4 + c loads the c-th 64-column (or 64-row) slice of every stage ----------------
-        // (one thread issuing all TMA tile loads cannot keep the copy engine busy; four in parallel can)
+        // ---------------- B producers: warp 4 + w loads the stages j = w, w + NBP, ... (a ring slot always has the same owner) ----------------
+        // One thread keeps the copy engine only about a third busy with TMA tile loads (measured), so the stages
+        // are dealt to three threads, and a stage is a single 16 KiB box wherever the tensor map allows it.
         setmaxnreg_dec<64>();
-        if (lane == 0) {
-            const int c = warp - 4;
+        if (lane == 0 && warp - 4 < NBP) {
             tma_prefetch_desc(&tmap_tile);
-            int j = 0;
-            bool alive = true;
-            for (int tile = blockIdx.x; alive && tile < total_tiles; tile += gridDim.x) {
+            tma_prefetch_desc(&tmap_tile2);
+            const int per_tile = 4 * p.ktiles;
+            int j = warp - 4;
+            int tile_i = j / per_tile, jl = j - tile_i * per_tile;
+            const int total_j = my_tiles * per_tile;
+            for (; j < total_j; j += NBP) {
+                const int tile = (int)blockIdx.x + tile_i * (int)gridDim.x;
                 const int n0 = (tile / mpairs) * BN;
-                for (int jl = 0; jl < 4 * p.ktiles; ++jl, ++j) {
-                    const int s = j % SB;
-                    if (j >= SB) {
-                        const int jd = j - SB;
-                        if (!wait_one(&b_free[jd % SF], (uint32_t)(jd / SF) & 1u, abort_flag, p.status, DEV_TIMEOUT_PRODUCER)) { alive = false; break; }
-                    }
-                    if (c == 0) TRACE(1, j);
-                    if (p.gather_mode != GATHER_NONE) {
-                        mbar_arrive_expect_tx(&b_full[s], B_CHUNK_BYTES);
-                        // the last slice carries 16 columns of the next tile along (never read by the MMAs)
-                        if (p.b_nk) tma_load_2d(b_ring + s * B_STAGE_BYTES + c * B_CHUNK_BYTES, &tmap_tile, jl * 32, n0 + c * 64, &b_full[s]);
-                        else tma_load_2d(b_ring + s * B_STAGE_BYTES + c * B_CHUNK_BYTES, &tmap_tile, n0 + c * 64, jl * 32, &b_full[s]);
-                    } else {
-                        mbar_arrive(&b_full[s]);
+                const int s = j % SB;
+                if (j >= SB) {
+                    const int jd = j - SB;
+                    if (!wait_one(&b_free[jd % SF], (uint32_t)(jd / SF) & 1u, abort_flag, p.status, DEV_TIMEOUT_PRODUCER)) break;
+                }
+                TRACE(1, j);
+                uint8_t *dst = b_ring + s * B_STAGE_BYTES;
+                if (p.gather_mode == GATHER_NONE) {
+                    mbar_arrive(&b_full[s]);
+                } else {
+                    // columns n0 + 240 .. n0 + 255 of the next tile come along and are never read by the MMAs
+                    mbar_arrive_expect_tx(&b_full[s], B_STAGE_BYTES);
+                    if (p.b_nk) {
+                        tma_load_2d(dst, &tmap_tile, jl * 32, n0, &b_full[s]);  // 256 rows (n) x 32 k, 64-byte swizzle
+                    } else if (p.b_wide_ok && n0 + 256 <= p.N) {
+                        tma_load_4d(dst, &tmap_tile, 0, jl * 32, 0, n0 / 16, &b_full[s]);  // {64 columns, 32 rows, 4 slices} from column n0
+                    } else {  // ragged right edge: four boxes that clip (and zero-fill) at N
+                        for (int c = 0; c < 4; c++) tma_load_2d(dst + c * B_CHUNK_BYTES, &tmap_tile2, n0 + c * 64, jl * 32, &b_full[s]);
                     }
                 }
+                jl += NBP;
+                while (jl >= per_tile) { jl -= per_tile; ++tile_i; }
             }
             if (*abort_flag && p.gather_mode != GATHER_NONE) {
-                for (int k = j > SB ? j - SB : 0; k < j; ++k) drain_slot(&b_full[k % SB], (uint32_t)(k / SB) & 1u, p.status);
+                // this thread's copies still in flight: the last SB / NBP stages it issued
+                for (int k = j - NBP, n = 0; k >= 0 && n < SB / NBP; k -= NBP, ++n) drain_slot(&b_full[k % SB], (uint32_t)(k / SB) & 1u, p.status);
             }
         }
         __syncwarp();
@@ -410,10 +425,10 @@ void spmm_dense_b_config(int M, int N, SpmmConfig *cfg)
     cfg->grid = (int)(tiles < sms ? tiles : sms);
 }
 
-cudaError_t launch_spmm_dense_b(const SpmmConfig &cfg, const CUtensorMap &tmap_tile, const CUtensorMap &tmap_out, const SpmmParams &p,
-                                cudaStream_t stream)
+cudaError_t launch_spmm_dense_b(const SpmmConfig &cfg, const CUtensorMap &tmap_tile, const CUtensorMap &tmap_tile2, const CUtensorMap &tmap_out,
+                                const SpmmParams &p, cudaStream_t stream)
 {
-    spmm_dense_b_kernel<<<(unsigned)cfg.grid, NUM_THREADS, SMEM_BYTES, stream>>>(tmap_tile, tmap_out, p);
+    spmm_dense_b_kernel<<<(unsigned)cfg.grid, NUM_THREADS, SMEM_BYTES, stream>>>(tmap_tile, tmap_tile2, tmap_out, p);
     return cudaGetLastError();
 }
 
