@@ -168,6 +168,11 @@ int vnm_set_gather_mode(vnm_handle_t handle, int mode);
  * Both forms give the same result up to fp32 summation order. */
 enum { VNM_STRATEGY_AUTO = 0, VNM_STRATEGY_GATHER = 1, VNM_STRATEGY_DENSE_B = 2 };
 int vnm_set_strategy(int strategy);
+/* vnm_prepare with the operand form chosen for this one handle (DENSE_B falls back to GATHER where the form does
+ * not exist).  The torch op asks for DENSE_B when its dense operand arrives as a transposed [N, K] view, which
+ * only that form reads in place. */
+int vnm_prepare_as(const void *values, const uint32_t *meta, const uint32_t *colloc,
+                   int M, int K, int V, int n, int m, int strategy, vnm_handle_t *handle, void *stream);
 int vnm_set_producer_warps(vnm_handle_t handle, int warps);
 
 /* Kernel configuration that vnm_spmm_f16 would launch for this handle and N (for reporting). */

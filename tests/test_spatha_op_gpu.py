@@ -124,3 +124,28 @@ def test_bert_encoder_harness_small(spatha):
         a = dense(ids).last_hidden_state.float()
         b = sparse(ids).last_hidden_state.float()
     assert torch.allclose(a, b, rtol=3e-2, atol=3e-2), (a - b).abs().max()
+
+
+def test_transposed_view_prepares_dense_b_form_at_high_sparsity(spatha, oracle):
+    """At 128:2:32 the automatic choice is the gather form; an activation that arrives as a transposed view
+    makes the op prepare the dense-B form instead (read in place).  Both must agree with the oracle."""
+    import torch
+    from venom_b200 import capi
+    from venom_b200.synth import random_dense_b, random_vnm_dense
+    M, K, V, m, N = 256, 1024, 128, 32, 512
+    dense, cols, _ = random_vnm_dense(M, K, V, m, seed=77)
+    B = random_dense_b(K, N, seed=78)
+    ov, om, _ = oracle.compress(dense, cols, V, m)
+    values = torch.from_numpy(ov).cuda()
+    meta = torch.from_numpy(om.view(np.int32)).cuda()
+    idx = torch.from_numpy(cols.view(np.int32)).cuda()
+    act = torch.from_numpy(np.ascontiguousarray(B.T)).cuda()          # [N, K]
+    spatha.clear_cache()
+    out = spatha.spmm(meta, idx, values, act.t(), None, M, K, N, V, 2, m, values.numel(), 0, 32, 4)
+    want = oracle.spmm(ov, om, cols, M, K, V, m, B, layout=1)
+    bad, first, worst = oracle.check(out.cpu().numpy(), want, mode=1, tol=1e-2)
+    assert bad == 0, (bad, first, worst)
+    auto = capi.Prepared(values, meta, idx, M, K, V, m)
+    forced = capi.Prepared(values, meta, idx, M, K, V, m, strategy=capi.STRATEGY_DENSE_B)
+    assert not auto.dense_b_form() and forced.dense_b_form()
+    assert torch.equal(forced.spmm_nk(act, layout=capi.VNM_LAYOUT_NM), out)

@@ -39,6 +39,8 @@ def lib():
         L.vnm_prune_magnitude_f32.argtypes = [C.c_void_p, C.c_int64] + [C.c_int] * 5 + [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p]
         L.vnm_prune_magnitude_f32.restype = C.c_int
         L.vnm_prepare.argtypes = [C.c_void_p] * 3 + [C.c_int] * 5 + [C.POINTER(C.c_void_p), C.c_void_p]
+        L.vnm_prepare_as.argtypes = [C.c_void_p] * 3 + [C.c_int] * 6 + [C.POINTER(C.c_void_p), C.c_void_p]
+        L.vnm_prepare_as.restype = C.c_int
         L.vnm_prepared_bytes.argtypes = [C.c_int] * 5 + [i64p]
         L.vnm_destroy.argtypes = [C.c_void_p]
         L.vnm_spmm_f16.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_void_p, C.c_void_p, C.c_int64,
@@ -142,7 +144,8 @@ def decompress(values, meta, colloc, M, K, V, m, n=2):
 class Prepared:
     """Owns a vnm_handle_t: the kernel-private copy of one sparse operand."""
 
-    def __init__(self, values, meta, colloc, M, K, V, m, n=2):
+    def __init__(self, values, meta, colloc, M, K, V, m, n=2, strategy=None):
+        """strategy: None = the process-wide setting (set_strategy), else STRATEGY_AUTO / _GATHER / _DENSE_B."""
         _need_cuda(values, meta, colloc)
         ksp, nv, nm, nc = sizes(M, K, V, m, n)
         if values.numel() != nv or meta.numel() != nm or colloc.numel() != nc:
@@ -152,8 +155,12 @@ class Prepared:
         self.M, self.K, self.V, self.m, self.n = M, K, V, m, n
         self.device = values.device
         self._h = C.c_void_p()
-        _check(lib().vnm_prepare(values.data_ptr(), meta.data_ptr(), colloc.data_ptr(), M, K, V, n, m,
-                                 C.byref(self._h), _stream()))
+        if strategy is None:
+            _check(lib().vnm_prepare(values.data_ptr(), meta.data_ptr(), colloc.data_ptr(), M, K, V, n, m,
+                                     C.byref(self._h), _stream()))
+        else:
+            _check(lib().vnm_prepare_as(values.data_ptr(), meta.data_ptr(), colloc.data_ptr(), M, K, V, n, m, int(strategy),
+                                        C.byref(self._h), _stream()))
 
     def close(self):
         if getattr(self, "_h", None) is not None and self._h.value:

@@ -73,8 +73,10 @@ torch::Tensor spmm(torch::Tensor A_metadata, torch::Tensor A_indices, torch::Ten
         std::lock_guard<std::mutex> lock(g_mutex);
         auto it = g_cache.find(key);
         if (it == g_cache.end()) {
-            check(vnm_prepare(A_values.data_ptr(), (const uint32_t *)A_metadata.data_ptr(), (const uint32_t *)A_indices.data_ptr(), M, K, V,
-                              (int)n, (int)m, &h, stream), "vnm_prepare");
+            // An activation that arrives as a transposed [tokens, features] view is read in place only by the dense-B
+            // form, and the transpose copy it saves costs more than the gather form gains at high sparsity.
+            check(vnm_prepare_as(A_values.data_ptr(), (const uint32_t *)A_metadata.data_ptr(), (const uint32_t *)A_indices.data_ptr(), M, K, V,
+                                 (int)n, (int)m, rhs_is_t_view ? VNM_STRATEGY_DENSE_B : VNM_STRATEGY_AUTO, &h, stream), "vnm_prepare_as");
             g_cache.emplace(key, h);
         } else {
             h = it->second;

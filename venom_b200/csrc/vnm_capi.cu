@@ -74,15 +74,15 @@ int g_strategy = 0;  // VNM_STRATEGY_*
 // Gather form vs dense-B form (see vnm_set_strategy in the header).  Measured on B200: the gather path is
 // bound by the TMA gather rate and pays NB = 128/V times for small vector lengths, the dense-B form costs
 // m/4 times the MMA work but shares B between all vector blocks.
-bool choose_dense_b(int K, int V, int m)
+bool choose_dense_b(int K, int V, int m, int strategy)
 {
     const bool possible = (m % 4 == 0) && (K % m == 0);
-    if (!possible || g_strategy == VNM_STRATEGY_GATHER) return false;
-    if (g_strategy == VNM_STRATEGY_DENSE_B) return true;
-    // measured on B200 (N = 16384): the dense-B kernel wins for every V at m <= 8, and at m = 16 only for
-    // V = 32 (where the gather kernel pays four masked MMAs per stage)
+    if (!possible || strategy == VNM_STRATEGY_GATHER) return false;
+    if (strategy == VNM_STRATEGY_DENSE_B) return true;
+    // measured on B200 (N = 16384): the dense-B kernel wins for every V at m <= 8, and at m = 16 for V <= 64
+    // (where the gather kernel gathers, and multiplies with masked MMAs, once per vector block of a row tile)
     if (m <= 8) return true;
-    return V == 32 && m <= 16;
+    return V <= 64 && m <= 16;
 }
 
 }  // namespace
@@ -182,7 +182,7 @@ int vnm_prepared_bytes(int M, int K, int V, int n, int m, int64_t *bytes)
     if (rc) return rc;
     if (V != 32 && V != 64 && V != 128) return fail(VNM_ERR_UNSUPPORTED, "SpMM supports V in {32, 64, 128} (got %d)", V);
     const int64_t Ksp = ksp_of(K, m);
-    const bool dense_b = choose_dense_b(K, V, m);
+    const bool dense_b = choose_dense_b(K, V, m, g_strategy);
     const int64_t mtiles = (M + TILE_M - 1) / TILE_M, ktiles = dense_b ? (K + 127) / 128 : (Ksp + KT_COMP - 1) / KT_COMP;
     const int64_t nb = dense_b ? 1 : TILE_M / V;
     if (bytes) *bytes = mtiles * ktiles * AM_BLOCK_BYTES + mtiles * nb * ktiles * KT_GROUPS * 16 + 256;
@@ -192,6 +192,14 @@ int vnm_prepared_bytes(int M, int K, int V, int n, int m, int64_t *bytes)
 int vnm_prepare(const void *values, const uint32_t *meta, const uint32_t *colloc, int M, int K, int V, int n, int m,
                 vnm_handle_t *handle, void *stream)
 {
+    return vnm_prepare_as(values, meta, colloc, M, K, V, n, m, g_strategy, handle, stream);
+}
+
+int vnm_prepare_as(const void *values, const uint32_t *meta, const uint32_t *colloc, int M, int K, int V, int n, int m, int strategy,
+                   vnm_handle_t *handle, void *stream)
+{
+    if (strategy != VNM_STRATEGY_AUTO && strategy != VNM_STRATEGY_GATHER && strategy != VNM_STRATEGY_DENSE_B)
+        return fail(VNM_ERR_BAD_ARG, "vnm_prepare_as: unknown strategy %d", strategy);
     int rc = check_format(M, K, V, n, m);
     if (rc) return rc;
     if (!values || !meta || !colloc || !handle) return fail(VNM_ERR_BAD_ARG, "vnm_prepare: null pointer");
@@ -208,7 +216,7 @@ int vnm_prepare(const void *values, const uint32_t *meta, const uint32_t *colloc
     h->M = M; h->K = K; h->V = V; h->n = n; h->m = m;
     h->Ksp = ksp_of(K, m);
     h->mtiles = (M + TILE_M - 1) / TILE_M;
-    h->dense_b = choose_dense_b(K, V, m) ? 1 : 0;
+    h->dense_b = choose_dense_b(K, V, m, strategy) ? 1 : 0;
     if (h->dense_b) {
         h->ktiles = (K + 127) / 128;  // a k-tile covers 128 original columns
         h->nb = 1;
