@@ -34,7 +34,7 @@ MS = [4, 8, 16, 32]
 N_COLS = 16384
 # dram__bytes_read.sum + dram__bytes_write.sum per launch (mean of the 36 launches of one step) from an ncu
 # capture of this workload; the summary with the full command is kept under profiles/.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 96.1e6
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 96.5e6
 METRIC = "vnm_spmm_useful_tflops"
 UNIT = "TFLOP/s (useful = 2*M*N*K*n/m)"
 
@@ -350,7 +350,7 @@ def main():
         # roofline is therefore stated against HBM: algorithmic bytes per launch / mean launch duration.
         achieved = bytes_step / nl / (kernel_ms / nl * 1e-3) / 1e9
         roofline = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
-                    "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "peak_source": peaks["source"], "kernel": "vnm::spmm_dense_b_kernel (63 % of the step) + vnm::spmm_kernel, mean of the 36 launches",
+                    "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "peak_source": peaks["source"], "kernel": "vnm::spmm_dense_b_kernel (72 % of the step) + vnm::spmm_kernel, mean of the 36 launches",
                     "algorithmic_bytes_per_launch": bytes_step / nl, "mean_launch_ms": kernel_ms / nl,
                     "tensor_frac_of_sustained_dense_peak": (flops_step / (kernel_ms * 1e-3) / 1e12) / peaks["tflops_sustained"],
                     "ideal_ms_per_step": {"hbm": t_hbm * 1e3, "tensor": t_tensor * 1e3}}
