@@ -149,3 +149,11 @@ def test_transposed_view_prepares_dense_b_form_at_high_sparsity(spatha, oracle):
     forced = capi.Prepared(values, meta, idx, M, K, V, m, strategy=capi.STRATEGY_DENSE_B)
     assert not auto.dense_b_form() and forced.dense_b_form()
     assert torch.equal(forced.spmm_nk(act, layout=capi.VNM_LAYOUT_NM), out)
+
+
+def test_gpt_block_harness_small(spatha):
+    """The decoder-block harness on a small shape: sparse and dense forwards run and print the reference's lines."""
+    from venom_b200 import e2e_gpt
+    d, s_ = e2e_gpt.main(["-m", "16", "-v", "128", "--layers", "1", "--hidden", "512", "--heads", "8", "--ffn", "2048", "--batch", "2",
+                          "--seq", "128", "--repeats", "2"])
+    assert d > 0 and s_ > 0

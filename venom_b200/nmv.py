@@ -79,12 +79,12 @@ class NMVectorSparsifier:
         device = tensor.device if device is None else device
         ksp, nv, nm, nc = vnm_sizes(nrows, ncols, self.tileM, self.m, self.n)
         columns = torch.zeros(nc, dtype=torch.int32).reshape(-1, 4) + torch.tensor([0, 1, 2, 3], dtype=torch.int32)
-        pattern = torch.zeros(self.m, dtype=torch.int32)
+        pattern = torch.zeros(self.m, dtype=torch.int32, device=tensor.device)  # built where the weight lives: GBs for large layers
         pattern[0] = 1
         pattern[2] = 1
         reps = -(-ncols // self.m)
         mask = pattern.repeat(reps)[:ncols].unsqueeze(0).expand(nrows, ncols).contiguous()
-        dense = tensor.detach().to(torch.float16) * mask.to(tensor.device, torch.float16)
+        dense = tensor.detach().to(torch.float16) * mask.to(torch.float16)
         return SrNMTensor(self.n, self.m, self.tileM, dense, mask, columns, device)
 
 
