@@ -14,7 +14,8 @@ import subprocess
 import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF = os.environ.get("VENOM_REFERENCE_DIR", "/root/reference")
+# the reference checkout: VENOM_REFERENCE_DIR, else a directory "reference" next to this repository
+REF = os.environ.get("VENOM_REFERENCE_DIR", os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference"))
 
 
 def _newer(target, sources):

@@ -16,7 +16,7 @@ import numpy as np
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, ROOT)
-REF = os.environ.get("VENOM_REFERENCE_DIR", "/root/reference")
+REF = os.environ.get("VENOM_REFERENCE_DIR", os.path.join(os.path.dirname(ROOT), "reference"))
 
 from oracle.oracle import Reference  # noqa: E402
 from venom_b200.synth import random_vnm_dense  # noqa: E402

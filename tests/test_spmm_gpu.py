@@ -164,7 +164,7 @@ def test_bad_arguments_raise(capi, oracle):
 
 @pytest.mark.parametrize("shape", [(1024, 4096, 64, 8, 4096), (1024, 1024, 128, 4, 16384), (4096, 1024, 32, 16, 2048)])
 def test_spmm_baseline_shapes_sampled_rows(capi, oracle, shape):
-    """BASELINE-sized shapes: a seeded sample of output rows is checked against the oracle, and the
+    """Headline-sized shapes: a seeded sample of output rows is checked against the oracle, and the
     whole result against linearity (A*(B1+B2) on exactly representable integer data)."""
     import torch
     M, K, V, m, N = shape
