@@ -145,6 +145,19 @@ def test_spmm_host_async_calls_overlap_and_match(capi, oracle):
         assert torch.equal(oh, prep.spmm(Bd).cpu())
 
 
+def test_serialised_weight_loads_and_multiplies(capi, oracle, tmp_path):
+    """A compressed weight written to a file and loaded back gives the same product bit for bit."""
+    import torch
+    from venom_b200 import serialize
+    M, K, V, m, N = 256, 512, 64, 8, 264
+    prep, Bd, (ov, om, cols, B) = _setup(capi, oracle, M, K, V, m, N, seed=321, ints=False)
+    path = tmp_path / "w.vnm"
+    path.write_bytes(serialize.dumps(ov, om, cols, M, K, V, m))
+    prep2, hdr = serialize.load_prepared(str(path))
+    assert (hdr["M"], hdr["K"], hdr["V"], hdr["m"]) == (M, K, V, m)
+    assert torch.equal(prep2.spmm(Bd), prep.spmm(Bd))
+
+
 def test_bad_arguments_raise(capi, oracle):
     import torch
     M, K, V, m, N = 128, 256, 128, 8, 64
