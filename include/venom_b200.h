@@ -150,6 +150,13 @@ int vnm_spmm_f16_noalloc(const void *values, const uint32_t *meta, const uint32_
  * up).  Synchronises `stream`. */
 int vnm_device_status(vnm_handle_t handle, int *status, void *stream);
 
+/* Self-test of the failure path, without a fault: launches a two-warp kernel that waits, through the same bounded
+ * wait as the product kernels (about two seconds), on a barrier that nothing signals.  The wait runs out, the
+ * kernel records a status bit in this handle's status word and returns normally; the next vnm_device_status
+ * reports VNM_ERR_DEVICE_TIMEOUT and clears the word, and the handle stays usable.  No counterpart in the
+ * reference (its kernels have no waits that can fail). */
+int vnm_selftest_wait_expiry(vnm_handle_t handle, void *stream);
+
 /* Ablation switches.
  * Gather mode: how the selected rows of B reach shared memory.  0 = TMA tile::gather4, one group of four
  * rows per instruction (default for m > 4); 1 = plain TMA tiles of 64 consecutive rows, which is exact

@@ -158,6 +158,21 @@ def test_serialised_weight_loads_and_multiplies(capi, oracle, tmp_path):
     assert torch.equal(prep2.spmm(Bd), prep.spmm(Bd))
 
 
+def test_bounded_wait_expiry_is_reported_and_the_handle_stays_usable(capi, oracle):
+    """Failure detection without a fault: a wait on a barrier that nothing signals runs out, the kernel returns,
+    the host reads the status, and the next product on the same handle is correct."""
+    import torch
+    M, K, V, m, N = 128, 512, 128, 8, 256
+    prep, Bd, (ov, om, cols, B) = _setup(capi, oracle, M, K, V, m, N, seed=9, ints=True)
+    before = prep.spmm(Bd)
+    assert prep.device_status() == 0
+    prep.selftest_wait_expiry()
+    with pytest.raises(capi.VenomError, match="bounded device-side wait"):
+        prep.device_status()
+    assert prep.device_status() == 0                       # reading the status cleared it
+    assert torch.equal(prep.spmm(Bd), before)              # the context and the handle are intact
+
+
 def test_bad_arguments_raise(capi, oracle):
     import torch
     M, K, V, m, N = 128, 256, 128, 8, 64

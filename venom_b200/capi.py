@@ -47,6 +47,8 @@ def lib():
                                    C.c_int, C.c_void_p]
         L.vnm_spmm_f16_host_async.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]
         L.vnm_spmm_f16_host_async.restype = C.c_int
+        L.vnm_selftest_wait_expiry.argtypes = [C.c_void_p, C.c_void_p]
+        L.vnm_selftest_wait_expiry.restype = C.c_int
         L.vnm_host_wait.argtypes = [C.c_void_p]
         L.vnm_host_wait.restype = C.c_int
         L.vnm_spmm_f16_nk.argtypes = L.vnm_spmm_f16.argtypes
@@ -222,6 +224,10 @@ class Prepared:
 
     def host_wait(self):
         _check(lib().vnm_host_wait(self._h))
+
+    def selftest_wait_expiry(self):
+        """Lets a bounded device-side wait run out on purpose (about two seconds); device_status() then raises."""
+        _check(lib().vnm_selftest_wait_expiry(self._h, _stream()))
 
     def device_status(self):
         st = C.c_int(0)

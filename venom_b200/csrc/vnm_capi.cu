@@ -556,6 +556,13 @@ int vnm_host_wait(vnm_handle_t h)
     return VNM_OK;
 }
 
+int vnm_selftest_wait_expiry(vnm_handle_t h, void *stream)
+{
+    if (!h) return fail(VNM_ERR_BAD_ARG, "vnm_selftest_wait_expiry: null handle");
+    VNM_CUDA(launch_wait_expiry_selftest(h->status, (cudaStream_t)stream), "self-test launch");
+    return VNM_OK;
+}
+
 int vnm_device_status(vnm_handle_t h, int *status, void *stream)
 {
     if (!h || !status) return fail(VNM_ERR_BAD_ARG, "vnm_device_status: null pointer");

@@ -72,6 +72,7 @@ cudaError_t launch_spmm(const SpmmConfig &cfg, const CUtensorMap &tmap_rows, con
 
 // Dense-B form: 256 x 128 tiles, two accumulators sharing every B stage (vnm_spmm_dense_b.cu).
 cudaError_t spmm_dense_b_init();
+cudaError_t launch_wait_expiry_selftest(int *status, cudaStream_t stream);
 void spmm_dense_b_config(int M, int N, SpmmConfig *cfg);
 cudaError_t launch_spmm_dense_b(const SpmmConfig &cfg, const CUtensorMap &tmap_tile, const CUtensorMap &tmap_tile2, const CUtensorMap &tmap_out,
                                 const SpmmParams &p, cudaStream_t stream);

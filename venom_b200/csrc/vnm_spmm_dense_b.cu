@@ -401,7 +401,30 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_kernel(const __gr
 
 int g_num_sms_db = 0;
 
+// Self-test of the bounded waits: two threads wait, through the same wait_one as the product kernels and with the
+// same limit, on a barrier that nothing ever signals.  The first to run out of time records its status bit and
+// raises the abort flag; the other sees the flag and leaves.  The kernel then returns normally.
+__global__ void wait_expiry_selftest_kernel(int *status)
+{
+    __shared__ uint64_t bar;
+    __shared__ int abort_word;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        abort_word = 0;
+        fence_barrier_init();
+    }
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) wait_one(&bar, 0u, &abort_word, status, DEV_TIMEOUT_EPILOGUE);
+    __syncthreads();
+}
+
 }  // namespace
+
+cudaError_t launch_wait_expiry_selftest(int *status, cudaStream_t stream)
+{
+    wait_expiry_selftest_kernel<<<1, 64, 0, stream>>>(status);
+    return cudaGetLastError();
+}
 
 cudaError_t spmm_dense_b_init()
 {
