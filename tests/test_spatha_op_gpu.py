@@ -88,6 +88,9 @@ def test_srnm_spmm_module_replaces_linear(spatha):
     "--m 1024 --k 4096 --n 4096 --bm 64 --mm_row 8",
     "--m 1024 --k 1024 --n 2048 --bm 128 --mm_row 4",
     "--m 512 --k 2000 --n 1024 --bm 32 --mm_row 20",
+    "--m 1024 --k 1024 --n 2048 --bm 128 --mm_row 8 --strategy gather",
+    "--m 1024 --k 1024 --n 2048 --bm 128 --mm_row 16 --strategy dense-b",
+    "--m 1024 --k 1024 --n 2048 --bm 128 --mm_row 4 --ablation ideal",
 ])
 def test_benchmark_spmm_cli_check(flags):
     exe = os.path.join(ROOT, "venom_b200", "benchmark_spmm")

@@ -57,7 +57,11 @@ static const char *kUsage =
     "Required: --sparsity-type n-to-m --spmm spatha --gemm cuBlas --precision half --m M --k K --n N --d D\n"
     "          --nn_row 2 --mm_row m --bm V [--meta-block-size 32] [--block-size 4]\n"
     "Accepted and echoed: --bn --bk --wm --wn --wk --mm --mn --mk --nstage --acc_t fp32\n"
-    "Optional: --random (time-based seed), --check (compare with cuBLAS on the decompressed matrix)\n";
+    "Optional: --random (time-based seed), --check (compare with cuBLAS on the decompressed matrix)\n"
+    "          --strategy auto|gather|dense-b   operand form (default auto: chosen per V and m)\n"
+    "          --ablation none|ideal|no-b      ideal: gather form without column-loc (plain row tiles of B, the\n"
+    "                                          reference's IDEAL_KERNEL build; results differ unless m = 4);\n"
+    "                                          no-b: no loads of B at all (timing floor of the pipeline)\n";
 
 int main(int argc, const char **argv)
 {
@@ -66,6 +70,7 @@ int main(int argc, const char **argv)
     float density = 0.f;
     unsigned seed = 2022;
     bool check = false;
+    int strategy = VNM_STRATEGY_AUTO, ablation = 0;
     for (int i = 1; i < argc; ++i) {
         auto is = [&](const char *f) { return !strcmp(argv[i], f); };
         const bool has = i != argc - 1;
@@ -92,6 +97,8 @@ int main(int argc, const char **argv)
         else if (is("--sparsity-type") && has) pattern_code = !strcmp(argv[i + 1], "n-to-m") ? 2 : -2;
         else if (is("--precision") && has) precision_code = !strcmp(argv[i + 1], "half") ? 1 : -2;
         else if (is("--check")) check = true;
+        else if (is("--strategy") && has) strategy = !strcmp(argv[i + 1], "gather") ? VNM_STRATEGY_GATHER : (!strcmp(argv[i + 1], "dense-b") ? VNM_STRATEGY_DENSE_B : VNM_STRATEGY_AUTO);
+        else if (is("--ablation") && has) ablation = !strcmp(argv[i + 1], "ideal") ? 1 : (!strcmp(argv[i + 1], "no-b") ? 2 : 0);
         else if (is("--random")) seed = (unsigned)std::chrono::system_clock::now().time_since_epoch().count();
     }
     if (m == 0 || n == 0 || k == 0 || density == 0.f) {
@@ -159,7 +166,9 @@ int main(int argc, const char **argv)
     CK(cudaMemset(dC, 0, (size_t)M * N * 2));
 
     vnm_handle_t h = nullptr;
-    VK(vnm_prepare(dval, dmeta, dcol, M, K, V, nn_row, mrow, &h, nullptr));
+    if (ablation == 1) strategy = VNM_STRATEGY_GATHER;  // "no column-loc" only means something for the gather form
+    VK(vnm_prepare_as(dval, dmeta, dcol, M, K, V, nn_row, mrow, strategy, &h, nullptr));
+    if (ablation) VK(vnm_set_gather_mode(h, ablation));
     VK(vnm_decompress_f16(dval, dmeta, dcol, M, K, V, nn_row, mrow, dAd, K, nullptr));  // to_dense() for the cuBLAS side
 
     const int TIMES = 100, WARM = 11;
