@@ -366,7 +366,7 @@ def main():
                        "launches_per_step": nl, "l2": "inputs larger than L2: one pass cycles through 320 MB of dense operands and outputs",
                        "parallelism": "N-sharded x%d (weak)" % world},
             "clocks": clocks.summary(),
-            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": d2h * world, "ms_per_step": e2e_ms},
             "gpu_launches": nl * args.steps,
             "roofline": roofline,
             "cpu_baseline": cpu,

@@ -279,7 +279,7 @@ cudaError_t launch_compress(const void *dense, int64_t ldd, const int32_t *mask,
 }
 
 // ------------------------------------------------------------------------------------------------
-// Decompressor (Format_sr_nm<T>::to_dense, format_sr_nm.cpp:327-417).  The output is zero-filled by
+// Decompressor, general form (Format_sr_nm<T>::to_dense, format_sr_nm.cpp:327-417).  The output is zero-filled by
 // the caller side of the launch; one thread scatters the two values of one (row, group), slot 0
 // first, so a padded slot overwrites exactly as the reference's loop order does.
 // ------------------------------------------------------------------------------------------------
@@ -303,10 +303,99 @@ __global__ void __launch_bounds__(256) decompress_kernel(const __half *__restric
     }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Tiled decompressor (the one normally used): the mirror image of compress_tiled_kernel.  A CTA takes 32 rows x
+// TS tiles: the values (TS * 256 contiguous bytes per 16 rows) and metadata (TS * 64 bytes) come in with 16-byte
+// loads, lane = row / warp = tile scatters the two values of every (row, group) into a zeroed shared-memory image
+// of the 32 dense row segments (slot 0 first, like the general kernel), and the image leaves with 8-byte stores.
+// Every output element is written exactly once, so no memset pass is needed.
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) decompress_tiled_kernel(const uint32_t *__restrict__ values, const uint32_t *__restrict__ meta,
+                                                               const uint32_t *__restrict__ colloc, int M, int K, int V, int m, int64_t Ksp, int TS,
+                                                               __half *__restrict__ dense, int64_t ldd)
+{
+    extern __shared__ __align__(16) uint8_t csm[];
+    const int span = TS * 4 * m;
+    const int pitch = span + 4;  // halves; rows 8-byte aligned, pitch / 2 = 2 mod 32
+    uint32_t *val_s = reinterpret_cast<uint32_t *>(csm);                 // [2][TS][64]
+    uint32_t *meta_s = val_s + 2 * TS * 64;                              // [TS][16]
+    unsigned short *out_s = reinterpret_cast<unsigned short *>(meta_s + TS * 16);  // [32][pitch]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t tiles = Ksp / 8;
+    const int spans = (int)((tiles + TS - 1) / TS);
+    const int64_t chunks = (int64_t)(M / 32) * spans;
+    for (int64_t ch = blockIdx.x; ch < chunks; ch += gridDim.x) {
+        const int64_t rc = ch / spans;
+        const int sp = (int)(ch - rc * spans);
+        const int64_t R0 = rc * 32;
+        const int64_t t0 = (int64_t)sp * TS;
+        const int tcount = (int)(tiles - t0 < TS ? tiles - t0 : TS);
+        const int64_t c0 = t0 * 4 * m;
+        const int valid = (int)(c0 >= K ? 0 : (K - c0 < span ? K - c0 : span));
+        // ---- compressed arrays -> shared memory, dense image zeroed
+        const int vq = tcount * 16;
+        for (int i = threadIdx.x; i < 2 * vq; i += 256) {
+            const int rg = i >= vq ? 1 : 0;
+            const int k = i - rg * vq;
+            reinterpret_cast<uint4 *>(val_s + rg * TS * 64)[k] = __ldg(reinterpret_cast<const uint4 *>(values + ((R0 / 16 + rg) * 16 * Ksp + t0 * 128) / 2) + k);
+        }
+        for (int i = threadIdx.x; i < tcount * 4; i += 256)
+            reinterpret_cast<uint4 *>(meta_s)[i] = __ldg(reinterpret_cast<const uint4 *>(meta + (R0 / 32) * 16 * tiles + t0 * 16) + i);
+        for (int i = threadIdx.x; i < 32 * pitch / 4; i += 256) reinterpret_cast<uint2 *>(out_s)[i] = make_uint2(0u, 0u);
+        __syncthreads();
+        // ---- lane = row, warp = tile
+        const uint32_t *crow = colloc + (R0 / V) * (Ksp / 2) * 4;
+        unsigned short *my_out = out_s + lane * pitch;
+        for (int tl = warp; tl < tcount; tl += 8) {
+            const uint32_t hw = (meta_s[tl * 16 + (lane >> 1)] >> ((lane & 1) * 16)) & 0xFFFFu;
+            const uint32_t *vsrc = val_s + ((lane >> 4) * TS + tl) * 64 + ((lane & 15) >> 2) * 16 + (lane & 3);
+            const uint4 *c4p = reinterpret_cast<const uint4 *>(crow + (t0 + tl) * 16);
+#pragma unroll
+            for (int gi = 0; gi < 4; gi++) {
+                const uint4 c4 = __ldg(c4p + gi);
+                const int cand[4] = {(int)c4.x, (int)c4.y, (int)c4.z, (int)c4.w};
+                const int lg = (tl * 4 + gi) * m;
+                const uint32_t two = vsrc[gi * 4];
+#pragma unroll
+                for (int sl = 0; sl < 2; sl++) {
+                    const int sel = (int)((hw >> (gi * 4 + sl * 2)) & 3u);
+                    const int lc = lg + (sel == 0 ? cand[0] : sel == 1 ? cand[1] : sel == 2 ? cand[2] : cand[3]);
+                    if (lc < valid) my_out[lc] = (unsigned short)(two >> (16 * sl));
+                }
+            }
+        }
+        __syncthreads();
+        // ---- dense image -> global memory
+        const int nq = valid / 4;  // whole 8-byte pieces per row
+        for (int r = warp; r < 32; r += 8) {
+            __half *drow = dense + (R0 + r) * ldd + c0;
+            const unsigned short *srow = out_s + r * pitch;
+            for (int q = lane; q < nq; q += 32) reinterpret_cast<uint2 *>(drow)[q] = reinterpret_cast<const uint2 *>(srow)[q];
+            for (int c = nq * 4 + lane; c < valid; c += 32) drow[c] = __ushort_as_half(srow[c]);
+        }
+        __syncthreads();
+    }
+}
+
 cudaError_t launch_decompress(const void *values, const uint32_t *meta, const uint32_t *colloc, int M, int K, int V, int m,
                               void *dense, int64_t ldd, cudaStream_t stream)
 {
     const int64_t Ksp = ksp_of(K, m);
+    const bool aligned = ldd % 4 == 0 && ((uintptr_t)dense & 7) == 0 && ((uintptr_t)values & 15) == 0 && ((uintptr_t)meta & 15) == 0 &&
+                         m <= 128 && M % 32 == 0 && V % 32 == 0;
+    if (aligned) {
+        const int TS = m >= 128 ? 1 : (m <= 8 ? 16 : 128 / m);
+        const int span = TS * 4 * m;
+        const size_t smem = (size_t)(2 * TS * 64 + TS * 16) * 4 + (size_t)32 * (span + 4) * 2;
+        const int64_t chunks = (int64_t)(M / 32) * ((Ksp / 8 + TS - 1) / TS);
+        int64_t blocks = chunks < (int64_t)148 * 5 ? chunks : (int64_t)148 * 5;
+        if (blocks < 1) blocks = 1;
+        cudaError_t e = cudaFuncSetAttribute(decompress_tiled_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+        if (e != cudaSuccess) return e;
+        decompress_tiled_kernel<<<(unsigned)blocks, 256, smem, stream>>>((const uint32_t *)values, meta, colloc, M, K, V, m, Ksp, TS,
+                                                                         (__half *)dense, ldd);
+        return cudaGetLastError();
+    }
     cudaError_t e = cudaMemset2DAsync(dense, (size_t)ldd * 2, 0, (size_t)K * 2, (size_t)M, stream);
     if (e != cudaSuccess) return e;
     const int64_t total = (int64_t)M * (Ksp / 2);

@@ -5,7 +5,7 @@
 // the widest N that leaves room for the metadata columns).  The mainloop runs at the rate at which an SM
 // takes in data from L2 (about 64 bytes per clock), so the tile is as large as tensor memory allows: per
 // k-tile (128 original columns of A = 128 rows of B) the CTA streams
-//     2 x 18 KiB value + metadata blocks   and   2 x 32 KiB stages of B (64 rows x 256 columns, 240 used)
+//     2 x 18 KiB value + metadata blocks   and   4 x 16 KiB stages of B (32 rows x 256 columns, 240 used)
 // = 100 KiB for eight 128 x 240 x 32 MMAs (152 clocks each), i.e. 53 KiB per 256 x 128 outputs.
 //
 // Warp roles (512 threads; the first two warpgroups give registers to the last two):
@@ -15,9 +15,9 @@
 //   warp 3      MMA issuer (one thread) and tensor-memory owner: per K=32 block one wait for its B stage, two
 //               MMAs (one per row tile) and one commit that frees the stage.
 //   warps 4..6  B producers (one thread each): stages are dealt round-robin; a stage is one 16 KiB TMA box (a 4-D
-//               map {64 columns, K rows, 4 slices of 64 columns, start column / 16} gives the [slice][row][64 columns]
-//               layout in one instruction; for B given as [N, K] a 2-D box of 256 rows x 32 k).  One thread issuing every TMA tile load keeps
-//               the copy engine about a third busy (measured); three do.
+//               map {64 columns, K rows, 4 slices of 64 columns, start column / 16} gives the [slice][row][64
+//               columns] layout in one instruction; for B given as [N, K] a 2-D box of 256 rows x 32 k).  One
+//               thread issuing every TMA tile load keeps the copy engine about a third busy (measured).
 //   warps 8..15 epilogue: four warps per accumulator read their rows into registers, hand the accumulator
 //               back, and store six parts of 40 columns through shared memory with one TMA store each.
 // Every wait is bounded: on expiry the kernel records a status bit, drains and returns.

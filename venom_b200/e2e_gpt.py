@@ -93,6 +93,8 @@ def main(argv=None):
     ap.add_argument("--repeats", type=int, default=5)
     ap.add_argument("--magnitude", action="store_true", help="prune by magnitude on the GPU instead of the fixed mask")
     ap.add_argument("--skip-dense", action="store_true")
+    ap.add_argument("--gather-every-layer", action="store_true",
+                    help="additionally all-gather the output of every linear (communication-bound variant; the gathered copies are discarded)")
     args = ap.parse_args(argv)
     if not torch.cuda.is_available():
         raise SystemExit("needs a CUDA device (there is no CPU path)")
@@ -108,13 +110,43 @@ def main(argv=None):
         raise SystemExit("batch must be a multiple of the number of ranks")
     torch.set_grad_enabled(False)
     torch.manual_seed(0)                       # the same weights on every rank
-    block = build_block(args.layers, args.hidden, args.heads, args.ffn).half().cuda()
+    # built on the GPU in fp16 straight away: on the host the fp32 copy would take 29 GB and minutes per rank
+    prev = torch.get_default_dtype()
+    torch.set_default_dtype(torch.float16)
+    try:
+        with torch.device("cuda"):
+            block = build_block(args.layers, args.hidden, args.heads, args.ffn)
+    finally:
+        torch.set_default_dtype(prev)
     g = torch.Generator(device="cuda")
     g.manual_seed(1)
     x_all = torch.randn((args.batch, args.seq, args.hidden), device="cuda", generator=g).half()
     per = args.batch // world
     x = x_all[rank * per:(rank + 1) * per].contiguous()
     gathered = torch.empty_like(x_all) if world > 1 else None
+
+    hooks = []
+
+    def install_gather_hooks():
+        # the replicated copy of every linear's output, as a caller that does not shard the following op would need it
+        bufs = {}
+
+        def hook(mod, inp, out):
+            flat = out.reshape(-1, out.shape[-1])
+            key = flat.shape
+            if key not in bufs:
+                bufs[key] = torch.empty((flat.shape[0] * world, flat.shape[1]), dtype=flat.dtype, device=flat.device)
+            dist.all_gather_into_tensor(bufs[key], flat.contiguous())
+        for h in hooks:
+            h.remove()
+        hooks.clear()
+        for layer in block:
+            for child in layer.children():
+                if hasattr(child, "nrows_sp") or isinstance(child, torch.nn.Linear):
+                    hooks.append(child.register_forward_hook(hook))
+
+    if args.gather_every_layer and world > 1:
+        install_gather_hooks()
 
     def step():
         y = block(x)
@@ -134,6 +166,8 @@ def main(argv=None):
         d_ms = max_over_ranks(time_forward(step, args.repeats))
     replaced = sparsify(block, args.n, args.m, args.v, args.magnitude)
     torch.cuda.empty_cache()
+    if args.gather_every_layer and world > 1:
+        install_gather_hooks()
     s_ms = max_over_ranks(time_forward(step, args.repeats))
     if rank == 0:
         def line(tag, ms):
@@ -143,8 +177,9 @@ def main(argv=None):
         if d_ms:
             line("0,0,", d_ms)
         line("%d,%d," % (args.n, args.m), s_ms)
-        msg = "# %d GPUs, %d linears replaced (%s mask); %d:%d:%d %.0f tokens/s" % (
-            world, replaced, "magnitude" if args.magnitude else "fixed", args.v, args.n, args.m, tokens / statistics.median(s_ms) * 1e3)
+        msg = "# %d GPUs%s, %d linears replaced (%s mask); %d:%d:%d %.0f tokens/s" % (
+            world, ", all-gather after every linear" if args.gather_every_layer and world > 1 else "", replaced,
+            "magnitude" if args.magnitude else "fixed", args.v, args.n, args.m, tokens / statistics.median(s_ms) * 1e3)
         if d_ms:
             msg += "; dense %.0f tokens/s, speed-up %.2fx" % (tokens / statistics.median(d_ms) * 1e3, statistics.median(d_ms) / statistics.median(s_ms))
         print(msg)
