@@ -60,7 +60,9 @@ struct Traits {
     static constexpr int A_RING_BYTES = SA * AM_BLOCK_BYTES;
     static constexpr int B_RING_BYTES = SB * B_STAGE_BYTES;
     static constexpr int BAR_BYTES = 256;
-    static constexpr int SMEM_BYTES = A_RING_BYTES + B_RING_BYTES + BAR_BYTES + 1024;  // + alignment slack
+    static constexpr int OUT_STAGE_BYTES = 4 * 32 * 64;  // per epilogue warp: 32 rows x 32 fp16 columns
+    static constexpr int SMEM_BYTES = A_RING_BYTES + B_RING_BYTES + BAR_BYTES + OUT_STAGE_BYTES + 1024;  // + alignment slack
+    static_assert(SMEM_BYTES <= 227 * 1024, "shared memory per CTA");
     static constexpr int SEQ_WARP = 1 + PB;      // sequencer: waits for the operands of a k-tile, copies its metadata
     static constexpr int MMA_WARP = 2 + PB;      // MMA issuer (and tensor-memory owner)
     static constexpr int NUM_WARPS = 3 + PB + 4;
@@ -137,6 +139,7 @@ __global__ void __launch_bounds__(Traits<BN, NB, SA, SB, PB>::NUM_THREADS, 1)
     uint8_t *a_ring = smem;
     uint8_t *b_ring = smem + T::A_RING_BYTES;
     uint64_t *a_full = reinterpret_cast<uint64_t *>(smem + T::A_RING_BYTES + T::B_RING_BYTES);
+    uint8_t *out_stage = smem + T::A_RING_BYTES + T::B_RING_BYTES + T::BAR_BYTES;
     uint64_t *a_empty = a_full + SA;
     uint64_t *b_full = a_empty + SA;
     uint64_t *b_empty = b_full + SB;
@@ -388,12 +391,7 @@ __global__ void __launch_bounds__(Traits<BN, NB, SA, SB, PB>::NUM_THREADS, 1)
                 if (row_ok) {
                     const int nbase = n0 + part * PART;
                     if (p.layout == 0) {
-                        __half *dst = p.out + row * p.ldo + nbase;
-#pragma unroll
-                        for (int jj = 0; jj < PART / 8; jj++) {
-                            if (nbase + jj * 8 + 8 <= p.N)
-                                *reinterpret_cast<uint4 *>(dst + jj * 8) = make_uint4(pk[4 * jj], pk[4 * jj + 1], pk[4 * jj + 2], pk[4 * jj + 3]);
-                        }
+                        // handled below, by the whole warp
                     } else {
                         __half *dst = p.out + (int64_t)nbase * p.ldo + row;
                         const int64_t step = p.ldo;
@@ -407,6 +405,33 @@ __global__ void __launch_bounds__(Traits<BN, NB, SA, SB, PB>::NUM_THREADS, 1)
                             if (nbase + 2 * jj + 1 < p.N) *dst = hi;
                             dst += step;
                         }
+                    }
+                }
+                if (p.layout == 0) {
+                    // [M,N]: a lane holds 64 columns of ONE row, so a 16-byte store per lane would touch 32 rows with half
+                    // a sector each.  The warp's 32 rows x 32 columns go through its own 2 KiB of shared memory instead
+                    // (16-byte pieces XOR-swizzled, conflict-free both ways) and leave as full sectors: four lanes per row,
+                    // eight rows per store instruction.
+                    uint8_t *stg = out_stage + q * (32 * 64);
+                    const int slot = arow - q * 32;  // this lane's row inside the warp's 32 rows (actual order)
+                    const int nbase = n0 + part * PART;
+#pragma unroll
+                    for (int half = 0; half < 2; half++) {
+#pragma unroll
+                        for (int c = 0; c < 4; c++)
+                            *reinterpret_cast<uint4 *>(stg + slot * 64 + ((c ^ ((slot >> 1) & 3)) << 4)) =
+                                make_uint4(pk[half * 16 + 4 * c], pk[half * 16 + 4 * c + 1], pk[half * 16 + 4 * c + 2], pk[half * 16 + 4 * c + 3]);
+                        __syncwarp();
+                        const int c = lane & 3;
+                        const int col = nbase + half * 32 + c * 8;
+#pragma unroll
+                        for (int rr = 0; rr < 4; rr++) {
+                            const int r = (lane >> 2) + 8 * rr;
+                            const int64_t grow = (int64_t)mt * TILE_M + q * 32 + r;
+                            const uint4 v = *reinterpret_cast<const uint4 *>(stg + r * 64 + ((c ^ ((r >> 1) & 3)) << 4));
+                            if (grow < p.M && col + 8 <= p.N) *reinterpret_cast<uint4 *>(p.out + grow * p.ldo + col) = v;
+                        }
+                        __syncwarp();
                     }
                 }
             }
