@@ -21,8 +21,12 @@
 //   warp PB+2         tensor-memory allocation and MMA issue: one wait, 4 * NB tcgen05.mma.sp and one
 //                     tcgen05.commit per k-tile; for NB > 1 each MMA runs on all 128 rows of the value
 //                     tile with the output lanes of the other blocks disabled.
-//   last four warps   epilogue: tcgen05.ld -> packed fp16 registers, release the accumulator, store
-//                     ([M,N], or [N,M] with fused bias).
+//   last eight warps  epilogue, two warps per tensor-memory lane quadrant, each draining half of the columns:
+//                     tcgen05.ld -> packed fp16 registers, release the accumulator, store.  For [M,N] a warp's
+//                     32 rows x 32 columns go through 2 KiB of its own shared memory so that every store
+//                     instruction writes full sectors of eight rows; [N,M] with fused bias stores 2-byte elements.
+//                     With few k-tiles per tile (high sparsity) the kernel is bound by this part: four warps
+//                     storing 16 bytes per lane into 32 different rows took 1.3x longer.
 // Producers run ahead into the next tile while the epilogue drains.  Every wait is bounded: on expiry
 // the kernel records a status bit, drains and returns.
 #include "vnm_internal.h"
@@ -60,12 +64,13 @@ struct Traits {
     static constexpr int A_RING_BYTES = SA * AM_BLOCK_BYTES;
     static constexpr int B_RING_BYTES = SB * B_STAGE_BYTES;
     static constexpr int BAR_BYTES = 256;
-    static constexpr int OUT_STAGE_BYTES = 4 * 32 * 64;  // per epilogue warp: 32 rows x 32 fp16 columns
+    static constexpr int EPI_WARPS = 8;  // two per tensor-memory lane quadrant, each draining half of the columns
+    static constexpr int OUT_STAGE_BYTES = EPI_WARPS * 32 * 64;  // per epilogue warp: 32 rows x 32 fp16 columns
     static constexpr int SMEM_BYTES = A_RING_BYTES + B_RING_BYTES + BAR_BYTES + OUT_STAGE_BYTES + 1024;  // + alignment slack
     static_assert(SMEM_BYTES <= 227 * 1024, "shared memory per CTA");
     static constexpr int SEQ_WARP = 1 + PB;      // sequencer: waits for the operands of a k-tile, copies its metadata
     static constexpr int MMA_WARP = 2 + PB;      // MMA issuer (and tensor-memory owner)
-    static constexpr int NUM_WARPS = 3 + PB + 4;
+    static constexpr int NUM_WARPS = 3 + PB + EPI_WARPS;
     static constexpr int NUM_THREADS = NUM_WARPS * 32;
     static constexpr int SR = 4;                 // "k-tile ready" barriers (sequencer -> MMA issuer)
     static_assert((2 * (SA + SB) + 8) * 8 + 32 <= BAR_BYTES - 16, "barrier area too small");
@@ -161,7 +166,7 @@ __global__ void __launch_bounds__(Traits<BN, NB, SA, SB, PB>::NUM_THREADS, 1)
         for (int s = 0; s < T::SP; s++) mbar_init(&kdone[s], 1);
         for (int s = 0; s < T::SR; s++) mbar_init(&kready[s], 2);  // metadata copy done + operands landed
         mbar_init(acc_full_bar, 1);
-        mbar_init(acc_empty_bar, 4);
+        mbar_init(acc_empty_bar, T::EPI_WARPS);
         *abort_flag = 0;
         fence_barrier_init();
     }
@@ -349,6 +354,7 @@ __global__ void __launch_bounds__(Traits<BN, NB, SA, SB, PB>::NUM_THREADS, 1)
     } else {
         // ---------------- epilogue ----------------
         const int q = warp & 3;  // tensor-memory lane quadrant this warp may read
+        const int ew = warp - (3 + PB);  // 0..7: warps 0..3 drain the first half of the columns, 4..7 the second
         const int i = q * 32 + lane;
         const int arow = mma_row_to_actual(i);
         int ti = 0;
@@ -365,8 +371,17 @@ __global__ void __launch_bounds__(Traits<BN, NB, SA, SB, PB>::NUM_THREADS, 1)
             const bool row_ok = row < p.M;
             const bool has_bias = p.layout == 1 && p.bias != nullptr;
             const __half bias = (has_bias && row_ok) ? p.bias[row] : __ushort_as_half((unsigned short)0);
+            constexpr int PARTS = BN / PART;
+            constexpr int PER_GROUP = PARTS >= 2 ? PARTS / 2 : 1;  // parts per group of four warps
+            const int part0 = (ew >> 2) * PER_GROUP;
+            if (PARTS < 2 && ew >= 4) {  // a single part: the second group has nothing to read
+                __syncwarp();
+                if (lane == 0) mbar_arrive(acc_empty_bar);
+                continue;
+            }
 #pragma unroll
-            for (int part = 0; part < BN / PART; part++) {
+            for (int pi = 0; pi < PER_GROUP; pi++) {
+                const int part = part0 + pi;
                 uint32_t pk[PART / 2];  // packed fp16 pairs: pk[c] = columns 2c, 2c+1 of this part
                 {
                     uint32_t v0[32], v1[32];  // both loads in flight before the single wait
@@ -382,7 +397,7 @@ __global__ void __launch_bounds__(Traits<BN, NB, SA, SB, PB>::NUM_THREADS, 1)
                         pk[16 + jj] = *reinterpret_cast<uint32_t *>(&h1);
                     }
                 }
-                if (part == BN / PART - 1) {
+                if (pi == PER_GROUP - 1) {
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(acc_empty_bar);
@@ -412,7 +427,7 @@ __global__ void __launch_bounds__(Traits<BN, NB, SA, SB, PB>::NUM_THREADS, 1)
                     // a sector each.  The warp's 32 rows x 32 columns go through its own 2 KiB of shared memory instead
                     // (16-byte pieces XOR-swizzled, conflict-free both ways) and leave as full sectors: four lanes per row,
                     // eight rows per store instruction.
-                    uint8_t *stg = out_stage + q * (32 * 64);
+                    uint8_t *stg = out_stage + ew * (32 * 64);
                     const int slot = arow - q * 32;  // this lane's row inside the warp's 32 rows (actual order)
                     const int nbase = n0 + part * PART;
 #pragma unroll
@@ -465,7 +480,7 @@ cudaError_t launch_one(const SpmmConfig &cfg, const CUtensorMap &tmap_rows, cons
 
 int g_num_sms = 0;
 
-constexpr int kSA = 3, kSB = 5;
+constexpr int kSA = 3, kSB = 4;
 
 }  // namespace
 
@@ -477,7 +492,7 @@ bool spmm_select_config(int V, int N, int M, int producer_warps, SpmmConfig *cfg
     const int mtiles = (M + TILE_M - 1) / TILE_M;
     const int pb = (producer_warps == 4) ? 4 : 8;
     cfg->stages = pb;
-    cfg->threads = (3 + pb + 4) * 32;
+    cfg->threads = (3 + pb + 8) * 32;
     if (V == 128) {
         cfg->bn = 256; cfg->nb = 1;
     } else if (V == 64) {
