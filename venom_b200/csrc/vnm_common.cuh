@@ -129,14 +129,6 @@ __device__ __forceinline__ void tma_load_2d(void *smem_dst, const void *tmap, in
                  "l"(tmap), "r"(col), "r"(row), "r"(smem_u32(bar))
                  : "memory");
 }
-// TMA tile load of a 3-D box at (c0, c1, c2), c0 innermost.
-__device__ __forceinline__ void tma_load_3d(void *smem_dst, const void *tmap, int c0, int c1, int c2, uint64_t *bar)
-{
-    asm volatile("cp.async.bulk.tensor.3d.shared::cta.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(
-                     smem_u32(smem_dst)),
-                 "l"(tmap), "r"(c0), "r"(c1), "r"(c2), "r"(smem_u32(bar))
-                 : "memory");
-}
 // TMA tile load of a 4-D box at (c0, c1, c2, c3), c0 innermost.
 __device__ __forceinline__ void tma_load_4d(void *smem_dst, const void *tmap, int c0, int c1, int c2, int c3, uint64_t *bar)
 {
@@ -171,16 +163,6 @@ __device__ __forceinline__ bool named_barrier_and(uint32_t id, uint32_t threads,
         : "memory");
     return r != 0;
 }
-// 16-byte asynchronous copy global -> shared; src_bytes < 16 zero-fills the remainder (0 = all zeros).
-__device__ __forceinline__ void cp_async_16(uint32_t saddr, const void *gsrc, uint32_t src_bytes)
-{
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(saddr), "l"(gsrc), "r"(src_bytes) : "memory");
-}
-// 4-byte asynchronous copy global -> shared (any 4-byte aligned destination), grouped with commit / wait.
-__device__ __forceinline__ void cp_async_4(uint32_t saddr, const void *gsrc)
-{
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(saddr), "l"(gsrc) : "memory");
-}
 __device__ __forceinline__ void cp_async_8(uint32_t saddr, const void *gsrc)
 {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(saddr), "l"(gsrc) : "memory");
@@ -190,12 +172,6 @@ template <int kPending>
 __device__ __forceinline__ void cp_async_wait()
 {
     asm volatile("cp.async.wait_group %0;" ::"n"(kPending) : "memory");
-}
-// The barrier receives one arrival from this thread once all its earlier cp.async copies have landed
-// (the arrival must be part of the barrier's expected count).
-__device__ __forceinline__ void cp_async_mbar_arrive_noinc(uint64_t *bar)
-{
-    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 // Register re-allocation between warpgroups (all four warps of a warpgroup must execute the same one).
 template <int kRegs>
@@ -262,16 +238,6 @@ __device__ __forceinline__ void tc_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[3
           "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
           "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
           "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr)
-        : "memory");
-}
-__device__ __forceinline__ void tc_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)[16])
-{
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
-          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
         : "r"(taddr)
         : "memory");
 }
