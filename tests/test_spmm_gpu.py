@@ -229,7 +229,9 @@ def test_gather_modes_agree_when_every_row_is_selected(capi, oracle):
 
 
 @pytest.mark.parametrize("shape", [(128, 512, 128, 4, 256), (256, 1024, 128, 8, 512), (192, 768, 64, 8, 200), (128, 1024, 32, 16, 64),
-                                   (96, 512, 32, 32, 72), (256, 2048, 64, 16, 384)])
+                                   (96, 512, 32, 32, 72), (256, 2048, 64, 16, 384),
+                                   (128, 1000, 64, 8, 520),      # K ends inside a 128-column k-tile; N ends inside the third column tile
+                                   (384, 200, 128, 4, 1024)])    # three row tiles (odd), one short k-tile
 @pytest.mark.parametrize("strategy", ["gather", "dense_b"])
 def test_both_operand_forms_match_oracle(capi, oracle, shape, strategy):
     """The V:N:M gather form and the dense-B form (2:4 over all K columns) are interchangeable."""
@@ -253,7 +255,7 @@ def test_both_operand_forms_match_oracle(capi, oracle, shape, strategy):
         capi.set_strategy(capi.STRATEGY_AUTO)
 
 
-@pytest.mark.parametrize("shape", [(256, 1024, 64, 8, 384), (384, 512, 128, 4, 200), (128, 2048, 32, 16, 72)])
+@pytest.mark.parametrize("shape", [(256, 1024, 64, 8, 384), (384, 512, 128, 4, 200), (128, 2048, 32, 16, 72), (128, 1000, 64, 8, 520)])
 def test_transposed_dense_operand_and_tma_store_layouts(capi, oracle, shape):
     """Dense-B form: B given as [N,K] (no transpose copy) must equal the [K,N] call, in both output layouts."""
     import torch

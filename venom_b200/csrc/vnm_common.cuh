@@ -163,6 +163,7 @@ __device__ __forceinline__ bool named_barrier_and(uint32_t id, uint32_t threads,
         : "memory");
     return r != 0;
 }
+// 8-byte asynchronous copy global -> shared (8-byte aligned on both sides), grouped with commit / wait.
 __device__ __forceinline__ void cp_async_8(uint32_t saddr, const void *gsrc)
 {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(saddr), "l"(gsrc) : "memory");
