@@ -94,7 +94,8 @@ int vnm_destroy(vnm_handle_t handle);
  * spmm_cuda, end2end/spatha_mod/block_sparse/spmm/blockwise_library.cu:294-386 (layout NM + bias).
  *   B    fp16 [K, N] row-major, leading dimension ldb (ldb % 8 == 0, 16-byte aligned base)
  *   bias fp16 [M] or NULL (layout NM only)
- *   out  fp16, leading dimension ldo (ldo % 8 == 0 for layout MN), 16-byte aligned base
+ *   out  fp16, leading dimension ldo, 16-byte aligned base; ldo % 8 == 0 for layout MN, and for layout NM too when
+ *        the operand is held in dense-B form (its epilogue writes with TMA stores)
  * N must be a multiple of 8. */
 int vnm_spmm_f16(vnm_handle_t handle, const void *B, int64_t ldb, int N,
                  const void *bias, void *out, int64_t ldo, int layout, void *stream);
@@ -107,9 +108,11 @@ int vnm_spmm_f16_nk(vnm_handle_t handle, const void *Bt, int64_t ldbt, int N,
                     const void *bias, void *out, int64_t ldo, int layout, void *stream);
 int vnm_operand_form(vnm_handle_t handle, int *dense_b);
 
-/* Same product with HOST buffers: copies B (and bias) to the device, runs vnm_spmm_f16 and copies the
- * result back, all on `stream`, then synchronises it.  Device staging buffers are owned by the handle
- * and grown on demand.  B_host [K, N] and out_host are dense row-major ([M,N] or [N,M]). */
+/* Same product with HOST buffers: B (and bias) go up, the product runs on `stream`, the result comes back, and
+ * the call returns after synchronising.  The columns are cut into up to eight slices so that the upload of one
+ * slice, the product of the previous and the download of the one before run at the same time (two copy streams
+ * per device, shared by all handles).  Device staging buffers are owned by the handle and grown on demand.
+ * B_host [K, N] and out_host are dense row-major ([M,N] or [N,M]); pinned memory gives the overlap. */
 int vnm_spmm_f16_host(vnm_handle_t handle, const void *B_host, int N, const void *bias_host,
                       void *out_host, int layout, void *stream);
 
