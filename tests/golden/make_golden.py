@@ -66,7 +66,10 @@ def main():
     np.savez_compressed(os.path.join(HERE, "format_golden.npz"), **out)
 
     sys.path.insert(0, os.path.join(REF, "end2end"))
+    import tempfile
     import torch
+    # the reference pruner JIT-compiles its embedded C++ into ./.compile_cache: keep that out of this repository
+    os.chdir(tempfile.mkdtemp(prefix="vnm_golden_"))
     import grouped_nmv_tensor as G
     out = {}
     for i, (M, K, V, m, quant) in enumerate(PRUNE_CASES):
