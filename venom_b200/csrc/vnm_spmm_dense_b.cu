@@ -36,7 +36,8 @@ constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;  // ~2 s at B200 clocks
 #define TRACE(slot, idx) do { } while (0)
 #endif
 
-constexpr int RT = 2;            // row tiles per CTA tile
+constexpr int RT = 2;            // row tiles per CTA tile the shared-memory and tensor-memory plans are sized for; the kernel
+                                 // template runs with R = 2, or R = 1 when the problem has too few tiles to fill the GPU otherwise
 constexpr int BN = 240;          // output columns per CTA tile
 constexpr int PART = 40;         // columns per epilogue part / TMA store
 constexpr int SA = 3;            // A ring: k-tiles (each RT blocks)
@@ -100,6 +101,7 @@ __device__ __forceinline__ void drain_slot(uint64_t *bar, uint32_t parity, int *
     atomicOr(status, DEV_TIMEOUT_DRAIN);
 }
 
+template <int R>
 __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_kernel(const __grid_constant__ CUtensorMap tmap_tile, const __grid_constant__ CUtensorMap tmap_tile2,
                                                                       const __grid_constant__ CUtensorMap tmap_out,
                                                                       const SpmmParams p)
@@ -121,7 +123,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_kernel(const __gr
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     // tiles: pairs of row tiles (fastest) x column tiles
-    const int mpairs = (p.mtiles + RT - 1) / RT;
+    static_assert(R == 1 || R == RT, "row tiles per CTA tile");
+    const int mpairs = (p.mtiles + R - 1) / R;
     const int total_tiles = mpairs * p.ntiles;
     const int my_tiles = ((int)blockIdx.x < total_tiles) ? (total_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
     const int total_it = my_tiles * p.ktiles;
@@ -132,7 +135,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_kernel(const __gr
         for (int s = 0; s < SF; s++) mbar_init(&b_free[s], 1);
         for (int s = 0; s < SR; s++) mbar_init(&kready[s], 1);  // A block landed and its metadata copied to tensor memory
         mbar_init(acc_full_bar, 1);
-        mbar_init(acc_empty_bar, 4 * RT);
+        mbar_init(acc_empty_bar, 4 * R);
         *abort_flag = 0;
         fence_barrier_init();
     }
@@ -162,11 +165,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_kernel(const __gr
                         if (!wait_one(&b_free[jd % SF], (uint32_t)(jd / SF) & 1u, abort_flag, p.status, DEV_TIMEOUT_PRODUCER)) { alive = false; break; }
                     }
                     TRACE(0, it);
-                    mbar_arrive_expect_tx(&a_full[s], A_STAGE_BYTES);
+                    mbar_arrive_expect_tx(&a_full[s], R * AM_BLOCK_BYTES);
 #pragma unroll
-                    for (int rt = 0; rt < RT; rt++) {
+                    for (int rt = 0; rt < R; rt++) {
                         // a missing second row tile (odd number of row tiles) re-reads the first one; its rows are never stored
-                        const int mt = (mp * RT + rt < p.mtiles) ? mp * RT + rt : mp * RT;
+                        const int mt = (mp * R + rt < p.mtiles) ? mp * R + rt : mp * R;
                         bulk_g2s(a_ring + s * A_STAGE_BYTES + rt * AM_BLOCK_BYTES, p.am + ((size_t)mt * p.ktiles + kt) * AM_BLOCK_BYTES, AM_BLOCK_BYTES,
                                  &a_full[s]);
                     }
@@ -238,7 +241,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_kernel(const __gr
                 tc_fence_after();
                 const uint32_t mcol = tmem_base + meta_col(it % META_SETS);
 #pragma unroll
-                for (int rt = 0; rt < RT; rt++)
+                for (int rt = 0; rt < R; rt++)
                     tc_cp_128x128b(mcol + rt * 4, mdesc0 + ((uint32_t)(sa * A_STAGE_BYTES + rt * AM_BLOCK_BYTES) >> 4));
                 tc_commit(&kready[it % SR]);
             }
@@ -278,7 +281,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_kernel(const __gr
                         TRACE(4, j);
                         const uint32_t boff = (uint32_t)((j % SB) * B_STAGE_BYTES) >> 4;
 #pragma unroll
-                        for (int rt = 0; rt < RT; rt++)
+                        for (int rt = 0; rt < R; rt++)
                             tc_mma_sp_f16(tmem_base + acc_col(rt), adesc0 + aoff + (uint32_t)((rt * AM_BLOCK_BYTES + kb * 32) >> 4), bdesc0 + boff,
                                           mcol + rt * 4 + (uint32_t)(kb & ~1), idesc0 | (uint32_t)(kb & 1), (kt | kb) != 0 ? 1u : 0u, 0u, 0u, 0u, 0u);
                         tc_commit(&b_free[j % SF]);  // the stage (and, after the fourth, the A blocks and metadata set) may be refilled
@@ -299,7 +302,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_kernel(const __gr
         const int i = q * 32 + lane;
         const int arow = mma_row_to_actual(i);
         int ti = 0;
-        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++ti) {
+        // with one row tile per CTA tile the second group of four warps has no accumulator to drain
+        for (int tile = ((warp - EPI_WARP0) >> 2) < R ? (int)blockIdx.x : total_tiles; tile < total_tiles; tile += gridDim.x, ++ti) {
             const int mp = tile % mpairs;
             const int n0 = (tile / mpairs) * BN;
             // the four warps of a group leave the loop together (they meet at named barriers below)
@@ -309,7 +313,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_kernel(const __gr
             if (warp == EPI_WARP0 && lane == 0) TRACE(6, ti * 3);
             {
                 const int rt = (warp - EPI_WARP0) >> 2;  // which accumulator this warp drains
-                const int mt = mp * RT + rt;
+                const int mt = mp * R + rt;
                 const int64_t row = (int64_t)mt * TILE_M + arow;
                 const bool row_ok = mt < p.mtiles && row < p.M;
                 const bool has_bias = p.layout == 1 && p.bias != nullptr;
@@ -428,8 +432,9 @@ cudaError_t launch_wait_expiry_selftest(int *status, cudaStream_t stream)
 
 cudaError_t spmm_dense_b_init()
 {
-    cudaError_t e = cudaFuncSetAttribute(spmm_dense_b_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(spmm_dense_b_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     if (e != cudaSuccess) return e;
+    if ((e = cudaFuncSetAttribute(spmm_dense_b_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES)) != cudaSuccess) return e;
     int dev = 0;
     if ((e = cudaGetDevice(&dev)) != cudaSuccess) return e;
     return cudaDeviceGetAttribute(&g_num_sms_db, cudaDevAttrMultiProcessorCount, dev);
@@ -438,10 +443,16 @@ cudaError_t spmm_dense_b_init()
 void spmm_dense_b_config(int M, int N, SpmmConfig *cfg)
 {
     const int mtiles = (M + TILE_M - 1) / TILE_M;
-    const long long tiles = (long long)((mtiles + RT - 1) / RT) * ((N + BN - 1) / BN);
+    const long long ntiles = (N + BN - 1) / BN;
     const int sms = g_num_sms_db > 0 ? g_num_sms_db : 148;
+    // Two row tiles per CTA tile take in 100 KiB per k-tile (about 1900 clocks), one takes in 82 KiB (about 1400) for
+    // half the outputs: the single form only pays when the double form would leave most of the GPU idle.
+    const long long t2 = (long long)((mtiles + 1) / 2) * ntiles, t1 = (long long)mtiles * ntiles;
+    const long long cost2 = ((t2 + sms - 1) / sms) * 1900, cost1 = ((t1 + sms - 1) / sms) * 1400;
+    const int rt = (mtiles >= 2 && cost1 < cost2) ? 1 : 2;
+    const long long tiles = rt == 2 ? t2 : t1;
     cfg->bn = BN;
-    cfg->nb = 1;
+    cfg->nb = rt;  // row tiles per CTA tile
     cfg->stages = 1;
     cfg->smem_bytes = SMEM_BYTES;
     cfg->threads = NUM_THREADS;
@@ -451,7 +462,10 @@ void spmm_dense_b_config(int M, int N, SpmmConfig *cfg)
 cudaError_t launch_spmm_dense_b(const SpmmConfig &cfg, const CUtensorMap &tmap_tile, const CUtensorMap &tmap_tile2, const CUtensorMap &tmap_out,
                                 const SpmmParams &p, cudaStream_t stream)
 {
-    spmm_dense_b_kernel<<<(unsigned)cfg.grid, NUM_THREADS, SMEM_BYTES, stream>>>(tmap_tile, tmap_tile2, tmap_out, p);
+    if (cfg.nb == 1)
+        spmm_dense_b_kernel<1><<<(unsigned)cfg.grid, NUM_THREADS, SMEM_BYTES, stream>>>(tmap_tile, tmap_tile2, tmap_out, p);
+    else
+        spmm_dense_b_kernel<2><<<(unsigned)cfg.grid, NUM_THREADS, SMEM_BYTES, stream>>>(tmap_tile, tmap_tile2, tmap_out, p);
     return cudaGetLastError();
 }
 
