@@ -79,10 +79,11 @@ bool choose_dense_b(int K, int V, int m, int strategy)
     const bool possible = (m % 4 == 0) && (K % m == 0);
     if (!possible || strategy == VNM_STRATEGY_GATHER) return false;
     if (strategy == VNM_STRATEGY_DENSE_B) return true;
-    // measured on B200 (N = 16384): the dense-B kernel wins for every V at m <= 8, and at m = 16 for V <= 64
-    // (where the gather kernel gathers, and multiplies with masked MMAs, once per vector block of a row tile)
+    // measured on B200 (N = 16384): the dense-B kernel wins for every V at m <= 8, at m = 16 for V <= 64 and at
+    // m = 32 for V = 32 (the gather kernel gathers, and multiplies with masked MMAs, once per vector block of a row tile)
     if (m <= 8) return true;
-    return V <= 64 && m <= 16;
+    if (V <= 64 && m <= 16) return true;
+    return V == 32 && m <= 32;
 }
 
 }  // namespace
