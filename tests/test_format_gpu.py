@@ -26,7 +26,21 @@ def capi():
     return capi
 
 
-@pytest.mark.parametrize("shape", SHAPES)
+def _random_format_shapes(count, seed):
+    rng = np.random.default_rng(seed)
+    out = []
+    for _ in range(count):
+        V = 32 * int(rng.integers(1, 6))                  # 32 .. 160, not only the three the SpMM takes
+        M = V * int(rng.integers(1, 5))
+        m = int(rng.choice([4, 5, 6, 7, 8, 9, 12, 16, 24, 32, 48, 100, 130]))
+        K = int(rng.integers(m, 30 * m))                   # any K >= m, aligned or not
+        if K % m == 1:
+            K += 1      # with one column in the last group the reference's to_dense drops a value: no round trip to check
+        out.append((M, K, V, m))
+    return out
+
+
+@pytest.mark.parametrize("shape", SHAPES + _random_format_shapes(24, seed=7))
 def test_compress_decompress_bit_exact(capi, oracle, shape):
     import torch
     from venom_b200.synth import random_vnm_dense

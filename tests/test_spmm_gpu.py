@@ -273,3 +273,33 @@ def test_transposed_dense_operand_and_tma_store_layouts(capi, oracle, shape):
     wide = torch.full((N, M + 8), 3.0, dtype=torch.float16, device="cuda")
     prep.spmm_nk(bt, layout=capi.VNM_LAYOUT_NM, out=wide[:, :M])
     assert torch.equal(wide[:, :M], prep.spmm(Bd, layout=capi.VNM_LAYOUT_NM)) and bool((wide[:, M:] == 3.0).all())
+
+
+def _random_cases(count, seed):
+    rng = np.random.default_rng(seed)
+    cases = []
+    while len(cases) < count:
+        V = int(rng.choice([32, 64, 128]))
+        M = V * int(rng.integers(1, 7))
+        m = int(rng.choice([4, 5, 6, 8, 10, 12, 16, 24, 32, 40, 64]))
+        K = int(rng.integers(1, 40)) * m + int(rng.choice([0, 0, 0, 1, 3]))     # mostly K % m == 0, sometimes a ragged last group
+        N = 8 * int(rng.integers(1, 90))
+        cases.append((M, K, V, m, N))
+    return cases
+
+
+@pytest.mark.parametrize("case", _random_cases(28, seed=2025))
+def test_random_shapes_match_oracle(capi, oracle, case):
+    """Seeded random shapes, small enough for the CPU oracle: tiny N, K shorter than a k-tile, odd m, single
+    vector block ... in both output layouts with bias, whichever operand form the library picks."""
+    import torch
+    M, K, V, m, N = case
+    prep, Bd, (ov, om, cols, B) = _setup(capi, oracle, M, K, V, m, N, seed=M + 3 * K + N, ints=False)
+    _check(oracle, prep.spmm(Bd).cpu().numpy(), oracle.spmm(ov, om, cols, M, K, V, m, B))
+    bias = np.random.default_rng(M + N).uniform(-1, 1, M).astype(np.float16)
+    if not prep.dense_b_form() or M % 8 == 0:
+        outT = prep.spmm(Bd, bias=torch.from_numpy(bias).cuda(), layout=capi.VNM_LAYOUT_NM)
+        _check(oracle, outT.cpu().numpy(), oracle.spmm(ov, om, cols, M, K, V, m, B, bias=bias, layout=1))
+    if prep.dense_b_form() and K % 8 == 0:
+        assert torch.equal(prep.spmm_nk(Bd.t().contiguous(), layout=capi.VNM_LAYOUT_MN), prep.spmm(Bd))
+    assert prep.device_status() == 0
