@@ -88,6 +88,10 @@ int vnm_prepare(const void *values, const uint32_t *meta, const uint32_t *colloc
 int vnm_prepared_bytes(int M, int K, int V, int n, int m, int64_t *bytes);
 int vnm_destroy(vnm_handle_t handle);
 
+/* Threading: a handle caches the tensor maps of the last dense operand and owns the host-buffer staging, so two
+ * host threads must not call into the SAME handle at the same time (different handles are independent).  A handle
+ * belongs to the device that was current in vnm_prepare; calls with another device current return VNM_ERR_BAD_ARG. */
+
 /* out = A_vnm * B (+ bias), fp16 in, fp32 accumulate, fp16 out.
  * Replaces: SpmmNMInitFn_t / SpmmNMExecFn_t -> SpmmBlockwiseOp::initialize / operator(),
  * include/spatha/block_sparse/spmm/blockwise_op.h:90-161,209-246 (layout MN, bias must be NULL) and
@@ -143,7 +147,8 @@ int vnm_host_wait(vnm_handle_t handle);
  *     what has to start at zero itself): two calls whose GPU work overlaps -- different streams or host
  *     threads -- race on it, so serialise them;
  *   - returns after the product has finished on `stream` (it synchronises the stream to read the device
- *     status word back); failures also print one line to stderr. */
+ *     status word back); failures set vnm_last_error_string() like every entry point and also print one
+ *     line to stderr. */
 #define VNM_NOALLOC_SCRATCH_BYTES (8 * 1024 * 1024)
 int vnm_spmm_f16_noalloc(const void *values, const uint32_t *meta, const uint32_t *colloc,
                          int M, int K, int V, int n, int m,

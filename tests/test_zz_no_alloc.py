@@ -5,7 +5,10 @@ taken the whole GPU for its own pool, a plug-in inside another component's memor
 accept the device-wide synchronisation that cudaMalloc / cudaFree bring.  The entry point keeps the re-packed
 sparse operand in an array built into the library, so this test calls it twice in a row with different
 operands (the array is shared and keeps old contents) and compares each result with the regular path, which
-is itself checked against the CPU oracle elsewhere.  The file name makes pytest collect it last.
+is itself checked against the CPU oracle elsewhere, and with the CPU oracle's product of the same operands.
+"Allocates nothing" is checked where it can be seen from outside the library: the device's free memory
+(cudaMemGetInfo, which also sees a cudaMalloc made inside the library) is the same before and after each
+call once a first call has done the per-device set-up.  The file name makes pytest collect it last.
 """
 import ctypes as C
 
@@ -31,8 +34,9 @@ def _operands(oracle, M, K, V, m, N, seed):
     dense, cols, _ = random_vnm_dense(M, K, V, m, seed=seed)
     ov, om, bad = oracle.compress(dense, cols, V, m)
     assert bad == 0
+    B = random_dense_b(K, N, seed + 1)
     return (torch.from_numpy(ov).cuda(), torch.from_numpy(om.view(np.int32)).cuda(), torch.from_numpy(cols.view(np.int32)).cuda(),
-            torch.from_numpy(random_dense_b(K, N, seed + 1)).cuda())
+            torch.from_numpy(B).cuda(), (ov, om, cols, B))
 
 
 def test_noalloc_matches_regular_path_on_two_calls_in_a_row(oracle):
@@ -42,9 +46,8 @@ def test_noalloc_matches_regular_path_on_two_calls_in_a_row(oracle):
     lib = capi.lib()
     # two different operands back to back: the second call must not see anything of the first
     cases = [(512, 2048, 64, 8, 384, 0), (256, 1024, 128, 16, 264, 1), (512, 2048, 64, 8, 384, 0)]
-    before = torch.cuda.memory_allocated()
-    for (M, K, V, m, N, layout) in cases:
-        values, meta, cols, B = _operands(oracle, M, K, V, m, N, seed=M + N)
+    for i, (M, K, V, m, N, layout) in enumerate(cases):
+        values, meta, cols, B, (ov, om, hcols, hB) = _operands(oracle, M, K, V, m, N, seed=M + N)
         bias = (torch.rand(M, device="cuda") - 0.5).half() if layout == 1 else None
         # the built-in-scratch entry point always uses the gather form of the operand; ask the regular
         # path for the same form so that the two results can be compared bit for bit
@@ -54,15 +57,23 @@ def test_noalloc_matches_regular_path_on_two_calls_in_a_row(oracle):
         finally:
             capi.set_strategy(capi.STRATEGY_AUTO)
         got = torch.full_like(want, float("nan"))
+        if i == 0:
+            # the first call on a device looks up the scratch array's address and sets kernel attributes
+            assert _call_noalloc(lib, values, meta, cols, M, K, V, m, B, got, bias=bias, layout=layout) == 0
+            got.fill_(float("nan"))
+        torch.cuda.synchronize()
+        free_before, _ = torch.cuda.mem_get_info()
         rc = _call_noalloc(lib, values, meta, cols, M, K, V, m, B, got, bias=bias, layout=layout)
+        free_after, _ = torch.cuda.mem_get_info()
         assert rc == 0
+        assert free_after == free_before, "the call changed the device's free memory by %d bytes" % (free_before - free_after)
         # same kernel, same re-pack: the results are required to be identical, which is within the
         # |C - C_ref| <= 1e-2 * (|C_ref| + 1) tolerance the SpMM tests use
         assert torch.equal(got, want)
-        bad, _, worst = oracle.check(got.cpu().numpy(), want.cpu().numpy(), mode=1, tol=1e-2)
-        assert bad == 0
-    del values, meta, cols, B, want, got, bias
-    assert torch.cuda.memory_allocated() <= before + (1 << 20)
+        # and against the CPU oracle's product of the same operands
+        ref = oracle.spmm(ov, om, hcols, M, K, V, m, hB, bias=None if bias is None else bias.cpu().numpy(), layout=layout)
+        bad, _, worst = oracle.check(got.cpu().numpy(), ref, mode=1, tol=1e-2)
+        assert bad == 0, "%d mismatches against the CPU oracle (max abs err %g)" % (bad, worst)
 
 
 def test_noalloc_rejects_operands_beyond_the_built_in_scratch(oracle, capfd):
@@ -81,3 +92,4 @@ def test_noalloc_rejects_operands_beyond_the_built_in_scratch(oracle, capfd):
     assert rc == 3                                   # VNM_ERR_UNSUPPORTED
     err = capfd.readouterr().err
     assert "too large" in err and "8388608" in err
+    assert b"too large" in lib.vnm_last_error_string()   # the same message through the library's error string

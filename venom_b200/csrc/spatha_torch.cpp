@@ -6,8 +6,11 @@
 //   * V is a run-time argument (the reference needs a separate -DV_64 build);
 //   * arguments are checked and errors raise RuntimeError (the reference checks nothing);
 //   * `bias` may be an undefined / empty tensor (the reference dereferences it unconditionally);
-//   * the reference-format arrays are re-packed once per distinct (values, metadata, indices) triple
-//     and the prepared operand is cached; call spatha.clear_cache() after modifying them in place.
+//   * the reference-format arrays are re-packed once per distinct (values, metadata, indices) triple and the
+//     prepared operand is cached.  An entry is tied to the three tensors' storages through weak references:
+//     once any of them has been freed (even if a new tensor later lands on the same address) the entry is
+//     dead, its device copy is released and the operand is re-packed.  In-place edits bump the tensors'
+//     version counters, which are part of the key.
 #include <torch/extension.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <c10/cuda/CUDAStream.h>
@@ -31,8 +34,39 @@ struct Key {
     }
 };
 
-std::map<Key, vnm_handle_t> g_cache;
+using WeakStorage = c10::weak_intrusive_ptr<c10::StorageImpl>;
+
+struct Entry {
+    vnm_handle_t handle;
+    WeakStorage values, meta, idx;   // the storages the operand was re-packed from
+    bool alive() const { return !values.expired() && !meta.expired() && !idx.expired(); }
+};
+
+std::map<Key, Entry> g_cache;
 std::mutex g_mutex;
+
+WeakStorage weak_of(const torch::Tensor &t)
+{
+    return WeakStorage(t.storage().getWeakStorageImpl());
+}
+
+bool same_storage(const WeakStorage &w, const torch::Tensor &t)
+{
+    return !w.expired() && w._unsafe_get_target() == t.storage().unsafeGetStorageImpl();
+}
+
+// Releases the device copies of operands whose source tensors no longer exist.
+void sweep_dead_entries()
+{
+    for (auto it = g_cache.begin(); it != g_cache.end();) {
+        if (!it->second.alive()) {
+            vnm_destroy(it->second.handle);
+            it = g_cache.erase(it);
+        } else {
+            ++it;
+        }
+    }
+}
 
 void check(int rc, const char *what)
 {
@@ -72,14 +106,22 @@ torch::Tensor spmm(torch::Tensor A_metadata, torch::Tensor A_indices, torch::Ten
     {
         std::lock_guard<std::mutex> lock(g_mutex);
         auto it = g_cache.find(key);
+        if (it != g_cache.end() && !(same_storage(it->second.values, A_values) && same_storage(it->second.meta, A_metadata) &&
+                                     same_storage(it->second.idx, A_indices))) {
+            // same addresses, different (or freed) tensors: the cached copy belongs to an operand that is gone
+            vnm_destroy(it->second.handle);
+            g_cache.erase(it);
+            it = g_cache.end();
+        }
         if (it == g_cache.end()) {
+            sweep_dead_entries();
             // An activation that arrives as a transposed [tokens, features] view is read in place only by the dense-B
             // form, and the transpose copy it saves costs more than the gather form gains at high sparsity.
             check(vnm_prepare_as(A_values.data_ptr(), (const uint32_t *)A_metadata.data_ptr(), (const uint32_t *)A_indices.data_ptr(), M, K, V,
                                  (int)n, (int)m, rhs_is_t_view ? VNM_STRATEGY_DENSE_B : VNM_STRATEGY_AUTO, &h, stream), "vnm_prepare_as");
-            g_cache.emplace(key, h);
+            g_cache.emplace(key, Entry{h, weak_of(A_values), weak_of(A_metadata), weak_of(A_indices)});
         } else {
-            h = it->second;
+            h = it->second.handle;
         }
     }
     auto out = torch::empty({N, M}, rhs_matrix.options());
@@ -99,7 +141,7 @@ torch::Tensor spmm(torch::Tensor A_metadata, torch::Tensor A_indices, torch::Ten
 void clear_cache()
 {
     std::lock_guard<std::mutex> lock(g_mutex);
-    for (auto &kv : g_cache) vnm_destroy(kv.second);
+    for (auto &kv : g_cache) vnm_destroy(kv.second.handle);
     g_cache.clear();
 }
 

@@ -13,8 +13,19 @@
 using namespace vnm;
 
 namespace {
-
 thread_local std::string g_last_error;
+}
+
+namespace vnm {
+// Records the message returned by vnm_last_error_string() on this thread and passes the code through.
+int set_last_error(int code, const char *msg)
+{
+    g_last_error = msg;
+    return code;
+}
+}  // namespace vnm
+
+namespace {
 
 int fail(int code, const char *fmt, ...)
 {
@@ -23,8 +34,7 @@ int fail(int code, const char *fmt, ...)
     va_start(ap, fmt);
     vsnprintf(buf, sizeof(buf), fmt, ap);
     va_end(ap);
-    g_last_error = buf;
-    return code;
+    return set_last_error(code, buf);
 }
 
 int fail_cuda(cudaError_t e, const char *what)
@@ -38,7 +48,9 @@ int fail_cuda(cudaError_t e, const char *what)
         if (e__ != cudaSuccess) return fail_cuda(e__, what);   \
     } while (0)
 
-int check_format(int M, int K, int V, int n, int m)
+}  // namespace
+
+int vnm::check_format(int M, int K, int V, int n, int m)
 {
     if (n != 2) return fail(VNM_ERR_BAD_ARG, "n must be 2 (got %d)", n);
     if (m < 4) return fail(VNM_ERR_BAD_ARG, "m must be >= 4 (got %d)", m);
@@ -49,27 +61,43 @@ int check_format(int M, int K, int V, int n, int m)
     return VNM_OK;
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
-                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn get_encode_fn()
+vnm::EncodeTiledFn vnm::get_encode_fn()
 {
     static EncodeTiledFn fn = nullptr;
-    static bool tried = false;
-    if (!tried) {
-        tried = true;
+    static std::once_flag once;
+    std::call_once(once, [] {
         void *p = nullptr;
         cudaDriverEntryPointQueryResult q;
         if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
             q == cudaDriverEntryPointSuccess)
             fn = (EncodeTiledFn)p;
-    }
+    });
     return fn;
 }
 
-bool g_kernels_ready = false;
+namespace {
+
+// cudaFuncSetAttribute (large dynamic shared memory) applies per device: one flag per device, set under a mutex.
+constexpr int kMaxDevices = 64;
+bool g_kernels_ready[kMaxDevices] = {};
+std::mutex g_init_mutex;
 int g_strategy = 0;  // VNM_STRATEGY_*
+
+// Opts every kernel instance into its shared-memory size on the current device (once per device).
+int ensure_kernels_ready(int *device_out)
+{
+    int dev = -1;
+    VNM_CUDA(cudaGetDevice(&dev), "cudaGetDevice");
+    if (dev < 0 || dev >= kMaxDevices) return fail(VNM_ERR_UNSUPPORTED, "device index %d not supported", dev);
+    std::lock_guard<std::mutex> lock(g_init_mutex);
+    if (!g_kernels_ready[dev]) {
+        VNM_CUDA(spmm_init_kernels(), "cudaFuncSetAttribute(max dynamic shared memory)");
+        VNM_CUDA(spmm_dense_b_init(), "cudaFuncSetAttribute(max dynamic shared memory)");
+        g_kernels_ready[dev] = true;
+    }
+    if (device_out) *device_out = dev;
+    return VNM_OK;
+}
 
 // Gather form vs dense-B form (see vnm_set_strategy in the header).  Measured on B200: the gather path is
 // bound by the TMA gather rate and pays NB = 128/V times for small vector lengths, the dense-B form costs
@@ -119,7 +147,6 @@ struct vnm_prepared_s {
     cudaEvent_t ev[2 * HOST_CHUNKS_MAX + 2];
     bool host_pipe_ready;
     int gather_mode;
-    long long *trace;  // debug builds only
     int dense_b;       // 1: A re-expressed as 2:4 over all K columns, B read as plain tiles
 };
 
@@ -206,11 +233,8 @@ int vnm_prepare_as(const void *values, const uint32_t *meta, const uint32_t *col
     if (!values || !meta || !colloc || !handle) return fail(VNM_ERR_BAD_ARG, "vnm_prepare: null pointer");
     if (V != 32 && V != 64 && V != 128) return fail(VNM_ERR_UNSUPPORTED, "SpMM supports V in {32, 64, 128} (got %d)", V);
     if (((uintptr_t)colloc & 15) || ((uintptr_t)values & 3)) return fail(VNM_ERR_BAD_ARG, "vnm_prepare: colloc must be 16-byte and values 4-byte aligned");
-    if (!g_kernels_ready) {
-        VNM_CUDA(spmm_init_kernels(), "cudaFuncSetAttribute(max dynamic shared memory)");
-        VNM_CUDA(spmm_dense_b_init(), "cudaFuncSetAttribute(max dynamic shared memory)");
-        g_kernels_ready = true;
-    }
+    int dev_now = -1;
+    if ((rc = ensure_kernels_ready(&dev_now))) return rc;
     vnm_prepared_s *h = new (std::nothrow) vnm_prepared_s();
     if (!h) return fail(VNM_ERR_CUDA, "out of host memory");
     memset(h, 0, sizeof(*h));
@@ -229,8 +253,8 @@ int vnm_prepare_as(const void *values, const uint32_t *meta, const uint32_t *col
     }
     h->vblocks_padded = h->mtiles * h->nb;
     h->producer_warps = 8;
-    cudaError_t e = cudaGetDevice(&h->device);
-    if (e == cudaSuccess) e = cudaMalloc(&h->am, (size_t)h->mtiles * h->ktiles * AM_BLOCK_BYTES);
+    h->device = dev_now;
+    cudaError_t e = cudaMalloc(&h->am, (size_t)h->mtiles * h->ktiles * AM_BLOCK_BYTES);
     if (e == cudaSuccess) e = cudaMalloc(&h->rows, (size_t)h->vblocks_padded * h->ktiles * KT_GROUPS * sizeof(int4));
     if (e == cudaSuccess) e = cudaMalloc((void **)&h->status, sizeof(int));
     if (e == cudaSuccess) e = cudaMemsetAsync(h->status, 0, sizeof(int), (cudaStream_t)stream);
@@ -273,16 +297,6 @@ int vnm_set_gather_mode(vnm_handle_t h, int mode)
     return VNM_OK;
 }
 
-#ifdef VNM_TRACE
-// Debug builds only: device buffer of 8 x 4096 clock stamps written by CTA 0 of the next launches.
-int vnm_debug_set_trace(vnm_handle_t h, long long *device_buffer)
-{
-    if (!h) return fail(VNM_ERR_BAD_ARG, "null handle");
-    h->trace = device_buffer;
-    return VNM_OK;
-}
-#endif
-
 int vnm_set_strategy(int strategy)
 {
     if (strategy != VNM_STRATEGY_AUTO && strategy != VNM_STRATEGY_GATHER && strategy != VNM_STRATEGY_DENSE_B)
@@ -317,6 +331,13 @@ static int spmm_impl(vnm_handle_t h, const void *B, int64_t ldb, int N, int b_nk
                      void *stream)
 {
     if (!h || !B || !out) return fail(VNM_ERR_BAD_ARG, "vnm_spmm_f16: null pointer");
+    {
+        // the handle's private copy, its status word and the kernel attributes belong to one device
+        int dev = -1;
+        VNM_CUDA(cudaGetDevice(&dev), "cudaGetDevice");
+        if (dev != h->device)
+            return fail(VNM_ERR_BAD_ARG, "vnm_spmm_f16: the handle was prepared on device %d but device %d is current", h->device, dev);
+    }
     if (N <= 0 || N % 8 != 0) return fail(VNM_ERR_BAD_ARG, "vnm_spmm_f16: N (%d) must be a positive multiple of 8", N);
     if (b_nk) {
         if (!h->dense_b) return fail(VNM_ERR_UNSUPPORTED, "a [N,K] dense operand needs an operand prepared in dense-B form (see vnm_operand_form)");
@@ -405,7 +426,6 @@ static int spmm_impl(vnm_handle_t h, const void *B, int64_t ldb, int N, int b_nk
     p.status = h->status;
     p.gather_mode = h->gather_mode;
     p.total_tiles = p.mtiles * p.ntiles;
-    p.trace = h->trace;
     p.b_nk = b_nk;
     p.b_wide_ok = h->tm_wide ? 1 : 0;
     if (h->dense_b) {

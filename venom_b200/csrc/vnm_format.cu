@@ -44,7 +44,9 @@ __global__ void __launch_bounds__(256) compress_kernel(const __half *__restrict_
 #pragma unroll
                 for (int j = 0; j < 4; j++) {
                     const int64_t col = g * m + (int64_t)cand[j];
-                    if (col < K) {
+                    if (cand[j] >= (uint32_t)m) {
+                        pos = 3;  // a column offset outside its group (corrupt column-loc): counted as a violation, never read
+                    } else if (col < K) {
                         const unsigned short bits = __half_as_ushort(drow[col]);
                         const bool keep = kHasMask ? (mrow[col] != 0) : ((bits & 0x7FFFu) != 0);  // value != +-0
                         if (keep) {
@@ -181,7 +183,9 @@ __global__ void __launch_bounds__(256) compress_tiled_kernel(const __half *__res
                 const int lg = (tl * 4 + gi) * m;  // first column of the group, relative to the chunk
                 uint32_t out = 0;
                 int pos = 0;
-                if (lg + m <= validc) {  // the whole group exists (same for every lane)
+                if (max(max(c4.x, c4.y), max(c4.z, c4.w)) >= (uint32_t)m) {
+                    pos = 3;  // a column offset outside its group (corrupt column-loc): counted as a violation, nothing is read
+                } else if (lg + m <= validc) {  // the whole group exists (same for every lane)
 #pragma unroll
                     for (int j = 0; j < 4; j++) {
                         const int lc = lg + cand[j];

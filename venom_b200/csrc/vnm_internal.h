@@ -28,7 +28,6 @@ struct SpmmParams {
     int *status;          // device status word
     int gather_mode;      // GATHER_* below
     int total_tiles;      // mtiles * ntiles
-    long long *trace;     // debug builds (-DVNM_TRACE) only: clock stamps of CTA 0, else null
     int b_nk;             // dense-B kernel only: the dense operand is given as [N, K] row-major (K contiguous)
     int b_wide_ok;        // dense-B kernel only: the 4-D tensor map exists (column tiles with 256 columns inside N use one box per stage)
 };
@@ -50,6 +49,14 @@ struct SpmmConfig {
     int grid;    // persistent CTAs
 };
 
+// Host-side helpers shared by the translation units that implement C-ABI entry points (defined in vnm_capi.cu).
+int set_last_error(int code, const char *msg);       // message of vnm_last_error_string() for this thread; returns code
+int check_format(int M, int K, int V, int n, int m);  // VNM_OK or an error code with the message set
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn get_encode_fn();                        // cuTensorMapEncodeTiled from the driver, or null (thread-safe)
+
 cudaError_t launch_compress(const void *dense, int64_t ldd, const int32_t *mask, const uint32_t *colloc, int M, int K, int V, int m,
                             void *values, uint32_t *meta, unsigned long long *violations, cudaStream_t stream);
 cudaError_t launch_decompress(const void *values, const uint32_t *meta, const uint32_t *colloc, int M, int K, int V, int m,
@@ -65,7 +72,7 @@ cudaError_t launch_prune(const float *w, int64_t ldw, int M, int K, int V, int m
 
 // Chooses the tile configuration for (V, N).  Returns false for an unsupported V.
 bool spmm_select_config(int V, int N, int M, int producer_warps, SpmmConfig *cfg);
-// One-time per-process opt-in to large dynamic shared memory for every kernel instance.
+// Opt-in to large dynamic shared memory for every kernel instance on the CURRENT device (call once per device).
 cudaError_t spmm_init_kernels();
 cudaError_t launch_spmm(const SpmmConfig &cfg, const CUtensorMap &tmap_rows, const CUtensorMap &tmap_tile, const SpmmParams &p,
                         cudaStream_t stream);

@@ -35,45 +35,26 @@ struct DeviceState {
 DeviceState g_dev[kMaxDevices];
 std::mutex g_mutex;
 
-
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
-                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn()
-{
-    static EncodeTiledFn fn = nullptr;
-    static bool tried = false;
-    if (!tried) {
-        tried = true;
-        void *p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiledFn)p;
-    }
-    return fn;
-}
-
 }  // namespace
 
 static int nfail(int code, const char *fmt, ...)
 {
-    // This entry point reports through its return code and one line on stderr.
+    // Reports like every other entry point (return code + vnm_last_error_string()) and, because the callers of
+    // this variant often run where nobody polls an error string, with one line on stderr as well.
     char msg[512];
     va_list ap;
     va_start(ap, fmt);
     vsnprintf(msg, sizeof(msg), fmt, ap);
     va_end(ap);
     fprintf(stderr, "vnm_spmm_f16_noalloc: %s\n", msg);
-    return code;
+    return set_last_error(code, msg);
 }
 
 extern "C" int vnm_spmm_f16_noalloc(const void *values, const uint32_t *meta, const uint32_t *colloc, int M, int K, int V, int n, int m,
                                     const void *B, int64_t ldb, int N, const void *bias, void *out, int64_t ldo, int layout, void *stream)
 {
     if (!values || !meta || !colloc || !B || !out) return nfail(VNM_ERR_BAD_ARG, "null pointer");
-    if (n != 2 || m < 4 || M <= 0 || K <= 0 || V <= 0 || V % 32 != 0 || M % V != 0)
-        return nfail(VNM_ERR_BAD_ARG, "bad format: need n == 2, m >= 4, V %% 32 == 0, M %% V == 0 (M=%d K=%d V=%d n=%d m=%d)", M, K, V, n, m);
+    if (int rc = check_format(M, K, V, n, m)) return nfail(rc, "%s", vnm_last_error_string());  // same format limits as every other entry point
     if (V != 32 && V != 64 && V != 128) return nfail(VNM_ERR_UNSUPPORTED, "V must be 32, 64 or 128 (got %d)", V);
     if (N <= 0 || N % 8 != 0) return nfail(VNM_ERR_BAD_ARG, "N (%d) must be a positive multiple of 8", N);
     if (ldb < N || ldb % 8 != 0 || ((uintptr_t)B & 15)) return nfail(VNM_ERR_BAD_ARG, "B needs ldb >= N, ldb %% 8 == 0 and a 16-byte aligned base");
@@ -134,7 +115,7 @@ extern "C" int vnm_spmm_f16_noalloc(const void *values, const uint32_t *meta, co
 
     SpmmConfig cfg;
     if (!spmm_select_config(V, N, M, 8, &cfg)) return nfail(VNM_ERR_UNSUPPORTED, "unsupported V");
-    EncodeTiledFn enc = encode_fn();
+    EncodeTiledFn enc = get_encode_fn();
     if (!enc) return nfail(VNM_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
     CUtensorMap tmap_rows, tmap_tile;
     cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)K};
@@ -159,7 +140,6 @@ extern "C" int vnm_spmm_f16_noalloc(const void *values, const uint32_t *meta, co
     p.status = status;
     p.gather_mode = (m == 4) ? GATHER_CONTIG : GATHER_TMA4;
     p.total_tiles = p.mtiles * p.ntiles;
-    p.trace = nullptr;
     p.b_nk = 0;
     p.b_wide_ok = 0;
     e = launch_spmm(cfg, tmap_rows, tmap_tile, p, s);

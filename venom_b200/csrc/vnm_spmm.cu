@@ -37,13 +37,6 @@ namespace {
 
 constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;  // ~2 s at B200 clocks
 
-#ifdef VNM_TRACE
-// Debug build only: CTA 0 records clock64() stamps of its pipeline hand-offs into p.trace.
-#define TRACE(slot, idx) do { if (blockIdx.x == 0 && lane == 0 && (idx) < 4096 && p.trace) p.trace[(slot) * 4096 + (idx)] = clock64(); } while (0)
-#else
-#define TRACE(slot, idx) do { } while (0)
-#endif
-
 constexpr int BS_ROWS = 64;     // gathered rows per B stage
 constexpr int BS_GROUPS = 16;   // groups per B stage
 
@@ -193,7 +186,6 @@ __global__ void __launch_bounds__(Traits<BN, NB, SA, SB, PB>::NUM_THREADS, 1)
                         const int kd = it - SA;
                         if (!wait_one(&kdone[kd % T::SP], (uint32_t)(kd / T::SP) & 1u, abort_flag, p.status, DEV_TIMEOUT_PRODUCER)) { alive = false; break; }
                     }
-                    TRACE(0, it);
                     mbar_arrive_expect_tx(&a_full[s], AM_BLOCK_BYTES);
                     bulk_g2s(a_ring + s * AM_BLOCK_BYTES, p.am + ((size_t)mt * p.ktiles + kt) * AM_BLOCK_BYTES, AM_BLOCK_BYTES, &a_full[s]);
                 }
@@ -246,7 +238,6 @@ __global__ void __launch_bounds__(Traits<BN, NB, SA, SB, PB>::NUM_THREADS, 1)
                 uint8_t *st = b_ring + s * T::B_STAGE_BYTES;
                 const int n0 = (tile / p.mtiles) * BN;
                 if (leader) {
-                    TRACE(1, j);
                     if (gmode == GATHER_NONE) mbar_arrive(&b_full[s]);
                     else mbar_arrive_expect_tx(&b_full[s], T::B_STAGE_BYTES);
                 }
@@ -306,15 +297,11 @@ __global__ void __launch_bounds__(Traits<BN, NB, SA, SB, PB>::NUM_THREADS, 1)
             bool alive = true;
             for (int ti = 0; alive && ti < my_tiles; ++ti) {
                 // the epilogue must have read the previous tile's accumulator
-                TRACE(7, ti * 2);
                 if (!wait_one(acc_empty_bar, ((uint32_t)ti & 1u) ^ 1u, abort_flag, p.status, DEV_TIMEOUT_MMA)) break;
                 tc_fence_after();
-                TRACE(7, ti * 2 + 1);
                 for (int kt = 0; kt < p.ktiles; ++kt, ++it) {
-                    TRACE(2, it);
                     if (!wait_one(&kready[it % T::SR], (uint32_t)(it / T::SR) & 1u, abort_flag, p.status, DEV_TIMEOUT_MMA)) { alive = false; break; }
                     tc_fence_after();
-                    TRACE(3, it);
                     const uint32_t aoff = (uint32_t)((it % SA) * AM_BLOCK_BYTES) >> 4;
                     const uint32_t mcol = meta0 + (uint32_t)(it & 1) * 4u;
 #pragma unroll
@@ -346,7 +333,6 @@ __global__ void __launch_bounds__(Traits<BN, NB, SA, SB, PB>::NUM_THREADS, 1)
                     }
                     tc_commit(&kdone[it % T::SP]);
                     if (kt == p.ktiles - 1) tc_commit(acc_full_bar);
-                    TRACE(5, 2 * it + 1);
                 }
             }
         }
@@ -363,7 +349,6 @@ __global__ void __launch_bounds__(Traits<BN, NB, SA, SB, PB>::NUM_THREADS, 1)
             const int n0 = (tile / p.mtiles) * BN;
             if (!wait_bounded(acc_full_bar, (uint32_t)ti & 1u, abort_flag, p.status, DEV_TIMEOUT_EPILOGUE)) break;
             tc_fence_after();
-            if (q == 0) TRACE(6, ti * 3);
             // The tile is drained in parts of 64 columns to bound the register footprint; the
             // accumulator goes back to the MMA warp as soon as the last part is in registers.
             constexpr int PART = 64;
@@ -401,7 +386,6 @@ __global__ void __launch_bounds__(Traits<BN, NB, SA, SB, PB>::NUM_THREADS, 1)
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(acc_empty_bar);
-                    if (q == 0) TRACE(6, ti * 3 + 1);
                 }
                 if (row_ok) {
                     const int nbase = n0 + part * PART;
@@ -450,7 +434,6 @@ __global__ void __launch_bounds__(Traits<BN, NB, SA, SB, PB>::NUM_THREADS, 1)
                     }
                 }
             }
-            if (q == 0) TRACE(6, ti * 3 + 2);
         }
     }
 

@@ -29,13 +29,6 @@ namespace {
 
 constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;  // ~2 s at B200 clocks
 
-#ifdef VNM_TRACE
-// Debug build only: CTA 0 records clock64() stamps of its pipeline hand-offs into p.trace.
-#define TRACE(slot, idx) do { if (blockIdx.x == 0 && (idx) < 4096 && p.trace) p.trace[(slot) * 4096 + (idx)] = clock64(); } while (0)
-#else
-#define TRACE(slot, idx) do { } while (0)
-#endif
-
 constexpr int RT = 2;            // row tiles per CTA tile the shared-memory and tensor-memory plans are sized for; the kernel
                                  // template runs with R = 2, or R = 1 when the problem has too few tiles to fill the GPU otherwise
 constexpr int BN = 240;          // output columns per CTA tile
@@ -164,7 +157,6 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_kernel(const __gr
                         const int jd = 4 * (it - SA) + 3;  // last B stage of the k-tile that used this slot
                         if (!wait_one(&b_free[jd % SF], (uint32_t)(jd / SF) & 1u, abort_flag, p.status, DEV_TIMEOUT_PRODUCER)) { alive = false; break; }
                     }
-                    TRACE(0, it);
                     mbar_arrive_expect_tx(&a_full[s], R * AM_BLOCK_BYTES);
 #pragma unroll
                     for (int rt = 0; rt < R; rt++) {
@@ -200,7 +192,6 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_kernel(const __gr
                     const int jd = j - SB;
                     if (!wait_one(&b_free[jd % SF], (uint32_t)(jd / SF) & 1u, abort_flag, p.status, DEV_TIMEOUT_PRODUCER)) break;
                 }
-                TRACE(1, j);
                 uint8_t *dst = b_ring + s * B_STAGE_BYTES;
                 if (p.gather_mode == GATHER_NONE) {
                     mbar_arrive(&b_full[s]);
@@ -261,15 +252,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_kernel(const __gr
             bool alive = true;
             for (int ti = 0; alive && ti < my_tiles; ++ti) {
                 for (int kt = 0; alive && kt < p.ktiles; ++kt, ++it) {
-                    TRACE(2, it);
                     if (!wait_one(&kready[it % SR], (uint32_t)(it / SR) & 1u, abort_flag, p.status, DEV_TIMEOUT_MMA)) { alive = false; break; }
                     tc_fence_after();
-                    TRACE(3, it);
                     if (kt == 0) {
-                        TRACE(7, ti * 2);
                         if (!wait_one(acc_empty_bar, ((uint32_t)ti & 1u) ^ 1u, abort_flag, p.status, DEV_TIMEOUT_MMA)) { alive = false; break; }
                         tc_fence_after();
-                        TRACE(7, ti * 2 + 1);
                     }
                     const uint32_t mcol = tmem_base + meta_col(it % META_SETS);
                     const uint32_t aoff = (uint32_t)((it % SA) * A_STAGE_BYTES) >> 4;
@@ -278,7 +265,6 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_kernel(const __gr
                         const int j = 4 * it + kb;
                         if (!wait_one(&b_full[j % SB], (uint32_t)(j / SB) & 1u, abort_flag, p.status, DEV_TIMEOUT_MMA)) { alive = false; break; }
                         tc_fence_after();
-                        TRACE(4, j);
                         const uint32_t boff = (uint32_t)((j % SB) * B_STAGE_BYTES) >> 4;
 #pragma unroll
                         for (int rt = 0; rt < R; rt++)
@@ -288,7 +274,6 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_kernel(const __gr
                     }
                     if (!alive) break;
                     if (kt == p.ktiles - 1) tc_commit(acc_full_bar);
-                    TRACE(5, it);
                 }
             }
         }
@@ -310,7 +295,6 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_kernel(const __gr
             const bool got = wait_warp(acc_full_bar, (uint32_t)ti & 1u, abort_flag, p.status, DEV_TIMEOUT_EPILOGUE);
             if (!named_barrier_and(1 + ((warp - EPI_WARP0) >> 2), 128, got)) break;
             tc_fence_after();
-            if (warp == EPI_WARP0 && lane == 0) TRACE(6, ti * 3);
             {
                 const int rt = (warp - EPI_WARP0) >> 2;  // which accumulator this warp drains
                 const int mt = mp * R + rt;
@@ -386,10 +370,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_kernel(const __gr
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(acc_empty_bar);
-                if (warp == EPI_WARP0 && lane == 0) TRACE(6, ti * 3 + 1);
 #pragma unroll
                 for (int h = 0; h < HELD; h++) store_part(NPARTS - HELD + h, held + h * (PART / 2));
-                if (warp == EPI_WARP0 && lane == 0) TRACE(6, ti * 3 + 2);
             }
         }
     }
