@@ -154,9 +154,62 @@ def test_transposed_view_prepares_dense_b_form_at_high_sparsity(spatha, oracle):
     assert torch.equal(forced.spmm_nk(act, layout=capi.VNM_LAYOUT_NM), out)
 
 
+def test_gpt_block_sparse_equals_masked_dense_twin(spatha):
+    """One GPT-shaped decoder layer pruned by magnitude to 128:2:16: the block whose linears run through the op
+    must agree with a dense block whose weights were masked with exactly what the sparse modules kept."""
+    import torch
+    from venom_b200 import capi, e2e_gpt
+    from venom_b200.nmv import SrnmSpmm
+    torch.manual_seed(0)
+    hidden, heads, ffn = 512, 8, 2048
+    with torch.device("cuda"):
+        dense = e2e_gpt.build_block(2, hidden, heads, ffn).half()
+        sparse = e2e_gpt.build_block(2, hidden, heads, ffn).half()
+    sparse.load_state_dict(dense.state_dict())
+    assert e2e_gpt.sparsify(sparse, 2, 16, 128, magnitude=True) == 8
+    twins = dict(dense.named_modules())
+    for name, mod in sparse.named_modules():
+        if isinstance(mod, SrnmSpmm):
+            kept = capi.decompress(mod.values, mod.metadata, mod.columns, mod.nrows_sp, mod.ncols_sp, mod.v, mod.m)
+            assert int((kept != 0).sum()) == mod.nrows_sp * mod.ncols_sp // 8      # 2 of every 16
+            twins[name].weight.data.copy_(kept)
+    x = torch.randn((2, 256, hidden), device="cuda").half()
+    with torch.no_grad():
+        a = dense(x).float()
+        b = sparse(x).float()
+    assert torch.allclose(a, b, rtol=3e-2, atol=3e-2), float((a - b).abs().max())
+
+
 def test_gpt_block_harness_small(spatha):
     """The decoder-block harness on a small shape: sparse and dense forwards run and print the reference's lines."""
     from venom_b200 import e2e_gpt
     d, s_ = e2e_gpt.main(["-m", "16", "-v", "128", "--layers", "1", "--hidden", "512", "--heads", "8", "--ffn", "2048", "--batch", "2",
                           "--seq", "128", "--repeats", "2"])
     assert d > 0 and s_ > 0
+
+
+def test_cache_does_not_outlive_the_operand_it_was_built_from(spatha, oracle):
+    """A weight is freed and a DIFFERENT one of the same shape lands on the same device addresses (torch's caching
+    allocator hands the blocks straight back): the op must multiply with the new weight, not the cached old one."""
+    import torch
+    from venom_b200.synth import random_dense_b, random_vnm_dense
+    M, K, V, m, N = 256, 1024, 64, 8, 256
+    B = random_dense_b(K, N, seed=5)
+    Bd = torch.from_numpy(B).cuda()
+    spatha.clear_cache()
+    seen = []
+    for seed in (1, 2):
+        dense, cols, _ = random_vnm_dense(M, K, V, m, seed=seed)
+        ov, om, _ = oracle.compress(dense, cols, V, m)
+        values = torch.from_numpy(ov).cuda()
+        meta = torch.from_numpy(om.view(np.int32)).cuda()
+        idx = torch.from_numpy(cols.view(np.int32)).cuda()
+        seen.append((values.data_ptr(), meta.data_ptr(), idx.data_ptr()))
+        out = spatha.spmm(meta, idx, values, Bd, None, M, K, N, V, 2, m, values.numel(), 0, 32, 4)
+        want = oracle.spmm(ov, om, cols, M, K, V, m, B, layout=1)
+        bad, first, worst = oracle.check(out.cpu().numpy(), want, mode=1, tol=1e-2)
+        assert bad == 0, "seed %d: %d mismatches (max abs err %g)" % (seed, bad, worst)
+        del values, meta, idx, out
+    if seen[0] != seen[1]:
+        pytest.skip("the allocator did not hand the same addresses back: the stale-entry case was not exercised")
+    assert spatha.cache_size() == 1     # the dead entry was released when the new operand arrived

@@ -1,8 +1,9 @@
 """GPT-3-shaped decoder block inference, dense vs V:N:M, sharded by sequences over the GPUs of one node.
 
 Mirrors the reference's end2end/gpt3_pytorch.py (argument names -m -n -v, every linear of the decoder layers
-replaced by SrnmSpmm with the fixed-mask sparsifier the script ships, output lines `0,n,m,v,mean,median,std,len`
-in milliseconds), with these differences:
+replaced by SrnmSpmm, output lines `0,n,m,v,mean,median,std,len` in milliseconds), with these differences:
+  * weights are pruned by magnitude inside every V x m block on the GPU (the path the reference keeps commented
+    out, end2end/bert_pytorch.py:63-64); --fixed-mask selects the fixed pattern the reference's script ships;
   * the layers are written out here (pre-LayerNorm attention + GELU MLP with torch.nn.Linear) instead of
     instantiating transformers' GPT2Model, whose Conv1D weights the reference has to transpose first; weights are
     random-init N(0, 0.02) -- no checkpoint is available offline;
@@ -13,7 +14,7 @@ in milliseconds), with these differences:
   * timing uses CUDA events, the maximum over ranks is reported.
 
     python -m venom_b200.e2e_gpt -m 16 -n 2 -v 128 [--layers 4] [--hidden 12288] [--heads 96] [--ffn 49152]
-           [--batch 8] [--seq 2048] [--repeats 5] [--magnitude]
+           [--batch 8] [--seq 2048] [--repeats 5] [--fixed-mask]
     python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 -m venom_b200.e2e_gpt ...
 """
 import argparse
@@ -91,7 +92,8 @@ def main(argv=None):
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--seq", type=int, default=2048)
     ap.add_argument("--repeats", type=int, default=5)
-    ap.add_argument("--magnitude", action="store_true", help="prune by magnitude on the GPU instead of the fixed mask")
+    ap.add_argument("--fixed-mask", action="store_true", help="the reference script's fixed pattern instead of magnitude pruning")
+    ap.add_argument("--magnitude", action="store_true", help="accepted for compatibility: magnitude pruning is the default")
     ap.add_argument("--skip-dense", action="store_true")
     ap.add_argument("--gather-every-layer", action="store_true",
                     help="additionally all-gather the output of every linear (communication-bound variant; the gathered copies are discarded)")
@@ -164,7 +166,7 @@ def main(argv=None):
     d_ms = None
     if not args.skip_dense:
         d_ms = max_over_ranks(time_forward(step, args.repeats))
-    replaced = sparsify(block, args.n, args.m, args.v, args.magnitude)
+    replaced = sparsify(block, args.n, args.m, args.v, not args.fixed_mask)
     torch.cuda.empty_cache()
     if args.gather_every_layer and world > 1:
         install_gather_hooks()
@@ -179,7 +181,7 @@ def main(argv=None):
         line("%d,%d," % (args.n, args.m), s_ms)
         msg = "# %d GPUs%s, %d linears replaced (%s mask); %d:%d:%d %.0f tokens/s" % (
             world, ", all-gather after every linear" if args.gather_every_layer and world > 1 else "", replaced,
-            "magnitude" if args.magnitude else "fixed", args.v, args.n, args.m, tokens / statistics.median(s_ms) * 1e3)
+            "fixed" if args.fixed_mask else "magnitude", args.v, args.n, args.m, tokens / statistics.median(s_ms) * 1e3)
         if d_ms:
             msg += "; dense %.0f tokens/s, speed-up %.2fx" % (tokens / statistics.median(d_ms) * 1e3, statistics.median(d_ms) / statistics.median(s_ms))
         print(msg)
