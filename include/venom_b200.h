@@ -189,9 +189,57 @@ int vnm_set_strategy(int strategy);
 int vnm_prepare_as(const void *values, const uint32_t *meta, const uint32_t *colloc,
                    int M, int K, int V, int n, int m, int strategy, vnm_handle_t *handle, void *stream);
 int vnm_set_producer_warps(vnm_handle_t handle, int warps);
+/* Caps the number of persistent CTAs (one per SM) the product of this handle launches; 0 = all SMs (default).  A caller
+ * that runs something else beside the product (the multi-GPU launcher's all-gather, another stream's kernels) keeps SMs
+ * free this way: a persistent CTA that has to wait for an SM would otherwise run after all the others.  No counterpart
+ * in the reference (its kernels launch one CTA per tile). */
+int vnm_set_max_ctas(vnm_handle_t handle, int max_ctas);
+/* Shape and settings of a prepared operand (any output pointer may be NULL). */
+int vnm_handle_info(vnm_handle_t handle, int *M, int *K, int *V, int *m, int *max_ctas);
 
 /* Kernel configuration that vnm_spmm_f16 would launch for this handle and N (for reporting). */
 int vnm_spmm_config(vnm_handle_t handle, int N, int *tile_m, int *tile_n, int *stages, int *grid, int *smem_bytes);
+
+/* ---------------------------------------------------------------------------------------------------------
+ * Multi-GPU launcher: the dense operand and the result sharded by columns (N) over the GPUs of one node, the
+ * sparse operand replicated.  One context per GPU (one process or host thread each, that GPU current).
+ * The reference has no multi-GPU path (its harness and its torch op drive one GPU); these entry points are
+ * what its callers would use in place of one vnm_prepare + vnm_spmm_f16 per process.
+ * NCCL is loaded at run time (libnccl.so.2; a copy already loaded by the process is reused): VNM_ERR_UNSUPPORTED
+ * if it cannot be found.  Collectives run on local buffers only.
+ * --------------------------------------------------------------------------------------------------------- */
+typedef struct vnm_mgpu_s *vnm_mgpu_t;
+#define VNM_MGPU_ID_BYTES 128
+
+/* Column range [lo, hi) of `rank`: contiguous, sizes differ by at most `multiple`, every boundary a multiple of
+ * `multiple` (the product needs 8).  Pure arithmetic; needs neither a GPU nor NCCL. */
+int vnm_mgpu_shard(int N, int world, int rank, int multiple, int *lo, int *hi);
+/* Rank 0 fills VNM_MGPU_ID_BYTES bytes (an ncclUniqueId) and hands them to the other ranks by any means. */
+int vnm_mgpu_unique_id(void *id128);
+/* Joins the communicator on the CURRENT device (collective over all ranks: ncclCommInitRank, with NCCL kept to a few
+ * CTAs because its kernels share the GPU with the product).  vnm_mgpu_create_from_comm adopts an ncclComm_t the caller
+ * already has (it stays the caller's). */
+int vnm_mgpu_create(const void *id128, int world, int rank, vnm_mgpu_t *ctx);
+int vnm_mgpu_create_from_comm(void *nccl_comm, vnm_mgpu_t *ctx);
+int vnm_mgpu_destroy(vnm_mgpu_t ctx);
+int vnm_mgpu_info(vnm_mgpu_t ctx, int *world, int *rank);
+/* SMs left free for NCCL's kernels while the chunks of a gathered product travel (default 16; 0 = none). */
+int vnm_mgpu_set_comm_sms(vnm_mgpu_t ctx, int sms);
+/* Replicates the three reference-format arrays from `root` (ncclBroadcast on `stream`); every rank passes buffers of
+ * the sizes vnm_sizes gives, and then calls vnm_prepare on its copy. */
+int vnm_mgpu_broadcast_operand(vnm_mgpu_t ctx, void *values, uint32_t *meta, uint32_t *colloc,
+                               int M, int K, int V, int n, int m, int root, void *stream);
+/* This rank's columns: exactly vnm_spmm_f16 on the shard -- the product has no exchange step. */
+int vnm_mgpu_spmm_shard(vnm_mgpu_t ctx, vnm_handle_t handle, const void *B_shard, int64_t ldb, int n_shard,
+                        const void *bias, void *out, int64_t ldo, int layout, void *stream);
+/* The whole result on every rank: out_full is [N_total, M] fp16 (layout NM, ldo == M), rank r computes rows
+ * [r * N_total / world, (r + 1) * N_total / world) from its B_shard [K, N_total / world] and receives the rest.
+ * The shard is cut into `chunks` column chunks (clamped to 1..16 and to at least 256 columns each); chunk c+1 is
+ * multiplied on `stream` while chunk c is exchanged on the context's second stream, each message landing at its final
+ * rows.  chunks == 1 is the plain form: the product, then one in-place ncclAllGather.  `stream` continues after the last
+ * chunk has arrived.  N_total must be a multiple of 8 x world. */
+int vnm_mgpu_spmm_gathered(vnm_mgpu_t ctx, vnm_handle_t handle, const void *B_shard, int64_t ldb, int N_total,
+                           const void *bias, void *out_full, int64_t ldo, int chunks, void *stream);
 
 #ifdef __cplusplus
 }

@@ -177,3 +177,42 @@ class Reference:
         rc = self.lib.ref_random_init_f16(M, K, V, m, seed, _ptr(values), _ptr(meta), _ptr(cols), nv, nm, nc)
         assert rc == 0
         return values, meta, cols
+
+
+class RefSpatha:
+    """The reference's own Spatha SpMM kernel (legacy mma.sp, compiled for sm_100a from the reference checkout by
+    build_oracle.build_reference_spatha): the second comparator of the GPU parity tests.  Needs a CUDA device.
+    None-safe: use RefSpatha.load(), which returns None where the library was never built."""
+
+    @staticmethod
+    def load(build=True):
+        path = os.path.join(HERE, "_ref", "libvnm_ref_spatha.so")
+        if build:
+            from . import build_oracle
+            path = build_oracle.build_reference_spatha()
+        if not path or not os.path.exists(path):
+            return None
+        return RefSpatha(path)
+
+    def __init__(self, path):
+        self.lib = C.CDLL(path)
+        f = self.lib.ref_spatha_spmm_f16
+        f.restype = C.c_int
+        f.argtypes = [C.c_void_p] * 3 + [C.c_int] * 4 + [C.c_long] * 3 + [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.POINTER(C.c_float)]
+
+    def spmm(self, values, meta, columns, M, K, V, m, B, repeats=0):
+        """Host arrays in the reference format, B [K,N] float16 (N % 64 == 0).  Returns (C [M,N] float16, ms per launch
+        or None)."""
+        ksp, nv, nm, nc = sizes(M, K, V, m)
+        values = np.ascontiguousarray(values, dtype=np.float16)
+        meta = np.ascontiguousarray(meta, dtype=np.uint32)
+        columns = np.ascontiguousarray(columns, dtype=np.uint32)
+        B = np.ascontiguousarray(B, dtype=np.float16)
+        N = B.shape[1]
+        out = np.empty((M, N), dtype=np.float16)
+        ms = C.c_float(0)
+        rc = self.lib.ref_spatha_spmm_f16(_ptr(values), _ptr(meta), _ptr(columns), M, K, V, m, nv, nm, nc, _ptr(B), N, _ptr(out),
+                                          repeats, C.byref(ms))
+        if rc:
+            raise RuntimeError("reference Spatha kernel failed at step %d" % rc)
+        return out, (float(ms.value) if repeats > 0 else None)

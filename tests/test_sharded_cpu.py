@@ -46,9 +46,11 @@ def _worker(rank, world, port, N, q):
         bias = torch.randn(M, generator=g)
         op = ShardedSpmm(M, lambda Bs, b: (A @ Bs).T.contiguous() + (0 if b is None else b), None)
         lo, hi = shard_bounds(N, world, rank)
-        full = op.gathered(B[:, lo:hi].contiguous(), N, bias)
         want = (A @ B).T + bias
-        ok = torch.allclose(full, want, atol=1e-5)
+        ok = True
+        for chunks in (1, 2, 4):      # plain gather, and the chunked exchange pattern the library uses on GPUs
+            full = op.gathered(B[:, lo:hi].contiguous(), N, bias, chunks=chunks)
+            ok = ok and torch.allclose(full, want, atol=1e-5)
         local = op.local(B[:, lo:hi].contiguous(), bias)
         ok = ok and torch.allclose(local, want[lo:hi], atol=1e-5)
         q.put((rank, bool(ok), tuple(full.shape)))
@@ -56,7 +58,17 @@ def _worker(rank, world, port, N, q):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("N", [64, 72])      # equal and unequal shards
+def test_library_shard_arithmetic_rejects_bad_arguments():
+    """vnm_mgpu_shard is pure arithmetic behind the C ABI: usable (and checked) without a GPU or NCCL."""
+    from venom_b200 import capi
+    assert capi.mgpu_shard(32768, 8, 3) == (12288, 16384)
+    assert capi.mgpu_shard(264, 4, 0) == (0, 72) and capi.mgpu_shard(264, 4, 3) == (200, 264)
+    for bad in [(100, 2, 0), (64, 0, 0), (64, 2, 2), (64, 2, -1)]:
+        with pytest.raises(capi.VenomError):
+            capi.mgpu_shard(*bad)
+
+
+@pytest.mark.parametrize("N", [64, 72, 256])      # equal, unequal, and equal shards with several chunks each
 def test_two_rank_gather_gloo(N):
     world = 2
     ctx = mp.get_context("spawn")

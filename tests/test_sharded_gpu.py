@@ -28,7 +28,7 @@ def _worker(rank, world, port, q):
         from oracle.oracle import Oracle
         from venom_b200.sharded import ShardedSpmm, shard_bounds
         from venom_b200.synth import random_dense_b, random_vnm_dense
-        M, K, V, m, N = 256, 1024, 128, 8, 1024
+        M, K, V, m, N = 256, 1024, 128, 8, 4096
         dense, cols, _ = random_vnm_dense(M, K, V, m, seed=1)
         B = random_dense_b(K, N, seed=2)
         orc = Oracle()
@@ -39,11 +39,20 @@ def _worker(rank, world, port, q):
             args = (None, None, None)
         op = ShardedSpmm.from_reference_arrays(*args, M, K, V, m)
         lo, hi = shard_bounds(N, world, rank)
-        full = op.gathered(torch.from_numpy(B[:, lo:hi].copy()).cuda(), N)
-        torch.cuda.synchronize()
         want = orc.spmm(ov, om, cols, M, K, V, m, B, layout=1)
-        bad, _, worst = orc.check(full.cpu().numpy(), want, mode=1, tol=1e-2)
-        q.put((rank, bad, worst))
+        Bs = torch.from_numpy(B[:, lo:hi].copy()).cuda()
+        bad_total, worst = 0, 0.0
+        assert op.ctx is not None                      # the library's own communicator (vnm_mgpu_create)
+        for chunks in (1, 4):                          # product then all-gather; chunked exchange beside the product
+            full = op.gathered(Bs, N, chunks=chunks)
+            torch.cuda.synchronize()
+            bad, _, w = orc.check(full.cpu().numpy(), want, mode=1, tol=1e-2)
+            bad_total += bad
+            worst = max(worst, w)
+        local = op.ctx.spmm_shard(op.prepared, Bs)     # [M, n_shard], no communication
+        bad, _, w = orc.check(local.cpu().numpy(), np.ascontiguousarray(want[lo:hi].T), mode=1, tol=1e-2)
+        assert op.prepared.device_status() == 0
+        q.put((rank, bad_total + bad, max(worst, w)))
     finally:
         dist.destroy_process_group()
 

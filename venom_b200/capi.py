@@ -64,6 +64,26 @@ def lib():
         L.vnm_set_strategy.restype = C.c_int
         L.vnm_set_producer_warps.argtypes = [C.c_void_p, C.c_int]
         L.vnm_set_producer_warps.restype = C.c_int
+        L.vnm_set_max_ctas.argtypes = [C.c_void_p, C.c_int]
+        L.vnm_set_max_ctas.restype = C.c_int
+        L.vnm_handle_info.argtypes = [C.c_void_p] + [C.POINTER(C.c_int)] * 5
+        L.vnm_handle_info.restype = C.c_int
+        ip = C.POINTER(C.c_int)
+        L.vnm_mgpu_shard.argtypes = [C.c_int] * 4 + [ip, ip]
+        L.vnm_mgpu_unique_id.argtypes = [C.c_void_p]
+        L.vnm_mgpu_create.argtypes = [C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_void_p)]
+        L.vnm_mgpu_create_from_comm.argtypes = [C.c_void_p, C.POINTER(C.c_void_p)]
+        L.vnm_mgpu_destroy.argtypes = [C.c_void_p]
+        L.vnm_mgpu_info.argtypes = [C.c_void_p, ip, ip]
+        L.vnm_mgpu_set_comm_sms.argtypes = [C.c_void_p, C.c_int]
+        L.vnm_mgpu_broadcast_operand.argtypes = [C.c_void_p] * 4 + [C.c_int] * 6 + [C.c_void_p]
+        L.vnm_mgpu_spmm_shard.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_void_p, C.c_void_p, C.c_int64,
+                                          C.c_int, C.c_void_p]
+        L.vnm_mgpu_spmm_gathered.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_void_p, C.c_void_p, C.c_int64,
+                                             C.c_int, C.c_void_p]
+        for name in ("vnm_mgpu_shard", "vnm_mgpu_unique_id", "vnm_mgpu_create", "vnm_mgpu_create_from_comm", "vnm_mgpu_destroy",
+                     "vnm_mgpu_info", "vnm_mgpu_set_comm_sms", "vnm_mgpu_broadcast_operand", "vnm_mgpu_spmm_shard", "vnm_mgpu_spmm_gathered"):
+            getattr(L, name).restype = C.c_int
         for name in ("vnm_sizes", "vnm_compress_f16", "vnm_decompress_f16", "vnm_prepare", "vnm_prepared_bytes",
                      "vnm_destroy", "vnm_spmm_f16", "vnm_spmm_f16_host", "vnm_device_status", "vnm_spmm_config"):
             getattr(L, name).restype = C.c_int
@@ -244,7 +264,93 @@ class Prepared:
     def set_producer_warps(self, warps):
         _check(lib().vnm_set_producer_warps(self._h, warps))
 
+    def set_max_ctas(self, n):
+        """Cap on the persistent CTAs of this operand's products (0 = one per SM)."""
+        _check(lib().vnm_set_max_ctas(self._h, n))
+
     def config(self, N):
         v = [C.c_int() for _ in range(5)]
         _check(lib().vnm_spmm_config(self._h, N, *[C.byref(x) for x in v]))
         return dict(zip(("tile_m", "tile_n", "stages", "grid", "smem_bytes"), (int(x.value) for x in v)))
+
+
+def mgpu_shard(N, world, rank, multiple=8):
+    """Half-open column range [lo, hi) of `rank` (vnm_mgpu_shard; pure arithmetic, no GPU needed)."""
+    lo, hi = C.c_int(), C.c_int()
+    _check(lib().vnm_mgpu_shard(N, world, rank, multiple, C.byref(lo), C.byref(hi)))
+    return int(lo.value), int(hi.value)
+
+
+class Mgpu:
+    """Owns a vnm_mgpu_t: this rank's place in the N-sharded launcher (NCCL communicator + exchange stream).
+
+    Mgpu.create(exchange_id) is collective: rank 0 draws the id (Mgpu.unique_id()) and `exchange_id(bytes_or_None)`
+    hands it to every rank (torch.distributed, MPI, a file ... -- the library does not care)."""
+
+    def __init__(self, handle, world, rank):
+        self._c, self.world, self.rank = handle, world, rank
+
+    @staticmethod
+    def unique_id():
+        buf = C.create_string_buffer(128)
+        _check(lib().vnm_mgpu_unique_id(buf))
+        return buf.raw
+
+    @classmethod
+    def create(cls, world, rank, exchange_id):
+        ident = exchange_id(cls.unique_id() if rank == 0 else None)
+        if len(ident) != 128:
+            raise VenomError("the communicator id must be 128 bytes")
+        h = C.c_void_p()
+        _check(lib().vnm_mgpu_create(C.create_string_buffer(bytes(ident), 128), world, rank, C.byref(h)))
+        return cls(h, world, rank)
+
+    @classmethod
+    def create_torch(cls, group=None):
+        """Collective over a torch.distributed group (any backend): the id travels through the group."""
+        import torch.distributed as dist
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+
+        def exchange(ident):
+            box = [ident]
+            dist.broadcast_object_list(box, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
+            return box[0]
+        return cls.create(world, rank, exchange)
+
+    def close(self):
+        if getattr(self, "_c", None) is not None and self._c.value:
+            lib().vnm_mgpu_destroy(self._c)
+            self._c = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def set_comm_sms(self, sms):
+        _check(lib().vnm_mgpu_set_comm_sms(self._c, sms))
+
+    def broadcast_operand(self, values, meta, colloc, M, K, V, m, n=2, root=0):
+        _need_cuda(values, meta, colloc)
+        _check(lib().vnm_mgpu_broadcast_operand(self._c, values.data_ptr(), meta.data_ptr(), colloc.data_ptr(), M, K, V, n, m, root, _stream()))
+
+    def spmm_shard(self, prep, B_shard, bias=None, layout=VNM_LAYOUT_MN, out=None):
+        _need_cuda(B_shard, bias, out)
+        n = B_shard.shape[1]
+        if out is None:
+            out = torch.empty((prep.M, n) if layout == VNM_LAYOUT_MN else (n, prep.M), dtype=torch.float16, device=B_shard.device)
+        _check(lib().vnm_mgpu_spmm_shard(self._c, prep._h, B_shard.data_ptr(), B_shard.stride(0), n, None if bias is None else bias.data_ptr(),
+                                         out.data_ptr(), out.stride(0), layout, _stream()))
+        return out
+
+    def spmm_gathered(self, prep, B_shard, N_total, bias=None, out=None, chunks=4):
+        """Every rank ends with the full [N_total, M] result; the exchange overlaps the product chunk by chunk."""
+        _need_cuda(B_shard, bias, out)
+        if B_shard.dtype != torch.float16 or B_shard.dim() != 2 or B_shard.stride(1) != 1 or B_shard.shape[1] * self.world != N_total:
+            raise VenomError("B shard must be [K, N_total / world] fp16 with unit inner stride")
+        if out is None:
+            out = torch.empty((N_total, prep.M), dtype=torch.float16, device=B_shard.device)
+        _check(lib().vnm_mgpu_spmm_gathered(self._c, prep._h, B_shard.data_ptr(), B_shard.stride(0), N_total,
+                                            None if bias is None else bias.data_ptr(), out.data_ptr(), out.stride(0), chunks, _stream()))
+        return out

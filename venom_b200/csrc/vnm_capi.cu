@@ -148,6 +148,7 @@ struct vnm_prepared_s {
     bool host_pipe_ready;
     int gather_mode;
     int dense_b;       // 1: A re-expressed as 2:4 over all K columns, B read as plain tiles
+    int max_ctas;      // 0 = one persistent CTA per SM, else the cap set by vnm_set_max_ctas
 };
 
 extern "C" {
@@ -305,6 +306,25 @@ int vnm_set_strategy(int strategy)
     return VNM_OK;
 }
 
+int vnm_handle_info(vnm_handle_t h, int *M, int *K, int *V, int *m, int *max_ctas)
+{
+    if (!h) return fail(VNM_ERR_BAD_ARG, "vnm_handle_info: null handle");
+    if (M) *M = h->M;
+    if (K) *K = h->K;
+    if (V) *V = h->V;
+    if (m) *m = h->m;
+    if (max_ctas) *max_ctas = h->max_ctas;
+    return VNM_OK;
+}
+
+int vnm_set_max_ctas(vnm_handle_t h, int max_ctas)
+{
+    if (!h) return fail(VNM_ERR_BAD_ARG, "null handle");
+    if (max_ctas < 0) return fail(VNM_ERR_BAD_ARG, "max_ctas must be >= 0 (got %d)", max_ctas);
+    h->max_ctas = max_ctas;
+    return VNM_OK;
+}
+
 int vnm_set_producer_warps(vnm_handle_t h, int warps)
 {
     if (!h) return fail(VNM_ERR_BAD_ARG, "null handle");
@@ -317,8 +337,8 @@ int vnm_spmm_config(vnm_handle_t h, int N, int *tile_m, int *tile_n, int *stages
 {
     if (!h) return fail(VNM_ERR_BAD_ARG, "null handle");
     SpmmConfig cfg;
-    if (h->dense_b) spmm_dense_b_config(h->M, N, &cfg);
-    else if (!spmm_select_config(h->V, N, h->M, h->producer_warps, &cfg)) return fail(VNM_ERR_UNSUPPORTED, "unsupported V");
+    if (h->dense_b) spmm_dense_b_config(h->M, N, h->max_ctas, &cfg);
+    else if (!spmm_select_config(h->V, N, h->M, h->producer_warps, h->max_ctas, &cfg)) return fail(VNM_ERR_UNSUPPORTED, "unsupported V");
     if (tile_m) *tile_m = h->dense_b ? 2 * TILE_M : TILE_M;
     if (tile_n) *tile_n = cfg.bn;
     if (stages) *stages = cfg.stages;
@@ -356,8 +376,8 @@ static int spmm_impl(vnm_handle_t h, const void *B, int64_t ldb, int N, int b_nk
         return fail(VNM_ERR_BAD_ARG, "vnm_spmm_f16: unknown layout %d", layout);
     }
     SpmmConfig cfg;
-    if (h->dense_b) spmm_dense_b_config(h->M, N, &cfg);
-    else if (!spmm_select_config(h->V, N, h->M, h->producer_warps, &cfg)) return fail(VNM_ERR_UNSUPPORTED, "unsupported V");
+    if (h->dense_b) spmm_dense_b_config(h->M, N, h->max_ctas, &cfg);
+    else if (!spmm_select_config(h->V, N, h->M, h->producer_warps, h->max_ctas, &cfg)) return fail(VNM_ERR_UNSUPPORTED, "unsupported V");
     EncodeTiledFn enc = get_encode_fn();
     if (!enc) return fail(VNM_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
 

@@ -71,7 +71,7 @@ cudaError_t launch_prune(const float *w, int64_t ldw, int M, int K, int V, int m
                          cudaStream_t stream);
 
 // Chooses the tile configuration for (V, N).  Returns false for an unsupported V.
-bool spmm_select_config(int V, int N, int M, int producer_warps, SpmmConfig *cfg);
+bool spmm_select_config(int V, int N, int M, int producer_warps, int max_ctas, SpmmConfig *cfg);  // max_ctas: 0 = one per SM
 // Opt-in to large dynamic shared memory for every kernel instance on the CURRENT device (call once per device).
 cudaError_t spmm_init_kernels();
 cudaError_t launch_spmm(const SpmmConfig &cfg, const CUtensorMap &tmap_rows, const CUtensorMap &tmap_tile, const SpmmParams &p,
@@ -80,7 +80,7 @@ cudaError_t launch_spmm(const SpmmConfig &cfg, const CUtensorMap &tmap_rows, con
 // Dense-B form: 256 x 128 tiles, two accumulators sharing every B stage (vnm_spmm_dense_b.cu).
 cudaError_t spmm_dense_b_init();
 cudaError_t launch_wait_expiry_selftest(int *status, cudaStream_t stream);
-void spmm_dense_b_config(int M, int N, SpmmConfig *cfg);
+void spmm_dense_b_config(int M, int N, int max_ctas, SpmmConfig *cfg);  // max_ctas: 0 = one per SM
 cudaError_t launch_spmm_dense_b(const SpmmConfig &cfg, const CUtensorMap &tmap_tile, const CUtensorMap &tmap_tile2, const CUtensorMap &tmap_out,
                                 const SpmmParams &p, cudaStream_t stream);
 

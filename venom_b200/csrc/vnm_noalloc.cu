@@ -114,7 +114,7 @@ extern "C" int vnm_spmm_f16_noalloc(const void *values, const uint32_t *meta, co
     if (e != cudaSuccess) return nfail(VNM_ERR_CUDA, "re-pack launch: %s", cudaGetErrorString(e));
 
     SpmmConfig cfg;
-    if (!spmm_select_config(V, N, M, 8, &cfg)) return nfail(VNM_ERR_UNSUPPORTED, "unsupported V");
+    if (!spmm_select_config(V, N, M, 8, 0, &cfg)) return nfail(VNM_ERR_UNSUPPORTED, "unsupported V");
     EncodeTiledFn enc = get_encode_fn();
     if (!enc) return nfail(VNM_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
     CUtensorMap tmap_rows, tmap_tile;

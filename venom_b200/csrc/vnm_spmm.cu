@@ -470,7 +470,7 @@ constexpr int kSA = 3, kSB = 4;
 // Tile configurations (128 rows x BN columns with NB * BN = 256, so every B stage is 32 KiB):
 // V=128 -> one block per tile, BN 256; V=64 -> two blocks, BN 128; V=32 -> four blocks, BN 64.
 // cfg->stages carries the number of B-producer warps (4 or 8).
-bool spmm_select_config(int V, int N, int M, int producer_warps, SpmmConfig *cfg)
+bool spmm_select_config(int V, int N, int M, int producer_warps, int max_ctas, SpmmConfig *cfg)
 {
     const int mtiles = (M + TILE_M - 1) / TILE_M;
     const int pb = (producer_warps == 4) ? 4 : 8;
@@ -487,7 +487,8 @@ bool spmm_select_config(int V, int N, int M, int producer_warps, SpmmConfig *cfg
     }
     cfg->smem_bytes = Traits<256, 1, kSA, kSB, 8>::SMEM_BYTES;
     const long long tiles = (long long)mtiles * ((N + cfg->bn - 1) / cfg->bn);
-    const int sms = g_num_sms > 0 ? g_num_sms : 148;
+    int sms = g_num_sms > 0 ? g_num_sms : 148;
+    if (max_ctas > 0 && max_ctas < sms) sms = max_ctas;  // the caller keeps some SMs free (e.g. for a collective that runs beside the product)
     cfg->grid = (int)(tiles < sms ? tiles : sms);
     return true;
 }

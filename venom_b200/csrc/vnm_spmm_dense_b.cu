@@ -422,11 +422,12 @@ cudaError_t spmm_dense_b_init()
     return cudaDeviceGetAttribute(&g_num_sms_db, cudaDevAttrMultiProcessorCount, dev);
 }
 
-void spmm_dense_b_config(int M, int N, SpmmConfig *cfg)
+void spmm_dense_b_config(int M, int N, int max_ctas, SpmmConfig *cfg)
 {
     const int mtiles = (M + TILE_M - 1) / TILE_M;
     const long long ntiles = (N + BN - 1) / BN;
-    const int sms = g_num_sms_db > 0 ? g_num_sms_db : 148;
+    int sms = g_num_sms_db > 0 ? g_num_sms_db : 148;
+    if (max_ctas > 0 && max_ctas < sms) sms = max_ctas;
     // Two row tiles per CTA tile take in 100 KiB per k-tile (about 1900 clocks), one takes in 82 KiB (about 1400) for
     // half the outputs: the single form only pays when the double form would leave most of the GPU idle.
     const long long t2 = (long long)((mtiles + 1) / 2) * ntiles, t1 = (long long)mtiles * ntiles;

@@ -1,4 +1,5 @@
-"""N-sharded multi-GPU launcher for the V:N:M SpMM (one process per GPU, torch.distributed).
+"""N-sharded multi-GPU launcher for the V:N:M SpMM (one process per GPU): a thin caller of the library's
+vnm_mgpu_* entry points (NCCL inside the library) with torch.distributed as the plumbing that starts the ranks.
 
 Column c of C = A * B depends only on column c of B, so the dense operand and the output are split by
 columns (N) across the ranks; the sparse operand is replicated (broadcast once from rank 0).  There is
@@ -6,9 +7,11 @@ no communication inside the product.  An all-gather over the process group is is
 caller asks for a replicated output; in the [N, M] layout an N-shard is a contiguous block of rows, so
 the gather writes straight into the full output.
 
-The sharding arithmetic and the collectives are independent of the device: with backend "gloo" and
-CPU tensors the same class runs with `compute=None` replaced by a caller-supplied function, which is how
-the host-side logic is tested without GPUs.
+On GPUs (`from_reference_arrays`) the broadcast of the sparse operand, the shard product and the gathered product
+-- chunked, the exchange of one chunk overlapping the product of the next -- all run inside the library.  The
+same class also runs with backend "gloo" and CPU tensors when it is given a plain `compute` function: the
+sharding arithmetic and the exchange pattern are then exercised with torch collectives, which is how the host-side
+logic is tested without GPUs (the arithmetic itself is the library's: vnm_mgpu_shard).
 """
 import torch
 import torch.distributed as dist
@@ -19,11 +22,8 @@ def shard_bounds(N, world, rank, multiple=8):
     boundary a multiple of `multiple` (the kernel needs N % 8 == 0 per shard)."""
     if N % multiple:
         raise ValueError("N must be a multiple of %d" % multiple)
-    units = N // multiple
-    base, extra = divmod(units, world)
-    lo = rank * base + min(rank, extra)
-    hi = lo + base + (1 if rank < extra else 0)
-    return lo * multiple, hi * multiple
+    from . import capi
+    return capi.mgpu_shard(N, world, rank, multiple)
 
 
 class ShardedSpmm:
@@ -54,29 +54,64 @@ class ShardedSpmm:
             values = torch.empty(nv, dtype=torch.float16, device=device)
             metadata = torch.empty(nm, dtype=torch.int32, device=device)
             columns = torch.empty(nc, dtype=torch.int32, device=device)
+        ctx = None
         if dist.is_initialized() and dist.get_world_size(group) > 1:
-            for t in (values, metadata, columns):
-                dist.broadcast(t, src=src, group=group)
+            ctx = capi.Mgpu.create_torch(group)
+            ctx.broadcast_operand(values, metadata, columns, M, K, V, m, n, root=src)
         prep = capi.Prepared(values, metadata, columns, M, K, V, m, n)
         obj = cls(M, lambda B, bias: prep.spmm(B, bias=bias, layout=capi.VNM_LAYOUT_NM), group)
         obj.prepared = prep
+        obj.ctx = ctx
         return obj
 
     def local(self, B_shard, bias=None):
         """Product of this rank's shard: [n_shard, M]."""
         return self.compute(B_shard, bias)
 
-    def gathered(self, B_shard, N, bias=None):
-        """Replicated output [N, M]: every rank computes its rows and all-gathers the rest.  The shard
-        of rank r is rows shard_bounds(N, world, r) of the result."""
-        out = torch.empty((N, self.M), dtype=B_shard.dtype, device=B_shard.device)
+    ctx = None        # capi.Mgpu when the ranks run on GPUs
+    prepared = None
+
+    def gathered(self, B_shard, N, bias=None, chunks=4, out=None):
+        """Replicated output [N, M]: every rank computes its rows and receives the rest.  The shard of rank r is rows
+        shard_bounds(N, world, r) of the result.  On GPUs with equal shards this is vnm_mgpu_spmm_gathered: the shard
+        goes through in `chunks` column chunks, each exchanged while the next is multiplied (chunks=1: product, then
+        one in-place all-gather)."""
         lo, hi = shard_bounds(N, self.world, self.rank)
+        if self.ctx is not None and N % (8 * self.world) == 0:
+            if B_shard.shape[1] != hi - lo:
+                raise ValueError("B shard has %d columns, expected %d" % (B_shard.shape[1], hi - lo))
+            return self.ctx.spmm_gathered(self.prepared, B_shard, N, bias=bias, out=out, chunks=chunks)
+        if out is None:
+            out = torch.empty((N, self.M), dtype=B_shard.dtype, device=B_shard.device)
         if B_shard.shape[1] != hi - lo:
             raise ValueError("B shard has %d columns, expected %d" % (B_shard.shape[1], hi - lo))
+        bounds = [shard_bounds(N, self.world, r) for r in range(self.world)]
+        equal = len({b[1] - b[0] for b in bounds}) == 1
+        if self.world > 1 and equal and chunks > 1:
+            # The library's pattern with torch point-to-point messages (what the CPU tests run): every chunk is
+            # computed, then sent to every peer and the peers' chunks are received at their final rows; the
+            # requests of chunk c are only waited for after chunk c+1 has been computed.
+            ns = hi - lo
+            w = -(-(-(-ns // chunks)) // 8) * 8
+            pending = []
+            for c0 in range(0, ns, w):
+                cw = min(w, ns - c0)
+                out[lo + c0:lo + c0 + cw] = self.compute(B_shard[:, c0:c0 + cw].contiguous(), bias)
+                for req in pending:
+                    req.wait()
+                ops = []
+                for r in range(self.world):
+                    if r == self.rank:
+                        continue
+                    peer = dist.get_global_rank(self.group, r) if self.group is not None else r
+                    ops.append(dist.P2POp(dist.isend, out[lo + c0:lo + c0 + cw], peer, self.group))
+                    ops.append(dist.P2POp(dist.irecv, out[r * ns + c0:r * ns + c0 + cw], peer, self.group))
+                pending = dist.batch_isend_irecv(ops)
+            for req in pending:
+                req.wait()
+            return out
         out[lo:hi] = self.compute(B_shard, bias)
         if self.world > 1:
-            bounds = [shard_bounds(N, self.world, r) for r in range(self.world)]
-            equal = len({b[1] - b[0] for b in bounds}) == 1
             if equal and dist.get_backend(self.group) == "nccl":
                 # in place: this rank's rows already sit at their final position inside `out`
                 dist.all_gather_into_tensor(out, out[lo:hi], group=self.group)
