@@ -56,6 +56,11 @@ class Oracle:
     def num_threads(self):
         return int(self.lib.vnm_oracle_num_threads())
 
+    def set_num_threads(self, n):
+        """Explicit OpenMP thread count (overrides an inherited OMP_NUM_THREADS); returns the count in effect."""
+        self.lib.vnm_oracle_set_num_threads(int(n))
+        return self.num_threads()
+
     def compress(self, dense, columns, V, m, mask=None):
         """dense: [M,K] float16; columns: uint32 column-loc.  Returns (values f16, meta u32, violations)."""
         M, K = dense.shape

@@ -8,7 +8,9 @@
 //
 // Call sequence = what the reference harness does (src/spmm/spatha_spmm.cpp:24-38,60-90): BlockwiseSpMatrix
 // init_sparse(brow = 4, mbrow = 32, bm = V) + transform_and_sync_device, SpmmNMInitFn / SpmmNMExecFn of one
-// tile configuration per V taken from the reference's own instantiation list (spmm_library_decl.h).
+// tile configuration per V: block V x 64 x 32, warp 32 x 64 x 32, mma 16 x 8 x 32, 2 stages -- the first
+// configuration the reference's own benchmark scripts run for each V (benchmark/run_ablation2.sh:21,
+// run_spmm_spatha.sh); a warp tile narrower than the block tile in N gives wrong results with the reference kernel.
 // The dense operand is allocated with twice its size, as the reference's dataset does
 // (src/dataset/dataset.cpp:81), because the kernel's zero-fill predicate `k > K` (blockwise_kernel.h:875)
 // lets a padded group read row K.
@@ -76,7 +78,7 @@ int ref_spatha_spmm_f16(const uint16_t *values, const uint32_t *meta, const uint
     cudaMemset(D, 0, d_bytes);
     cudaMemcpy(B, B_host, b_bytes, cudaMemcpyHostToDevice);
     int rc;
-    if (V == 128) rc = run<128, 64, 32, 64, 32, 32>(spmat, N, B, D, repeats, ms);
+    if (V == 128) rc = run<128, 64, 32, 32, 64, 32>(spmat, N, B, D, repeats, ms);
     else if (V == 64) rc = run<64, 64, 32, 32, 64, 32>(spmat, N, B, D, repeats, ms);
     else rc = run<32, 64, 32, 32, 64, 32>(spmat, N, B, D, repeats, ms);
     if (rc == 0 && cudaMemcpy(D_host, D, d_bytes, cudaMemcpyDeviceToHost) != cudaSuccess) rc = 6;

@@ -352,6 +352,17 @@ int vnm_oracle_prune(const float *absw, int M, int K, int V, int n, int m, int32
     return 0;
 }
 
+/* Sets the number of OpenMP threads of the host routines explicitly (launchers such as torchrun export
+ * OMP_NUM_THREADS=1, which would otherwise silently make the timed CPU baseline single-threaded). */
+void vnm_oracle_set_num_threads(int n)
+{
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 int vnm_oracle_num_threads(void)
 {
 #ifdef _OPENMP
