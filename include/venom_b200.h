@@ -166,8 +166,11 @@ int vnm_device_status(vnm_handle_t handle, int *status, void *stream);
 int vnm_selftest_wait_expiry(vnm_handle_t handle, void *stream);
 
 /* Ablation switches.
- * Gather mode: how the selected rows of B reach shared memory.  0 = TMA tile::gather4, one group of four
- * rows per instruction (default for m > 4); 1 = plain TMA tiles of 64 consecutive rows, which is exact
+ * Gather mode: how the selected rows of B reach shared memory.  3 = 16-byte asynchronous copies (cp.async) issued
+ * per thread from the row table, written straight into the swizzled operand layout (default for m > 4; the staging
+ * the reference uses, include/spatha/block_sparse/spmm/blockwise_kernel.h:868-881); 0 = TMA tile::gather4, one
+ * group of four rows per instruction (about half the rate: bound by the TMA instruction rate); 1 = plain TMA tiles
+ * of 64 consecutive rows, which is exact
  * for m == 4 (every row is selected; the default there) and otherwise removes the column-loc
  * indirection exactly like the reference's compile-time IDEAL_KERNEL experiment
  * (include/spatha/block_sparse/spmm/blockwise_kernel.h:328-642, row = nz_block_idx % 4 at :536);

@@ -257,7 +257,7 @@ class Prepared:
         return int(st.value)
 
     def set_gather_mode(self, mode):
-        """0 = TMA gather4 (default for m > 4), 1 = 64-row TMA tiles (exact for m == 4, otherwise the
+        """3 = per-thread 16-byte cp.async copies (default for m > 4), 0 = TMA gather4, 1 = 64-row TMA tiles (exact for m == 4, otherwise the
         "no column-loc" ablation), 2 = no B loads (timing floor only)."""
         _check(lib().vnm_set_gather_mode(self._h, mode))
 

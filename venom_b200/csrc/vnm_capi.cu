@@ -250,7 +250,7 @@ int vnm_prepare_as(const void *values, const uint32_t *meta, const uint32_t *col
     } else {
         h->ktiles = (int)((h->Ksp + KT_COMP - 1) / KT_COMP);
         h->nb = TILE_M / V;
-        h->gather_mode = (m == 4) ? GATHER_CONTIG : GATHER_TMA4;  // with m == 4 every row of B is selected
+        h->gather_mode = (m == 4) ? GATHER_CONTIG : GATHER_CPASYNC;  // with m == 4 every row of B is selected
     }
     h->vblocks_padded = h->mtiles * h->nb;
     h->producer_warps = 8;
@@ -292,8 +292,8 @@ int vnm_destroy(vnm_handle_t h)
 int vnm_set_gather_mode(vnm_handle_t h, int mode)
 {
     if (!h) return fail(VNM_ERR_BAD_ARG, "null handle");
-    if (mode != GATHER_TMA4 && mode != GATHER_CONTIG && mode != GATHER_NONE) return fail(VNM_ERR_BAD_ARG, "unknown gather mode %d", mode);
-    if (h->dense_b && mode == GATHER_TMA4) return fail(VNM_ERR_BAD_ARG, "this operand was prepared in dense-B form: it has no gather");
+    if (mode != GATHER_TMA4 && mode != GATHER_CONTIG && mode != GATHER_NONE && mode != GATHER_CPASYNC) return fail(VNM_ERR_BAD_ARG, "unknown gather mode %d", mode);
+    if (h->dense_b && (mode == GATHER_TMA4 || mode == GATHER_CPASYNC)) return fail(VNM_ERR_BAD_ARG, "this operand was prepared in dense-B form: it has no gather");
     h->gather_mode = mode;
     return VNM_OK;
 }
@@ -446,6 +446,8 @@ static int spmm_impl(vnm_handle_t h, const void *B, int64_t ldb, int N, int b_nk
     p.status = h->status;
     p.gather_mode = h->gather_mode;
     p.total_tiles = p.mtiles * p.ntiles;
+    p.B = (const __half *)B;
+    p.ldb = ldb;
     p.b_nk = b_nk;
     p.b_wide_ok = h->tm_wide ? 1 : 0;
     if (h->dense_b) {

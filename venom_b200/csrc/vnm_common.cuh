@@ -168,6 +168,18 @@ __device__ __forceinline__ void cp_async_8(uint32_t saddr, const void *gsrc)
 {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(saddr), "l"(gsrc) : "memory");
 }
+// 16-byte asynchronous copy global -> shared that bypasses L1; src_bytes = 16 copies, 0 writes zeros (src is not read).
+__device__ __forceinline__ void cp_async_16_zfill(uint32_t saddr, const void *gsrc, uint32_t src_bytes)
+{
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(saddr), "l"(gsrc), "r"(src_bytes) : "memory");
+}
+// Deferred arrival: the barrier receives one arrival (already counted in its initial count) once every asynchronous
+// copy this thread has issued so far has completed.
+__device__ __forceinline__ void cp_async_mbar_arrive_noinc(uint64_t *bar)
+{
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int kPending>
 __device__ __forceinline__ void cp_async_wait()

@@ -28,16 +28,19 @@ struct SpmmParams {
     int *status;          // device status word
     int gather_mode;      // GATHER_* below
     int total_tiles;      // mtiles * ntiles
+    const __half *B;      // gather kernel, GATHER_CPASYNC: the dense operand [K, N] itself (row pieces are copied by address)
+    int64_t ldb;
     int b_nk;             // dense-B kernel only: the dense operand is given as [N, K] row-major (K contiguous)
     int b_wide_ok;        // dense-B kernel only: the 4-D tensor map exists (column tiles with 256 columns inside N use one box per stage)
 };
 
 // How the producer warps bring the selected rows of B into shared memory.
 enum : int {
-    GATHER_TMA4 = 0,    // TMA tile::gather4, four rows (one group) per instruction (default)
+    GATHER_TMA4 = 0,    // TMA tile::gather4, four rows (one group) per instruction
     GATHER_CONTIG = 1,  // plain TMA tiles of 64 consecutive rows: exact when m == 4 (every row is
                         // selected), otherwise an ablation that drops the column-loc indirection
-    GATHER_NONE = 2     // ablation only: B is not loaded at all (results are meaningless)
+    GATHER_NONE = 2,    // ablation only: B is not loaded at all (results are meaningless)
+    GATHER_CPASYNC = 3  // per-thread 16-byte asynchronous copies of the selected rows (default for m > 4)
 };
 
 struct SpmmConfig {

@@ -155,7 +155,9 @@ __global__ void __launch_bounds__(Traits<BN, NB, SA, SB, PB>::NUM_THREADS, 1)
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < SA; s++) { mbar_init(&a_full[s], 1); mbar_init(&a_empty[s], 1); }
-        for (int s = 0; s < SB; s++) { mbar_init(&b_full[s], 1); mbar_init(&b_empty[s], 1); }
+        // a B stage is complete after one arrival with a byte count (TMA modes) or after one deferred arrival of every
+        // producer thread (per-thread 16-byte asynchronous copies)
+        for (int s = 0; s < SB; s++) { mbar_init(&b_full[s], gmode == GATHER_CPASYNC ? PB * 32 : 1); mbar_init(&b_empty[s], 1); }
         for (int s = 0; s < T::SP; s++) mbar_init(&kdone[s], 1);
         for (int s = 0; s < T::SR; s++) mbar_init(&kready[s], 2);  // metadata copy done + operands landed
         mbar_init(acc_full_bar, 1);
@@ -200,6 +202,64 @@ __global__ void __launch_bounds__(Traits<BN, NB, SA, SB, PB>::NUM_THREADS, 1)
         // Every producer warp takes part in every stage (GATHERS / PB of its lanes issue one load each),
         // so each lane meets the ring slots strictly in order and the phase parity stays unambiguous.
         // The row numbers of the next stage are fetched before waiting for the current slot.
+        if (gmode == GATHER_CPASYNC) {
+            // ---- per-thread 16-byte asynchronous copies driven by the row table ----
+            // A stage holds NB blocks x 64 gathered rows x BN columns = 2048 pieces of 16 bytes; thread t copies the
+            // pieces (column piece cc = t % CPR, flattened row t / CPR + i * RPP), so a warp reads whole rows of B
+            // (512 contiguous bytes at BN = 256) and writes them in the 128-byte-swizzled N-major operand layout.
+            // The TMA gather (four 128-byte row pieces per instruction) is limited by its instruction rate, about a
+            // third of what the SM can take in; plain asynchronous copies have no such limit.
+            constexpr int NT = PB * 32;           // producer threads
+            constexpr int CPR = BN / 8;           // 16-byte pieces per row of a block
+            constexpr int RPP = NT / CPR;         // flattened rows covered by one pass of all threads
+            constexpr int PASSES = NB * BS_ROWS / RPP;
+            static_assert(NT % CPR == 0 && (NB * BS_ROWS) % RPP == 0 && PASSES >= 1, "producer threads do not tile a B stage");
+            const int t = (warp - 1) * 32 + lane;
+            const int cc = t % CPR, fr0 = t / CPR;
+            const int *rows_i32 = reinterpret_cast<const int *>(p.rows);
+            const __half *Bg = p.B;
+            int rcur[PASSES], rnxt[PASSES];
+            auto load_rows = [&](int tl, int l, int(&dst)[PASSES]) {
+                const int mt = tl % p.mtiles;
+#pragma unroll
+                for (int i = 0; i < PASSES; i++) {
+                    const int fr = fr0 + i * RPP, b = fr / BS_ROWS, r = fr % BS_ROWS;
+                    dst[i] = __ldg(rows_i32 + ((size_t)(mt * NB + b) * p.ktiles * KT_GROUPS) * 4 + (size_t)l * BS_ROWS + r);
+                }
+            };
+            int j = 0, tile = blockIdx.x, jl = 0;
+            bool valid = tile < p.total_tiles;
+            if (valid) load_rows(tile, jl, rcur);
+            while (valid) {
+                int ntile = tile, njl = jl + 1;
+                if (njl == bstages_per_tile) { njl = 0; ntile += gridDim.x; }
+                const bool nvalid = ntile < p.total_tiles;
+                if (nvalid) load_rows(ntile, njl, rnxt);
+                const int s = j % SB;
+                if (j >= SB) {
+                    const int kd = (j - SB) >> 1;  // slot s was last used by stage j - SB, a half of k-tile (j - SB) / 2
+                    if (!wait_one(&kdone[kd % T::SP], (uint32_t)(kd / T::SP) & 1u, abort_flag, p.status, DEV_TIMEOUT_PRODUCER)) break;
+                }
+                const uint32_t st = smem_u32(b_ring + s * T::B_STAGE_BYTES);
+                const int col = (tile / p.mtiles) * BN + cc * 8;
+                const bool col_ok = col < p.N;  // N % 8 == 0: a piece lies entirely inside or outside
+#pragma unroll
+                for (int i = 0; i < PASSES; i++) {
+                    const int fr = fr0 + i * RPP, b = fr / BS_ROWS, r = fr % BS_ROWS;
+                    const int row = rcur[i];
+                    const bool ok = col_ok && row < p.K;  // padding rows (row == K) and columns past N read as zeros
+                    const __half *src = ok ? Bg + (size_t)row * p.ldb + col : Bg;
+                    const uint32_t dst = st + b * T::B_BLOCK_BYTES + (cc >> 3) * T::B_CHUNK_BYTES + r * 128 + (((cc & 7) ^ (r & 7)) << 4);
+                    cp_async_16_zfill(dst, src, ok ? 16u : 0u);
+                }
+                cp_async_mbar_arrive_noinc(&b_full[s]);  // arrives once this thread's copies have landed
+#pragma unroll
+                for (int i = 0; i < PASSES; i++) rcur[i] = rnxt[i];
+                tile = ntile; jl = njl; valid = nvalid; ++j;
+            }
+            cp_async_wait_all();  // nothing of this thread is in flight when the CTA leaves (also on the abort path)
+            __syncwarp();
+        } else {
         const int pw = warp - 1;
         constexpr int ACTIVE = T::GATHERS / PB;  // lanes of this warp that issue gather4 loads
         const bool leader = (pw == 0 && lane == 0);
@@ -252,6 +312,7 @@ __global__ void __launch_bounds__(Traits<BN, NB, SA, SB, PB>::NUM_THREADS, 1)
             }
         }
         __syncwarp();
+        }
     } else if (warp == T::SEQ_WARP) {
         // ---------------- sequencer (one thread) ----------------
         // Takes every wait except one off the MMA issuer: per k-tile it waits for the value/metadata block,
@@ -276,7 +337,10 @@ __global__ void __launch_bounds__(Traits<BN, NB, SA, SB, PB>::NUM_THREADS, 1)
                     const int j = 2 * it + h;
                     if (!wait_one(&b_full[j % SB], (uint32_t)(j / SB) & 1u, abort_flag, p.status, DEV_TIMEOUT_MMA)) { alive = false; break; }
                 }
-                if (alive) mbar_arrive(&kready[it % T::SR]);
+                if (alive) {
+                    fence_proxy_async();  // stages written by per-thread asynchronous copies are read by the tensor core's proxy
+                    mbar_arrive(&kready[it % T::SR]);
+                }
             }
         }
         __syncwarp();
