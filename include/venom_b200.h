@@ -177,6 +177,11 @@ int vnm_selftest_wait_expiry(vnm_handle_t handle, void *stream);
  * 2 = B is not loaded at all (timing floor; results are meaningless).
  * Producer warps: 4 or 8 warps issue the gather loads (default 8). */
 int vnm_set_gather_mode(vnm_handle_t handle, int mode);
+/* Epilogue of the V:N:M (gather) form for layout MN: 0 = results staged in shared memory and stored as full 128-bit
+ * sectors (default); 1 = every thread stores its own row in 32-bit words, the reference's OUT_32B experiment
+ * (include/spatha/block_sparse/common/epilogue.h:34-61, blockwise_kernel.h:911-943).  VNM_ERR_UNSUPPORTED for operands
+ * held in dense-B form, whose epilogue leaves through TMA stores. */
+int vnm_set_epilogue(vnm_handle_t handle, int mode);
 
 /* How vnm_prepare lays the sparse operand out for the kernel (process-wide, applies to later calls):
  *   AUTO     pick per (V, m) from measurements on B200 (default);

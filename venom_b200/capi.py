@@ -64,6 +64,8 @@ def lib():
         L.vnm_set_strategy.restype = C.c_int
         L.vnm_set_producer_warps.argtypes = [C.c_void_p, C.c_int]
         L.vnm_set_producer_warps.restype = C.c_int
+        L.vnm_set_epilogue.argtypes = [C.c_void_p, C.c_int]
+        L.vnm_set_epilogue.restype = C.c_int
         L.vnm_set_max_ctas.argtypes = [C.c_void_p, C.c_int]
         L.vnm_set_max_ctas.restype = C.c_int
         L.vnm_handle_info.argtypes = [C.c_void_p] + [C.POINTER(C.c_int)] * 5
@@ -263,6 +265,10 @@ class Prepared:
 
     def set_producer_warps(self, warps):
         _check(lib().vnm_set_producer_warps(self._h, warps))
+
+    def set_epilogue(self, mode):
+        """0 = staged 128-bit stores (default), 1 = 32-bit stores per thread (ablation; gather form, layout MN)."""
+        _check(lib().vnm_set_epilogue(self._h, mode))
 
     def set_max_ctas(self, n):
         """Cap on the persistent CTAs of this operand's products (0 = one per SM)."""

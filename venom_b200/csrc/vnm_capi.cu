@@ -148,6 +148,7 @@ struct vnm_prepared_s {
     bool host_pipe_ready;
     int gather_mode;
     int dense_b;       // 1: A re-expressed as 2:4 over all K columns, B read as plain tiles
+    int out32;         // ablation: 32-bit epilogue stores (gather form, layout MN)
     int max_ctas;      // 0 = one persistent CTA per SM, else the cap set by vnm_set_max_ctas
 };
 
@@ -306,6 +307,15 @@ int vnm_set_strategy(int strategy)
     return VNM_OK;
 }
 
+int vnm_set_epilogue(vnm_handle_t h, int mode)
+{
+    if (!h) return fail(VNM_ERR_BAD_ARG, "null handle");
+    if (mode != 0 && mode != 1) return fail(VNM_ERR_BAD_ARG, "unknown epilogue mode %d", mode);
+    if (mode == 1 && h->dense_b) return fail(VNM_ERR_UNSUPPORTED, "the 32-bit epilogue exists for the V:N:M (gather) form only; this operand is held in dense-B form");
+    h->out32 = mode;
+    return VNM_OK;
+}
+
 int vnm_handle_info(vnm_handle_t h, int *M, int *K, int *V, int *m, int *max_ctas)
 {
     if (!h) return fail(VNM_ERR_BAD_ARG, "vnm_handle_info: null handle");
@@ -448,6 +458,7 @@ static int spmm_impl(vnm_handle_t h, const void *B, int64_t ldb, int N, int b_nk
     p.total_tiles = p.mtiles * p.ntiles;
     p.B = (const __half *)B;
     p.ldb = ldb;
+    p.out32 = h->out32;
     p.b_nk = b_nk;
     p.b_wide_ok = h->tm_wide ? 1 : 0;
     if (h->dense_b) {

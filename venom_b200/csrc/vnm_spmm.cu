@@ -470,7 +470,16 @@ __global__ void __launch_bounds__(Traits<BN, NB, SA, SB, PB>::NUM_THREADS, 1)
                         }
                     }
                 }
-                if (p.layout == 0) {
+                if (p.layout == 0 && p.out32) {
+                    // ablation (the reference's OUT_32B build, common/epilogue.h:34-61): every lane stores its own row
+                    // in 32-bit words, 32 rows per instruction
+                    if (row_ok) {
+                        uint32_t *dst = reinterpret_cast<uint32_t *>(p.out + row * p.ldo + n0 + part * PART);
+#pragma unroll
+                        for (int jj = 0; jj < PART / 2; jj++)
+                            if (n0 + part * PART + 2 * jj + 2 <= p.N) dst[jj] = pk[jj];
+                    }
+                } else if (p.layout == 0) {
                     // [M,N]: a lane holds 64 columns of ONE row, so a 16-byte store per lane would touch 32 rows with half
                     // a sector each.  The warp's 32 rows x 32 columns go through its own 2 KiB of shared memory instead
                     // (16-byte pieces XOR-swizzled, conflict-free both ways) and leave as full sectors: four lanes per row,
