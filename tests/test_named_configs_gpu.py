@@ -131,3 +131,34 @@ def test_gpt3_layer_shapes_one_sequence_shard(capi, oracle, mk):
     assert prep.device_status() == 0
     _check_rows(oracle, outT, 1, values, meta, colloc, M, K, V, m, B, bias=bias, nrows=32, seed=2)
     _check_column_sums(dense, B, outT, 1, bias=bias)
+
+
+PAIR_CASES = [(1024, 1024, 64, 8, 17000), (2048, 512, 128, 4, 9000), (512, 4096, 32, 16, 18000), (4096, 1024, 128, 8, 4808)]
+
+
+@pytest.mark.parametrize("shape", PAIR_CASES, ids=lambda p: "%dx%d_V%d_2:%d_N%d" % p)
+def test_two_sm_kernel_matches_single_sm_kernel_and_oracle(capi, oracle, shape):
+    """Dense-B form on pairs of SMs (cta_group::2, each CTA loading half of every B stage) against the single-SM kernel:
+    same MMAs in the same order, so the bits must be identical -- [M,N], [N,M] + bias, and the [N,K] dense operand --
+    with a ragged last column tile; and against the CPU oracle on sampled rows."""
+    import torch
+    M, K, V, m, N = shape
+    dense, colloc, values, meta, B = _operands(capi, M, K, V, m, N, seed=M + 2 * K + N)
+    prep = capi.Prepared(values, meta, colloc, M, K, V, m, strategy=capi.STRATEGY_DENSE_B)
+    assert prep.dense_b_form()
+    assert prep.config(N)["tile_m"] == 512, "the pair kernel was expected to be chosen for this shape"
+    bias = (torch.rand(M, device="cuda") - 0.5).half()
+    bt = B.t().contiguous()
+    pair = [prep.spmm(B), prep.spmm(B, bias=bias, layout=capi.VNM_LAYOUT_NM), prep.spmm_nk(bt, bias=bias, layout=capi.VNM_LAYOUT_NM),
+            prep.spmm_nk(bt, layout=capi.VNM_LAYOUT_MN)]
+    assert prep.device_status() == 0
+    prep.set_pair_mode(0)
+    assert prep.config(N)["tile_m"] in (128, 256)
+    single = [prep.spmm(B), prep.spmm(B, bias=bias, layout=capi.VNM_LAYOUT_NM), prep.spmm_nk(bt, bias=bias, layout=capi.VNM_LAYOUT_NM),
+              prep.spmm_nk(bt, layout=capi.VNM_LAYOUT_MN)]
+    assert prep.device_status() == 0
+    for a, b in zip(pair, single):
+        assert torch.equal(a, b)
+    _check_rows(oracle, pair[0], 0, values, meta, colloc, M, K, V, m, B)
+    _check_rows(oracle, pair[1], 1, values, meta, colloc, M, K, V, m, B, bias=bias)
+    _check_column_sums(dense, B, pair[0], 0)

@@ -32,7 +32,7 @@ def _stale(target, sources):
 
 
 def _sources():
-    cu = [os.path.join(CSRC, f) for f in ("vnm_format.cu", "vnm_prune.cu", "vnm_spmm.cu", "vnm_spmm_dense_b.cu", "vnm_capi.cu", "vnm_noalloc.cu", "vnm_mgpu.cu")]
+    cu = [os.path.join(CSRC, f) for f in ("vnm_format.cu", "vnm_prune.cu", "vnm_spmm.cu", "vnm_spmm_dense_b.cu", "vnm_spmm_dense_b2.cu", "vnm_capi.cu", "vnm_noalloc.cu", "vnm_mgpu.cu")]
     hdr = [os.path.join(CSRC, f) for f in ("vnm_common.cuh", "vnm_internal.h")] + [os.path.join(ROOT, "include", "venom_b200.h")]
     return cu, hdr
 

@@ -64,6 +64,8 @@ def lib():
         L.vnm_set_strategy.restype = C.c_int
         L.vnm_set_producer_warps.argtypes = [C.c_void_p, C.c_int]
         L.vnm_set_producer_warps.restype = C.c_int
+        L.vnm_set_pair_mode.argtypes = [C.c_void_p, C.c_int]
+        L.vnm_set_pair_mode.restype = C.c_int
         L.vnm_set_epilogue.argtypes = [C.c_void_p, C.c_int]
         L.vnm_set_epilogue.restype = C.c_int
         L.vnm_set_max_ctas.argtypes = [C.c_void_p, C.c_int]
@@ -265,6 +267,10 @@ class Prepared:
 
     def set_producer_warps(self, warps):
         _check(lib().vnm_set_producer_warps(self._h, warps))
+
+    def set_pair_mode(self, mode):
+        """Dense-B form: 1 = two-SM (cta_group::2) kernel where it applies (default), 0 = single-SM kernel only."""
+        _check(lib().vnm_set_pair_mode(self._h, mode))
 
     def set_epilogue(self, mode):
         """0 = staged 128-bit stores (default), 1 = 32-bit stores per thread (ablation; gather form, layout MN)."""

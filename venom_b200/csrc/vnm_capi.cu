@@ -93,6 +93,7 @@ int ensure_kernels_ready(int *device_out)
     if (!g_kernels_ready[dev]) {
         VNM_CUDA(spmm_init_kernels(), "cudaFuncSetAttribute(max dynamic shared memory)");
         VNM_CUDA(spmm_dense_b_init(), "cudaFuncSetAttribute(max dynamic shared memory)");
+        VNM_CUDA(spmm_dense_b_pair_init(), "cudaFuncSetAttribute(max dynamic shared memory)");
         g_kernels_ready[dev] = true;
     }
     if (device_out) *device_out = dev;
@@ -131,6 +132,7 @@ struct vnm_prepared_s {
     int64_t tm_ldb;
     int tm_N;
     int tm_nk;
+    int tm_pair;             // the cached maps are the pair kernel's (half stages)
     bool tm_valid;
     CUtensorMap tmap_rows;
     CUtensorMap tmap_tile;
@@ -149,6 +151,7 @@ struct vnm_prepared_s {
     int gather_mode;
     int dense_b;       // 1: A re-expressed as 2:4 over all K columns, B read as plain tiles
     int out32;         // ablation: 32-bit epilogue stores (gather form, layout MN)
+    int pair_mode;     // dense-B form: 1 = use the two-SM (cta_group::2) kernel where it applies (default), 0 = never
     int max_ctas;      // 0 = one persistent CTA per SM, else the cap set by vnm_set_max_ctas
 };
 
@@ -255,6 +258,7 @@ int vnm_prepare_as(const void *values, const uint32_t *meta, const uint32_t *col
     }
     h->vblocks_padded = h->mtiles * h->nb;
     h->producer_warps = 8;
+    h->pair_mode = 1;
     h->device = dev_now;
     cudaError_t e = cudaMalloc(&h->am, (size_t)h->mtiles * h->ktiles * AM_BLOCK_BYTES);
     if (e == cudaSuccess) e = cudaMalloc(&h->rows, (size_t)h->vblocks_padded * h->ktiles * KT_GROUPS * sizeof(int4));
@@ -307,6 +311,14 @@ int vnm_set_strategy(int strategy)
     return VNM_OK;
 }
 
+int vnm_set_pair_mode(vnm_handle_t h, int mode)
+{
+    if (!h) return fail(VNM_ERR_BAD_ARG, "null handle");
+    if (mode != 0 && mode != 1) return fail(VNM_ERR_BAD_ARG, "pair mode must be 0 or 1 (got %d)", mode);
+    h->pair_mode = mode;
+    return VNM_OK;
+}
+
 int vnm_set_epilogue(vnm_handle_t h, int mode)
 {
     if (!h) return fail(VNM_ERR_BAD_ARG, "null handle");
@@ -347,9 +359,11 @@ int vnm_spmm_config(vnm_handle_t h, int N, int *tile_m, int *tile_n, int *stages
 {
     if (!h) return fail(VNM_ERR_BAD_ARG, "null handle");
     SpmmConfig cfg;
-    if (h->dense_b) spmm_dense_b_config(h->M, N, h->max_ctas, &cfg);
+    const bool pair = h->dense_b && h->pair_mode && N >= 128 && spmm_dense_b_pair_config(h->M, N, h->max_ctas, &cfg);
+    if (pair) { /* cfg filled */ }
+    else if (h->dense_b) spmm_dense_b_config(h->M, N, h->max_ctas, &cfg);
     else if (!spmm_select_config(h->V, N, h->M, h->producer_warps, h->max_ctas, &cfg)) return fail(VNM_ERR_UNSUPPORTED, "unsupported V");
-    if (tile_m) *tile_m = h->dense_b ? 2 * TILE_M : TILE_M;
+    if (tile_m) *tile_m = pair ? 4 * TILE_M : h->dense_b ? cfg.nb * TILE_M : TILE_M;
     if (tile_n) *tile_n = cfg.bn;
     if (stages) *stages = cfg.stages;
     if (grid) *grid = cfg.grid;
@@ -386,12 +400,14 @@ static int spmm_impl(vnm_handle_t h, const void *B, int64_t ldb, int N, int b_nk
         return fail(VNM_ERR_BAD_ARG, "vnm_spmm_f16: unknown layout %d", layout);
     }
     SpmmConfig cfg;
-    if (h->dense_b) spmm_dense_b_config(h->M, N, h->max_ctas, &cfg);
+    const bool pair = h->dense_b && h->pair_mode && (b_nk || N >= 128) && spmm_dense_b_pair_config(h->M, N, h->max_ctas, &cfg);
+    if (pair) { /* cfg filled */ }
+    else if (h->dense_b) spmm_dense_b_config(h->M, N, h->max_ctas, &cfg);
     else if (!spmm_select_config(h->V, N, h->M, h->producer_warps, h->max_ctas, &cfg)) return fail(VNM_ERR_UNSUPPORTED, "unsupported V");
     EncodeTiledFn enc = get_encode_fn();
     if (!enc) return fail(VNM_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
 
-    if (!h->tm_valid || h->tm_B != B || h->tm_ldb != ldb || h->tm_N != N || h->tm_nk != b_nk) {
+    if (!h->tm_valid || h->tm_B != B || h->tm_ldb != ldb || h->tm_N != N || h->tm_nk != b_nk || h->tm_pair != (pair ? 1 : 0)) {
         cuuint32_t estr[2] = {1, 1};
         CUresult r;
         if (b_nk) {
@@ -399,7 +415,7 @@ static int spmm_impl(vnm_handle_t h, const void *B, int64_t ldb, int N, int b_nk
             // is the K-major operand tile of one MMA (the last 16 rows belong to the next tile and are not read).
             cuuint64_t dims[2] = {(cuuint64_t)h->K, (cuuint64_t)N};
             cuuint64_t strides[1] = {(cuuint64_t)ldb * 2};
-            cuuint32_t box[2] = {32, 256};
+            cuuint32_t box[2] = {32, pair ? 128u : 256u};   // the pair kernel loads each CTA's 128-row half separately
             r = enc(&h->tmap_tile, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(B), dims, strides, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -423,7 +439,21 @@ static int spmm_impl(vnm_handle_t h, const void *B, int64_t ldb, int N, int b_nk
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
             h->tmap_tile2 = h->tmap_tile;
             h->tm_wide = false;
-            if (r == CUDA_SUCCESS && h->dense_b && N >= 256) {
+            if (r == CUDA_SUCCESS && pair) {
+                // pair kernel: a CTA's half of a stage is {64 columns, 32 rows, 2 slices} starting at any multiple of 8 columns
+                // (pair tiles start at multiples of 240, the peer's half 120 columns further)
+                cuuint64_t dims4[4] = {64, (cuuint64_t)h->K, 2, (cuuint64_t)((N - 128) / 8 + 1)};
+                cuuint64_t strides4[3] = {(cuuint64_t)ldb * 2, 128, 16};
+                cuuint32_t box4[4] = {64, 32, 2, 1};
+                cuuint32_t estr4[4] = {1, 1, 1, 1};
+                CUtensorMap wide;
+                if (enc(&wide, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void *>(B), dims4, strides4, box4, estr4,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS) {
+                    h->tmap_tile = wide;
+                    h->tm_wide = true;
+                }
+            } else if (r == CUDA_SUCCESS && h->dense_b && N >= 256) {
                 // dense-B kernel: {64 columns, K rows, 4 slices of 64 columns, start column / 16}.  A box {64, 32, 4, 1}
                 // lands as [slice][row][64 columns], the N-major operand tile of one MMA, with a single instruction.
                 // Only start columns whose 256 columns lie inside N are addressable; the ragged edge uses the 2-D map.
@@ -441,7 +471,7 @@ static int spmm_impl(vnm_handle_t h, const void *B, int64_t ldb, int N, int b_nk
             }
         }
         if (r != CUDA_SUCCESS) return fail(VNM_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
-        h->tm_B = B; h->tm_ldb = ldb; h->tm_N = N; h->tm_nk = b_nk; h->tm_valid = true;
+        h->tm_B = B; h->tm_ldb = ldb; h->tm_N = N; h->tm_nk = b_nk; h->tm_pair = pair ? 1 : 0; h->tm_valid = true;
     }
 
     SpmmParams p;
@@ -482,7 +512,8 @@ static int spmm_impl(vnm_handle_t h, const void *B, int64_t ldb, int N, int b_nk
                     CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         }
         if (r != CUDA_SUCCESS) return fail(VNM_ERR_CUDA, "cuTensorMapEncodeTiled (output) failed with CUresult %d", (int)r);
-        VNM_CUDA(launch_spmm_dense_b(cfg, h->tmap_tile, h->tmap_tile2, tmap_out, p, (cudaStream_t)stream), "spmm launch");
+        if (pair) VNM_CUDA(launch_spmm_dense_b_pair(cfg, h->tmap_tile, h->tmap_tile2, tmap_out, p, (cudaStream_t)stream), "spmm launch");
+        else VNM_CUDA(launch_spmm_dense_b(cfg, h->tmap_tile, h->tmap_tile2, tmap_out, p, (cudaStream_t)stream), "spmm launch");
     } else {
         VNM_CUDA(launch_spmm(cfg, h->tmap_rows, h->tmap_tile, p, (cudaStream_t)stream), "spmm launch");
     }

@@ -88,4 +88,10 @@ void spmm_dense_b_config(int M, int N, int max_ctas, SpmmConfig *cfg);  // max_c
 cudaError_t launch_spmm_dense_b(const SpmmConfig &cfg, const CUtensorMap &tmap_tile, const CUtensorMap &tmap_tile2, const CUtensorMap &tmap_out,
                                 const SpmmParams &p, cudaStream_t stream);
 
+// Dense-B form on pairs of SMs (clusters of two CTAs, tcgen05 cta_group::2): 512 x 240 pair tiles (vnm_spmm_dense_b2.cu).
+cudaError_t spmm_dense_b_pair_init();
+bool spmm_dense_b_pair_config(int M, int N, int max_ctas, SpmmConfig *cfg);  // false: use the single-CTA kernel
+cudaError_t launch_spmm_dense_b_pair(const SpmmConfig &cfg, const CUtensorMap &tmap_tile, const CUtensorMap &tmap_tile2, const CUtensorMap &tmap_out,
+                                     const SpmmParams &p, cudaStream_t stream);
+
 }  // namespace vnm
