@@ -166,10 +166,11 @@ int vnm_device_status(vnm_handle_t handle, int *status, void *stream);
 int vnm_selftest_wait_expiry(vnm_handle_t handle, void *stream);
 
 /* Ablation switches.
- * Gather mode: how the selected rows of B reach shared memory.  3 = 16-byte asynchronous copies (cp.async) issued
- * per thread from the row table, written straight into the swizzled operand layout (default for m > 4; the staging
- * the reference uses, include/spatha/block_sparse/spmm/blockwise_kernel.h:868-881); 0 = TMA tile::gather4, one
- * group of four rows per instruction (about half the rate: bound by the TMA instruction rate); 1 = plain TMA tiles
+ * Gather mode: how the selected rows of B reach shared memory.  0 = TMA tile::gather4, one group of four rows per
+ * instruction (default for m > 4); 3 = 16-byte asynchronous copies (cp.async) issued per thread from the row table and
+ * written straight into the swizzled operand layout (the staging the reference uses,
+ * include/spatha/block_sparse/spmm/blockwise_kernel.h:868-881; measured slower than the TMA gather on B200, alone and
+ * in any split with it, see vnm_set_gather_split); 1 = plain TMA tiles
  * of 64 consecutive rows, which is exact
  * for m == 4 (every row is selected; the default there) and otherwise removes the column-loc
  * indirection exactly like the reference's compile-time IDEAL_KERNEL experiment
@@ -177,6 +178,9 @@ int vnm_selftest_wait_expiry(vnm_handle_t handle, void *stream);
  * 2 = B is not loaded at all (timing floor; results are meaningless).
  * Producer warps: 4 or 8 warps issue the gather loads (default 8). */
 int vnm_set_gather_mode(vnm_handle_t handle, int mode);
+/* Gather mode 3 only: of the 64 gathered rows of every stage, `tma_rows` (0, 16, 32 or 48) are fetched by TMA
+ * tile::gather4 and the others by the per-thread copies, so that both paths into the SM are busy at once. */
+int vnm_set_gather_split(vnm_handle_t handle, int tma_rows);
 /* Epilogue of the V:N:M (gather) form for layout MN: 0 = results staged in shared memory and stored as full 128-bit
  * sectors (default); 1 = every thread stores its own row in 32-bit words, the reference's OUT_32B experiment
  * (include/spatha/block_sparse/common/epilogue.h:34-61, blockwise_kernel.h:911-943).  VNM_ERR_UNSUPPORTED for operands
@@ -199,7 +203,8 @@ int vnm_prepare_as(const void *values, const uint32_t *meta, const uint32_t *col
 int vnm_set_producer_warps(vnm_handle_t handle, int warps);
 /* Dense-B form only: 1 (default) = products with at least one full wave of 512 x 240 tiles and M a multiple of 512 run on
  * pairs of SMs (thread-block clusters of two CTAs, tcgen05 cta_group::2: each CTA loads half of every B stage), 0 = always
- * the single-SM kernel.  An ablation switch; both give the same result up to fp32 summation order (identical bits). */
+ * the single-SM kernel, 2 = pairs with a second tcgen05.commit to the peer's barriers instead of the forwarding thread.
+ * Ablation switches; all give identical bits. */
 int vnm_set_pair_mode(vnm_handle_t handle, int mode);
 /* Caps the number of persistent CTAs (one per SM) the product of this handle launches; 0 = all SMs (default).  A caller
  * that runs something else beside the product (the multi-GPU launcher's all-gather, another stream's kernels) keeps SMs

@@ -91,7 +91,7 @@ def test_srnm_spmm_module_replaces_linear(spatha):
     "--m 1024 --k 1024 --n 2048 --bm 128 --mm_row 8 --strategy gather",
     "--m 1024 --k 1024 --n 2048 --bm 128 --mm_row 16 --strategy dense-b",
     "--m 1024 --k 1024 --n 2048 --bm 128 --mm_row 4 --ablation ideal",
-    "--m 1024 --k 2048 --n 2048 --bm 128 --mm_row 16 --ablation gather4",     # rows gathered by TMA gather4 instead of cp.async
+    "--m 1024 --k 2048 --n 2048 --bm 128 --mm_row 16 --ablation cpasync",     # rows gathered by per-thread cp.async instead of TMA gather4
     "--m 1024 --k 2048 --n 2056 --bm 64 --mm_row 8 --ablation out32",         # 32-bit epilogue stores, ragged N
 ])
 def test_benchmark_spmm_cli_check(flags):

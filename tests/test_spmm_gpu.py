@@ -228,6 +228,33 @@ def test_gather_modes_agree_when_every_row_is_selected(capi, oracle):
     assert torch.equal(a, b) and torch.equal(a, c)
 
 
+@pytest.mark.parametrize("shape", [(256, 1024, 128, 8, 512), (256, 2048, 64, 16, 384), (128, 1024, 32, 8, 72), (96, 520, 32, 10, 200),
+                                   (2048, 2048, 128, 16, 4096)])
+def test_gather_paths_give_identical_bits(capi, oracle, shape):
+    """The selected rows of B reach shared memory by per-thread cp.async copies (default), by TMA gather4, or by any
+    split of the two; the MMAs and their order do not change, so every variant must produce the same bits."""
+    import torch
+    M, K, V, m, N = shape
+    capi.set_strategy(capi.STRATEGY_GATHER)
+    try:
+        prep, Bd, (ov, om, cols, B) = _setup(capi, oracle, M, K, V, m, N, seed=11 * M + K, ints=False)
+    finally:
+        capi.set_strategy(capi.STRATEGY_AUTO)
+    assert not prep.dense_b_form()
+    ref = prep.spmm(Bd)                                   # default: TMA gather4
+    if M * N <= 1 << 20:
+        _check(oracle, ref.cpu().numpy(), oracle.spmm(ov, om, cols, M, K, V, m, B))
+    else:
+        rows = np.arange(0, M, 97, dtype=np.int32)
+        want = oracle.spmm(ov, om, cols, M, K, V, m, B, rows=rows)
+        _check(oracle, ref.cpu().numpy()[rows], want[rows])
+    prep.set_gather_mode(3)                               # per-thread cp.async copies, alone and split with TMA gather4
+    for split in (0, 16, 32, 48):
+        prep.set_gather_split(split)
+        assert torch.equal(prep.spmm(Bd), ref), "cp.async + TMA split %d differs" % split
+    assert prep.device_status() == 0
+
+
 @pytest.mark.parametrize("shape", [(128, 512, 128, 4, 256), (256, 1024, 128, 8, 512), (192, 768, 64, 8, 200), (128, 1024, 32, 16, 64),
                                    (96, 512, 32, 32, 72), (256, 2048, 64, 16, 384),
                                    (128, 1000, 64, 8, 520),      # K ends inside a 128-column k-tile; N ends inside the third column tile

@@ -64,6 +64,8 @@ def lib():
         L.vnm_set_strategy.restype = C.c_int
         L.vnm_set_producer_warps.argtypes = [C.c_void_p, C.c_int]
         L.vnm_set_producer_warps.restype = C.c_int
+        L.vnm_set_gather_split.argtypes = [C.c_void_p, C.c_int]
+        L.vnm_set_gather_split.restype = C.c_int
         L.vnm_set_pair_mode.argtypes = [C.c_void_p, C.c_int]
         L.vnm_set_pair_mode.restype = C.c_int
         L.vnm_set_epilogue.argtypes = [C.c_void_p, C.c_int]
@@ -261,12 +263,16 @@ class Prepared:
         return int(st.value)
 
     def set_gather_mode(self, mode):
-        """3 = per-thread 16-byte cp.async copies (default for m > 4), 0 = TMA gather4, 1 = 64-row TMA tiles (exact for m == 4, otherwise the
+        """0 = TMA gather4 (default for m > 4), 3 = per-thread 16-byte cp.async copies (ablation), 1 = 64-row TMA tiles (exact for m == 4, otherwise the
         "no column-loc" ablation), 2 = no B loads (timing floor only)."""
         _check(lib().vnm_set_gather_mode(self._h, mode))
 
     def set_producer_warps(self, warps):
         _check(lib().vnm_set_producer_warps(self._h, warps))
+
+    def set_gather_split(self, tma_rows):
+        """Gather mode 3: rows of every 64-row stage fetched by TMA gather4 beside the per-thread copies (0, 16, 32, 48)."""
+        _check(lib().vnm_set_gather_split(self._h, tma_rows))
 
     def set_pair_mode(self, mode):
         """Dense-B form: 1 = two-SM (cta_group::2) kernel where it applies (default), 0 = single-SM kernel only."""

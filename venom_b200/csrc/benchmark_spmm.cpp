@@ -61,11 +61,11 @@ static const char *kUsage =
     "Accepted and echoed: --bn --bk --wm --wn --wk --mm --mn --mk --nstage --acc_t fp32\n"
     "Optional: --random (time-based seed), --check (compare with cuBLAS on the decompressed matrix)\n"
     "          --strategy auto|gather|dense-b   operand form (default auto: chosen per V and m)\n"
-    "          --ablation none|ideal|no-b|gather4|out32\n"
+    "          --ablation none|ideal|no-b|cpasync|out32\n"
     "                                          ideal: gather form without column-loc (plain row tiles of B, the\n"
     "                                          reference's IDEAL_KERNEL build; results differ unless m = 4);\n"
     "                                          no-b: no loads of B at all (timing floor of the pipeline);\n"
-    "                                          gather4: rows gathered by TMA tile::gather4 instead of per-thread cp.async;\n"
+    "                                          cpasync: rows gathered by per-thread cp.async copies instead of TMA tile::gather4;\n"
     "                                          out32: 32-bit epilogue stores (the reference's OUT_32B build)\n";
 
 int main(int argc, const char **argv)
@@ -103,7 +103,7 @@ int main(int argc, const char **argv)
         else if (is("--precision") && has) precision_code = !strcmp(argv[i + 1], "half") ? 1 : -2;
         else if (is("--check")) check = true;
         else if (is("--strategy") && has) strategy = !strcmp(argv[i + 1], "gather") ? VNM_STRATEGY_GATHER : (!strcmp(argv[i + 1], "dense-b") ? VNM_STRATEGY_DENSE_B : VNM_STRATEGY_AUTO);
-        else if (is("--ablation") && has) ablation = !strcmp(argv[i + 1], "ideal") ? 1 : !strcmp(argv[i + 1], "no-b") ? 2 : !strcmp(argv[i + 1], "gather4") ? 3 : !strcmp(argv[i + 1], "out32") ? 4 : 0;
+        else if (is("--ablation") && has) ablation = !strcmp(argv[i + 1], "ideal") ? 1 : !strcmp(argv[i + 1], "no-b") ? 2 : !strcmp(argv[i + 1], "cpasync") ? 3 : !strcmp(argv[i + 1], "out32") ? 4 : 0;
         else if (is("--random")) seed = (unsigned)std::chrono::system_clock::now().time_since_epoch().count();
     }
     if (m == 0 || n == 0 || k == 0 || density == 0.f) {
@@ -174,7 +174,7 @@ int main(int argc, const char **argv)
     if (ablation == 1 || ablation == 3 || ablation == 4) strategy = VNM_STRATEGY_GATHER;  // switches of the V:N:M (gather) form
     VK(vnm_prepare_as(dval, dmeta, dcol, M, K, V, nn_row, mrow, strategy, &h, nullptr));
     if (ablation == 1 || ablation == 2) VK(vnm_set_gather_mode(h, ablation));
-    if (ablation == 3) VK(vnm_set_gather_mode(h, 0));
+    if (ablation == 3) VK(vnm_set_gather_mode(h, 3));
     if (ablation == 4) VK(vnm_set_epilogue(h, 1));
     VK(vnm_decompress_f16(dval, dmeta, dcol, M, K, V, nn_row, mrow, dAd, K, nullptr));  // to_dense() for the cuBLAS side
 

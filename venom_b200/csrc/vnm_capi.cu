@@ -151,6 +151,7 @@ struct vnm_prepared_s {
     int gather_mode;
     int dense_b;       // 1: A re-expressed as 2:4 over all K columns, B read as plain tiles
     int out32;         // ablation: 32-bit epilogue stores (gather form, layout MN)
+    int hybrid_rows;   // gather form: rows of every 64-row stage fetched by TMA gather4 beside the per-thread copies
     int pair_mode;     // dense-B form: 1 = use the two-SM (cta_group::2) kernel where it applies (default), 0 = never
     int max_ctas;      // 0 = one persistent CTA per SM, else the cap set by vnm_set_max_ctas
 };
@@ -254,7 +255,7 @@ int vnm_prepare_as(const void *values, const uint32_t *meta, const uint32_t *col
     } else {
         h->ktiles = (int)((h->Ksp + KT_COMP - 1) / KT_COMP);
         h->nb = TILE_M / V;
-        h->gather_mode = (m == 4) ? GATHER_CONTIG : GATHER_CPASYNC;  // with m == 4 every row of B is selected
+        h->gather_mode = (m == 4) ? GATHER_CONTIG : GATHER_TMA4;  // with m == 4 every row of B is selected
     }
     h->vblocks_padded = h->mtiles * h->nb;
     h->producer_warps = 8;
@@ -311,10 +312,18 @@ int vnm_set_strategy(int strategy)
     return VNM_OK;
 }
 
+int vnm_set_gather_split(vnm_handle_t h, int tma_rows)
+{
+    if (!h) return fail(VNM_ERR_BAD_ARG, "null handle");
+    if (tma_rows != 0 && tma_rows != 16 && tma_rows != 32 && tma_rows != 48) return fail(VNM_ERR_BAD_ARG, "tma_rows must be 0, 16, 32 or 48 (got %d)", tma_rows);
+    h->hybrid_rows = tma_rows;
+    return VNM_OK;
+}
+
 int vnm_set_pair_mode(vnm_handle_t h, int mode)
 {
     if (!h) return fail(VNM_ERR_BAD_ARG, "null handle");
-    if (mode != 0 && mode != 1) return fail(VNM_ERR_BAD_ARG, "pair mode must be 0 or 1 (got %d)", mode);
+    if (mode < 0 || mode > 2) return fail(VNM_ERR_BAD_ARG, "pair mode must be 0, 1 or 2 (got %d)", mode);
     h->pair_mode = mode;
     return VNM_OK;
 }
@@ -489,6 +498,8 @@ static int spmm_impl(vnm_handle_t h, const void *B, int64_t ldb, int N, int b_nk
     p.B = (const __half *)B;
     p.ldb = ldb;
     p.out32 = h->out32;
+    p.hybrid_rows = h->hybrid_rows;
+    p.pair_relay = h->pair_mode == 2 ? 0 : 1;  // mode 2 (ablation): a second commit to the peer instead of the forwarding thread
     p.b_nk = b_nk;
     p.b_wide_ok = h->tm_wide ? 1 : 0;
     if (h->dense_b) {

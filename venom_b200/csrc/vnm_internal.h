@@ -30,6 +30,8 @@ struct SpmmParams {
     int total_tiles;      // mtiles * ntiles
     const __half *B;      // gather kernel, GATHER_CPASYNC: the dense operand [K, N] itself (row pieces are copied by address)
     int64_t ldb;
+    int hybrid_rows;      // gather kernel, GATHER_CPASYNC: rows per block and stage fetched by TMA gather4 beside the copies (0, 16, 32, 48)
+    int pair_relay;       // pair kernel: 1 = a thread of the leader forwards stage-free / accumulator-full arrivals to the peer instead of a second commit
     int out32;            // gather kernel, layout MN: 32-bit stores from registers instead of staged 128-bit stores (ablation)
     int b_nk;             // dense-B kernel only: the dense operand is given as [N, K] row-major (K contiguous)
     int b_wide_ok;        // dense-B kernel only: the 4-D tensor map exists (column tiles with 256 columns inside N use one box per stage)
@@ -37,11 +39,11 @@ struct SpmmParams {
 
 // How the producer warps bring the selected rows of B into shared memory.
 enum : int {
-    GATHER_TMA4 = 0,    // TMA tile::gather4, four rows (one group) per instruction
+    GATHER_TMA4 = 0,    // TMA tile::gather4, four rows (one group) per instruction (default for m > 4)
     GATHER_CONTIG = 1,  // plain TMA tiles of 64 consecutive rows: exact when m == 4 (every row is
                         // selected), otherwise an ablation that drops the column-loc indirection
     GATHER_NONE = 2,    // ablation only: B is not loaded at all (results are meaningless)
-    GATHER_CPASYNC = 3  // per-thread 16-byte asynchronous copies of the selected rows (default for m > 4)
+    GATHER_CPASYNC = 3  // per-thread 16-byte asynchronous copies of the selected rows, optionally split with TMA gather4 (ablation: measured slower)
 };
 
 struct SpmmConfig {

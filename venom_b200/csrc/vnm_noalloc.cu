@@ -138,11 +138,13 @@ extern "C" int vnm_spmm_f16_noalloc(const void *values, const uint32_t *meta, co
     p.mtiles = mtiles; p.ktiles = ktiles; p.ntiles = (N + cfg.bn - 1) / cfg.bn;
     p.layout = layout;
     p.status = status;
-    p.gather_mode = (m == 4) ? GATHER_CONTIG : GATHER_CPASYNC;
+    p.gather_mode = (m == 4) ? GATHER_CONTIG : GATHER_TMA4;
     p.total_tiles = p.mtiles * p.ntiles;
     p.B = (const __half *)B;
     p.ldb = ldb;
     p.out32 = 0;
+    p.hybrid_rows = 0;
+    p.pair_relay = 0;
     p.b_nk = 0;
     p.b_wide_ok = 0;
     e = launch_spmm(cfg, tmap_rows, tmap_tile, p, s);

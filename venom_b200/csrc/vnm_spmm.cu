@@ -157,7 +157,7 @@ __global__ void __launch_bounds__(Traits<BN, NB, SA, SB, PB>::NUM_THREADS, 1)
         for (int s = 0; s < SA; s++) { mbar_init(&a_full[s], 1); mbar_init(&a_empty[s], 1); }
         // a B stage is complete after one arrival with a byte count (TMA modes) or after one deferred arrival of every
         // producer thread (per-thread 16-byte asynchronous copies)
-        for (int s = 0; s < SB; s++) { mbar_init(&b_full[s], gmode == GATHER_CPASYNC ? PB * 32 : 1); mbar_init(&b_empty[s], 1); }
+        for (int s = 0; s < SB; s++) { mbar_init(&b_full[s], gmode == GATHER_CPASYNC ? PB * 32 + (p.hybrid_rows ? 1 : 0) : 1); mbar_init(&b_empty[s], 1); }
         for (int s = 0; s < T::SP; s++) mbar_init(&kdone[s], 1);
         for (int s = 0; s < T::SR; s++) mbar_init(&kready[s], 2);  // metadata copy done + operands landed
         mbar_init(acc_full_bar, 1);
@@ -203,61 +203,98 @@ __global__ void __launch_bounds__(Traits<BN, NB, SA, SB, PB>::NUM_THREADS, 1)
         // so each lane meets the ring slots strictly in order and the phase parity stays unambiguous.
         // The row numbers of the next stage are fetched before waiting for the current slot.
         if (gmode == GATHER_CPASYNC) {
-            // ---- per-thread 16-byte asynchronous copies driven by the row table ----
-            // A stage holds NB blocks x 64 gathered rows x BN columns = 2048 pieces of 16 bytes; thread t copies the
-            // pieces (column piece cc = t % CPR, flattened row t / CPR + i * RPP), so a warp reads whole rows of B
-            // (512 contiguous bytes at BN = 256) and writes them in the 128-byte-swizzled N-major operand layout.
-            // The TMA gather (four 128-byte row pieces per instruction) is limited by its instruction rate, about a
-            // third of what the SM can take in; plain asynchronous copies have no such limit.
+            // ---- per-thread 16-byte asynchronous copies driven by the row table, optionally beside TMA gathers ----
+            // A stage holds NB blocks x 64 gathered rows x BN columns = 2048 pieces of 16 bytes.  The first HT rows of
+            // every block (p.hybrid_rows: 0, 16, 32 or 48) are fetched by TMA tile::gather4 (four 128-byte row pieces per
+            // instruction), the others by plain asynchronous copies: thread t copies the pieces (column piece t % CPR,
+            // flattened row t / CPR + i * RPP), so a warp reads whole rows of B (512 contiguous bytes at BN = 256) and
+            // writes them in the 128-byte-swizzled N-major operand layout.  Measured on B200 this path is SLOWER than the
+            // TMA gather (which is therefore the default), alone and in every split: kept as an ablation.
             constexpr int NT = PB * 32;           // producer threads
             constexpr int CPR = BN / 8;           // 16-byte pieces per row of a block
             constexpr int RPP = NT / CPR;         // flattened rows covered by one pass of all threads
             constexpr int PASSES = NB * BS_ROWS / RPP;
             static_assert(NT % CPR == 0 && (NB * BS_ROWS) % RPP == 0 && PASSES >= 1, "producer threads do not tile a B stage");
+            const int HT = p.hybrid_rows;         // rows per block and stage that go through TMA
+            const int CR = BS_ROWS - HT;          // rows per block and stage that go through asynchronous copies
             const int t = (warp - 1) * 32 + lane;
             const int cc = t % CPR, fr0 = t / CPR;
             const int *rows_i32 = reinterpret_cast<const int *>(p.rows);
             const __half *Bg = p.B;
+            // this thread's fixed share of a stage, worked out once: block, row inside the block, shared-memory offset
+            int blk[PASSES], rsel[PASSES];
+            uint32_t doff[PASSES];
+            int passes = 0;
+#pragma unroll
+            for (int i = 0; i < PASSES; i++) {
+                const int fr = fr0 + i * RPP;
+                blk[i] = 0; rsel[i] = 0; doff[i] = 0;
+                if (fr < NB * CR) {
+                    const int b = fr / CR, r = HT + fr % CR;
+                    blk[i] = b; rsel[i] = r;
+                    doff[i] = (uint32_t)(b * T::B_BLOCK_BYTES + (cc >> 3) * T::B_CHUNK_BYTES + r * 128 + (((cc & 7) ^ (r & 7)) << 4));
+                    passes = i + 1;
+                }
+            }
+            // TMA share: HT gather4 instructions per stage (NB blocks x HT / 4 groups x CH slices), HT / PB per warp
+            const int tma_per_warp = HT / PB;
+            const bool tma_lane = lane < tma_per_warp;
+            const int gidx = lane * PB + (warp - 1);
+            const int gper_block = (HT / 4) * T::CH;
+            const int gb = gper_block ? gidx / gper_block : 0, gg = gper_block ? (gidx % gper_block) / T::CH : 0, gc = gidx % T::CH;
+            const bool leader = t == 0;
+            if (leader && HT) tma_prefetch_desc(&tmap_rows);
             int rcur[PASSES], rnxt[PASSES];
-            auto load_rows = [&](int tl, int l, int(&dst)[PASSES]) {
+            int4 gcur = make_int4(0, 0, 0, 0), gnxt = make_int4(0, 0, 0, 0);
+            auto load_rows = [&](int tl, int l, int(&dst)[PASSES], int4 &g4) {
                 const int mt = tl % p.mtiles;
 #pragma unroll
-                for (int i = 0; i < PASSES; i++) {
-                    const int fr = fr0 + i * RPP, b = fr / BS_ROWS, r = fr % BS_ROWS;
-                    dst[i] = __ldg(rows_i32 + ((size_t)(mt * NB + b) * p.ktiles * KT_GROUPS) * 4 + (size_t)l * BS_ROWS + r);
-                }
+                for (int i = 0; i < PASSES; i++)
+                    if (i < passes) dst[i] = __ldg(rows_i32 + ((size_t)(mt * NB + blk[i]) * p.ktiles * KT_GROUPS) * 4 + (size_t)l * BS_ROWS + rsel[i]);
+                if (tma_lane) g4 = __ldg(p.rows + ((size_t)(mt * NB + gb) * p.ktiles) * KT_GROUPS + (size_t)l * BS_GROUPS + gg);
             };
             int j = 0, tile = blockIdx.x, jl = 0;
             bool valid = tile < p.total_tiles;
-            if (valid) load_rows(tile, jl, rcur);
+            if (valid) load_rows(tile, jl, rcur, gcur);
             while (valid) {
                 int ntile = tile, njl = jl + 1;
                 if (njl == bstages_per_tile) { njl = 0; ntile += gridDim.x; }
                 const bool nvalid = ntile < p.total_tiles;
-                if (nvalid) load_rows(ntile, njl, rnxt);
+                if (nvalid) load_rows(ntile, njl, rnxt, gnxt);
                 const int s = j % SB;
                 if (j >= SB) {
                     const int kd = (j - SB) >> 1;  // slot s was last used by stage j - SB, a half of k-tile (j - SB) / 2
-                    if (!wait_one(&kdone[kd % T::SP], (uint32_t)(kd / T::SP) & 1u, abort_flag, p.status, DEV_TIMEOUT_PRODUCER)) break;
+                    // one lane per warp polls: hundreds of threads spinning on a barrier slow the other roles' polls down
+                    if (!wait_bounded(&kdone[kd % T::SP], (uint32_t)(kd / T::SP) & 1u, abort_flag, p.status, DEV_TIMEOUT_PRODUCER)) break;
                 }
-                const uint32_t st = smem_u32(b_ring + s * T::B_STAGE_BYTES);
-                const int col = (tile / p.mtiles) * BN + cc * 8;
+                uint8_t *stp = b_ring + s * T::B_STAGE_BYTES;
+                const uint32_t st = smem_u32(stp);
+                const int n0 = (tile / p.mtiles) * BN;
+                if (HT) {
+                    if (leader) mbar_arrive_expect_tx(&b_full[s], (uint32_t)(HT * 512));  // NB * BN = 256 columns of HT rows
+                    if (tma_lane) tma_gather4(stp + gb * T::B_BLOCK_BYTES + gc * T::B_CHUNK_BYTES + gg * 512, &tmap_rows, n0 + gc * 64, gcur, &b_full[s]);
+                }
+                const int col = n0 + cc * 8;
                 const bool col_ok = col < p.N;  // N % 8 == 0: a piece lies entirely inside or outside
 #pragma unroll
                 for (int i = 0; i < PASSES; i++) {
-                    const int fr = fr0 + i * RPP, b = fr / BS_ROWS, r = fr % BS_ROWS;
-                    const int row = rcur[i];
-                    const bool ok = col_ok && row < p.K;  // padding rows (row == K) and columns past N read as zeros
-                    const __half *src = ok ? Bg + (size_t)row * p.ldb + col : Bg;
-                    const uint32_t dst = st + b * T::B_BLOCK_BYTES + (cc >> 3) * T::B_CHUNK_BYTES + r * 128 + (((cc & 7) ^ (r & 7)) << 4);
-                    cp_async_16_zfill(dst, src, ok ? 16u : 0u);
+                    if (i < passes) {
+                        const int row = rcur[i];
+                        const bool ok = col_ok && row < p.K;  // padding rows (row == K) and columns past N read as zeros
+                        const __half *src = ok ? Bg + (size_t)row * p.ldb + col : Bg;
+                        cp_async_16_zfill(st + doff[i], src, ok ? 16u : 0u);
+                    }
                 }
                 cp_async_mbar_arrive_noinc(&b_full[s]);  // arrives once this thread's copies have landed
 #pragma unroll
                 for (int i = 0; i < PASSES; i++) rcur[i] = rnxt[i];
+                gcur = gnxt;
                 tile = ntile; jl = njl; valid = nvalid; ++j;
             }
             cp_async_wait_all();  // nothing of this thread is in flight when the CTA leaves (also on the abort path)
+            if (*abort_flag && leader && HT) {
+                for (int k = j > SB ? j - SB : 0; k < j; ++k) drain_slot(&b_full[k % SB], (uint32_t)(k / SB) & 1u, p.status);
+            }
             __syncwarp();
         } else {
         const int pw = warp - 1;

@@ -9,12 +9,15 @@
 // Cluster protocol (rank 0 = leader, rank 1 = peer); every load stays local to the CTA that issues it:
 //   * both CTAs run their own A producer, B producers and epilogue on their own shared / tensor memory;
 //   * the peer forwards "my A blocks of k-tile it landed" and "my half of stage j landed" to the leader with remote
-//     mbarrier arrivals (peer_a / peer_b barriers in the leader's shared memory);
+//     mbarrier arrivals on the leader's own a_full / b_full barriers (which expect two arrivals there: the leader's
+//     loads and the peer's message), so the leader's sequencer and MMA issuer wait on one barrier per hand-off,
+//     exactly as in the single-CTA kernel -- anything more on the issuing thread leaves the tensor pipe idle;
 //   * only the leader issues tensor-core work: tcgen05.cp.cta_group::2 copies each CTA's metadata image into that
 //     CTA's tensor memory, tcgen05.mma.sp.cta_group::2 reads A and B from both CTAs' shared memory;
-//   * the leader's tcgen05.commit.cta_group::2 arrives on the stage-free / accumulator-full barriers of BOTH CTAs
-//     (two commits: the local barrier and the peer's barrier through its shared::cluster address), and the peer's
-//     epilogue warps arrive remotely on the leader's accumulator-empty barrier.
+//   * the leader's tcgen05.commit.cta_group::2 arrives on the leader's stage-free / accumulator-full barriers and a
+//     spare thread of the leader forwards each arrival to the peer's barriers (p.pair_relay = 0 instead issues a
+//     second commit to the peer's barrier through its shared::cluster address); the peer's epilogue warps arrive
+//     remotely on the leader's accumulator-empty barrier.
 // No copy with cluster multicast is used anywhere.  Every wait is bounded (status bit, drain, return), and the two CTAs
 // meet at a cluster barrier before tensor memory is freed, so neither leaves while the other may still touch it.
 #include "vnm_internal.h"
@@ -54,7 +57,7 @@ __device__ __forceinline__ uint32_t meta_col(int set) { return set == 0 ? 240u :
 static_assert(SB % NBP == 0 && NBP <= 4, "B producers");
 static_assert(SF >= 4 * SA && SF >= 4 * META_SETS && SF >= 2 * SB && SF % SB == 0, "too few stage barriers: a waiter could miss a phase");
 static_assert(BN <= 240 && META_SETS == 3 && RT == 2 && BN % 16 == 0 && BN == 6 * PART, "tensor-memory column plan");
-static_assert((2 * SA + 2 * SB + SF + SR + 2) * 8 + 16 <= BAR_BYTES, "barrier area too small");
+static_assert((SA + SB + SF + SR + 2) * 8 + 16 <= BAR_BYTES, "barrier area too small");
 constexpr int HALF_N = BN / 2;   // columns of a B stage held by each CTA of the pair
 
 __device__ __forceinline__ bool wait_one(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int *status, int code)
@@ -99,20 +102,7 @@ __device__ __forceinline__ uint32_t mapa_shared(uint32_t saddr, uint32_t rank)
 }
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr)
 {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-// probe of a barrier that other CTAs of the cluster arrive on
-__device__ __forceinline__ bool mbar_test_wait_cluster(uint64_t *bar, uint32_t parity)
-{
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.test_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
-        : "memory");
-    return ok != 0;
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 __device__ __forceinline__ void cluster_sync_all()
 {
@@ -151,29 +141,11 @@ __device__ __forceinline__ void tc_mma2_sp_f16(uint32_t d_tmem, uint64_t adesc, 
         : "memory");
 }
 
-__device__ __forceinline__ bool wait_one_cluster(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int *status, int code);
-__device__ __forceinline__ bool wait_warp_cluster(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int *status, int code)
+__device__ __forceinline__ bool wait_warp(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int *status, int code)
 {
     int ok = 1;
-    if ((threadIdx.x & 31) == 0) ok = wait_one_cluster(bar, parity, abort_flag, status, code) ? 1 : 0;
+    if ((threadIdx.x & 31) == 0) ok = wait_one(bar, parity, abort_flag, status, code) ? 1 : 0;
     return __shfl_sync(0xffffffffu, ok, 0) != 0;
-}
-
-__device__ __forceinline__ bool wait_one_cluster(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int *status, int code)
-{
-    if (mbar_test_wait_cluster(bar, parity)) return true;
-    const long long t0 = clock64();
-    for (uint32_t it = 0;; ++it) {
-        if (mbar_test_wait_cluster(bar, parity)) return true;
-        if ((it & 1023u) == 1023u) {
-            if (*abort_flag) return false;
-            if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
-                *abort_flag = 1;
-                atomicOr(status, code);
-                return false;
-            }
-        }
-    }
 }
 
 // Warp roles (512 threads per CTA, as in the single-CTA kernel):
@@ -198,9 +170,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_pair_kernel(const
     uint64_t *kready = b_free + SF;
     uint64_t *acc_full_bar = kready + SR;
     uint64_t *acc_empty_bar = acc_full_bar + 1;
-    uint64_t *peer_a = acc_empty_bar + 1;  // leader only: the peer's A blocks of the k-tile in slot s have landed
-    uint64_t *peer_b = peer_a + SA;        // leader only: the peer's half of the B stage in slot s has landed
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(peer_b + SB);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty_bar + 1);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5;
@@ -215,8 +185,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_pair_kernel(const
     const int total_it = my_tiles * p.ktiles;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < SA; s++) { mbar_init(&a_full[s], 1); mbar_init(&peer_a[s], 1); }
-        for (int s = 0; s < SB; s++) { mbar_init(&b_full[s], 1); mbar_init(&peer_b[s], 1); }
+        // in the leader a slot is full once its own loads have landed AND the peer has reported the same for its half
+        for (int s = 0; s < SA; s++) mbar_init(&a_full[s], leader_cta ? 2 : 1);
+        for (int s = 0; s < SB; s++) mbar_init(&b_full[s], leader_cta ? 2 : 1);
         for (int s = 0; s < SF; s++) mbar_init(&b_free[s], 1);
         for (int s = 0; s < SR; s++) mbar_init(&kready[s], 1);
         mbar_init(acc_full_bar, 1);
@@ -248,7 +219,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_pair_kernel(const
                     const int s = it % SA;
                     if (it >= SA) {
                         const int jd = 4 * (it - SA) + 3;  // last B stage of the k-tile that used this slot
-                        if (!wait_one_cluster(&b_free[jd % SF], (uint32_t)(jd / SF) & 1u, abort_flag, p.status, DEV_TIMEOUT_PRODUCER)) { alive = false; break; }
+                        if (!wait_one(&b_free[jd % SF], (uint32_t)(jd / SF) & 1u, abort_flag, p.status, DEV_TIMEOUT_PRODUCER)) { alive = false; break; }
                     }
                     mbar_arrive_expect_tx(&a_full[s], R * AM_BLOCK_BYTES);
 #pragma unroll
@@ -281,9 +252,15 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_pair_kernel(const
                 const int s = j % SB;
                 if (j >= SB) {
                     const int jd = j - SB;
-                    if (!wait_one_cluster(&b_free[jd % SF], (uint32_t)(jd / SF) & 1u, abort_flag, p.status, DEV_TIMEOUT_PRODUCER)) break;
+                    if (!wait_one(&b_free[jd % SF], (uint32_t)(jd / SF) & 1u, abort_flag, p.status, DEV_TIMEOUT_PRODUCER)) break;
                 }
                 uint8_t *dst = b_ring + s * B_STAGE_BYTES;
+                if (p.gather_mode == GATHER_NONE) {  // ablation: no loads of B at all (timing floor; results are meaningless)
+                    mbar_arrive(&b_full[s]);
+                    jl += NBP;
+                    while (jl >= per_tile) { jl -= per_tile; ++tile_i; }
+                    continue;
+                }
                 // 128 columns come along per stage; the MMA reads the first 120 of them
                 mbar_arrive_expect_tx(&b_full[s], B_STAGE_BYTES);
                 if (p.b_nk) {
@@ -296,7 +273,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_pair_kernel(const
                 jl += NBP;
                 while (jl >= per_tile) { jl -= per_tile; ++tile_i; }
             }
-            if (*abort_flag) {
+            if (*abort_flag && p.gather_mode != GATHER_NONE) {
                 for (int k = j - NBP, n = 0; k >= 0 && n < SB / NBP; k -= NBP, ++n) drain_slot(&b_full[k % SB], (uint32_t)(k / SB) & 1u, p.status);
             }
         }
@@ -312,8 +289,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_pair_kernel(const
                     const int jd = 4 * (it - META_SETS) + 3;
                     if (!wait_one(&b_free[jd % SF], (uint32_t)(jd / SF) & 1u, abort_flag, p.status, DEV_TIMEOUT_MMA)) break;
                 }
-                if (!wait_one(&a_full[sa], (uint32_t)(it / SA) & 1u, abort_flag, p.status, DEV_TIMEOUT_MMA)) break;
-                if (!wait_one_cluster(&peer_a[sa], (uint32_t)(it / SA) & 1u, abort_flag, p.status, DEV_TIMEOUT_MMA)) break;
+                if (!wait_one(&a_full[sa], (uint32_t)(it / SA) & 1u, abort_flag, p.status, DEV_TIMEOUT_MMA)) break;  // both CTAs' blocks
                 tc_fence_after();
                 const uint32_t mcol = tmem_base + meta_col(it % META_SETS);
 #pragma unroll
@@ -323,7 +299,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_pair_kernel(const
             }
         } else if (lane == 0) {
             // ---------------- peer: forward "A blocks landed" ----------------
-            const uint32_t remote0 = mapa_shared(smem_u32(peer_a), 0);
+            const uint32_t remote0 = mapa_shared(smem_u32(a_full), 0);
             for (int it = 0; it < total_it; ++it) {
                 const int sa = it % SA;
                 if (!wait_one(&a_full[sa], (uint32_t)(it / SA) & 1u, abort_flag, p.status, DEV_TIMEOUT_MMA)) break;
@@ -343,6 +319,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_pair_kernel(const
             const uint64_t bdesc0 = b_nk ? make_smem_desc(smem_u32(b_ring), 16, 512, 4) : make_smem_desc(smem_u32(b_ring), B_CHUNK_BYTES, 1024, 2);
             const uint32_t free_local = smem_u32(b_free), free_peer = mapa_shared(smem_u32(b_free), 1);
             const uint32_t full_local = smem_u32(acc_full_bar), full_peer = mapa_shared(smem_u32(acc_full_bar), 1);
+            const bool relay_commits = p.pair_relay != 0;  // a spare thread forwards the arrivals to the peer
             int it = 0;
             bool alive = true;
             for (int ti = 0; alive && ti < my_tiles; ++ti) {
@@ -350,7 +327,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_pair_kernel(const
                     if (!wait_one(&kready[it % SR], (uint32_t)(it / SR) & 1u, abort_flag, p.status, DEV_TIMEOUT_MMA)) { alive = false; break; }
                     tc_fence_after();
                     if (kt == 0) {
-                        if (!wait_one_cluster(acc_empty_bar, ((uint32_t)ti & 1u) ^ 1u, abort_flag, p.status, DEV_TIMEOUT_MMA)) { alive = false; break; }
+                        if (!wait_one(acc_empty_bar, ((uint32_t)ti & 1u) ^ 1u, abort_flag, p.status, DEV_TIMEOUT_MMA)) { alive = false; break; }
                         tc_fence_after();
                     }
                     const uint32_t mcol = tmem_base + meta_col(it % META_SETS);
@@ -358,8 +335,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_pair_kernel(const
 #pragma unroll
                     for (int kb = 0; kb < 4; kb++) {  // K=32 blocks of the k-tile, one B stage each
                         const int j = 4 * it + kb;
-                        if (!wait_one(&b_full[j % SB], (uint32_t)(j / SB) & 1u, abort_flag, p.status, DEV_TIMEOUT_MMA)) { alive = false; break; }
-                        if (!wait_one_cluster(&peer_b[j % SB], (uint32_t)(j / SB) & 1u, abort_flag, p.status, DEV_TIMEOUT_MMA)) { alive = false; break; }
+                        if (!wait_one(&b_full[j % SB], (uint32_t)(j / SB) & 1u, abort_flag, p.status, DEV_TIMEOUT_MMA)) { alive = false; break; }  // both halves
                         tc_fence_after();
                         const uint32_t boff = (uint32_t)((j % SB) * B_STAGE_BYTES) >> 4;
 #pragma unroll
@@ -368,18 +344,18 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_pair_kernel(const
                                            mcol + rt * 4 + (uint32_t)(kb & ~1), idesc0 | (uint32_t)(kb & 1), (kt | kb) != 0 ? 1u : 0u);
                         // the stage (and, after the fourth, the A blocks and metadata set) may be refilled in both CTAs
                         tc_commit2(free_local + (uint32_t)(j % SF) * 8u);
-                        tc_commit2(free_peer + (uint32_t)(j % SF) * 8u);
+                        if (!relay_commits) tc_commit2(free_peer + (uint32_t)(j % SF) * 8u);
                     }
                     if (!alive) break;
                     if (kt == p.ktiles - 1) {
                         tc_commit2(full_local);
-                        tc_commit2(full_peer);
+                        if (!relay_commits) tc_commit2(full_peer);
                     }
                 }
             }
         } else if (lane == 0) {
             // ---------------- peer: forward "my half of stage j landed" ----------------
-            const uint32_t remote0 = mapa_shared(smem_u32(peer_b), 0);
+            const uint32_t remote0 = mapa_shared(smem_u32(b_full), 0);
             const int total_j = 4 * total_it;
             for (int j = 0; j < total_j; ++j) {
                 if (!wait_one(&b_full[j % SB], (uint32_t)(j / SB) & 1u, abort_flag, p.status, DEV_TIMEOUT_MMA)) break;
@@ -388,7 +364,25 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_pair_kernel(const
         }
         __syncwarp();
     } else if (warp == 2) {
-        setmaxnreg_dec<64>();  // idle warp of the first warpgroup
+        setmaxnreg_dec<64>();
+        if (lane == 0 && leader_cta && p.pair_relay) {
+            // ---------------- leader: forward "stage free" and "accumulators full" to the peer ----------------
+            // (variant in which the MMA issuer commits to its own barriers only)
+            const uint32_t free_peer = mapa_shared(smem_u32(b_free), 1), full_peer = mapa_shared(smem_u32(acc_full_bar), 1);
+            const int per_tile = 4 * p.ktiles;
+            int j = 0;
+            bool alive = true;
+            for (int ti = 0; alive && ti < my_tiles; ++ti) {
+                for (int l = 0; l < per_tile; ++l, ++j) {
+                    if (!wait_one(&b_free[j % SF], (uint32_t)(j / SF) & 1u, abort_flag, p.status, DEV_TIMEOUT_MMA)) { alive = false; break; }
+                    mbar_arrive_cluster(free_peer + (uint32_t)(j % SF) * 8u);
+                }
+                if (!alive) break;
+                if (!wait_one(acc_full_bar, (uint32_t)ti & 1u, abort_flag, p.status, DEV_TIMEOUT_MMA)) break;
+                mbar_arrive_cluster(full_peer);
+            }
+        }
+        __syncwarp();
     } else {
         // ---------------- epilogue (both CTAs, own accumulators) ----------------
         setmaxnreg_inc<192>();
@@ -401,7 +395,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_pair_kernel(const
             const int mq = tile % mquads;
             const int n0 = (tile / mquads) * BN;
             // the four warps of a group leave the loop together (they meet at named barriers below)
-            const bool got = wait_warp_cluster(acc_full_bar, (uint32_t)ti & 1u, abort_flag, p.status, DEV_TIMEOUT_EPILOGUE);
+            const bool got = wait_warp(acc_full_bar, (uint32_t)ti & 1u, abort_flag, p.status, DEV_TIMEOUT_EPILOGUE);
             if (!named_barrier_and(1 + ((warp - EPI_WARP0) >> 2), 128, got)) break;
             tc_fence_after();
             {
