@@ -323,7 +323,7 @@ int vnm_set_gather_split(vnm_handle_t h, int tma_rows)
 int vnm_set_pair_mode(vnm_handle_t h, int mode)
 {
     if (!h) return fail(VNM_ERR_BAD_ARG, "null handle");
-    if (mode < 0 || mode > 2) return fail(VNM_ERR_BAD_ARG, "pair mode must be 0, 1 or 2 (got %d)", mode);
+    if (mode != 0 && mode != 1) return fail(VNM_ERR_BAD_ARG, "pair mode must be 0 or 1 (got %d)", mode);
     h->pair_mode = mode;
     return VNM_OK;
 }
@@ -424,9 +424,10 @@ static int spmm_impl(vnm_handle_t h, const void *B, int64_t ldb, int N, int b_nk
             // is the K-major operand tile of one MMA (the last 16 rows belong to the next tile and are not read).
             cuuint64_t dims[2] = {(cuuint64_t)h->K, (cuuint64_t)N};
             cuuint64_t strides[1] = {(cuuint64_t)ldb * 2};
-            cuuint32_t box[2] = {32, pair ? 128u : 256u};   // the pair kernel loads each CTA's 128-row half separately
+            // the pair kernel loads each CTA's 128-row half separately, 64 k (two MMA K blocks, 128-byte rows) per box
+            cuuint32_t box[2] = {pair ? 64u : 32u, pair ? 128u : 256u};
             r = enc(&h->tmap_tile, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(B), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, pair ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
             h->tmap_rows = h->tmap_tile;
             h->tmap_tile2 = h->tmap_tile;
@@ -438,7 +439,7 @@ static int spmm_impl(vnm_handle_t h, const void *B, int64_t ldb, int N, int b_nk
             cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)h->K};
             cuuint64_t strides[1] = {(cuuint64_t)ldb * 2};
             cuuint32_t box_rows[2] = {64, 1};
-            cuuint32_t box_tile[2] = {64, h->dense_b ? 32u : 64u};
+            cuuint32_t box_tile[2] = {64, (h->dense_b && !pair) ? 32u : 64u};
             r = enc(&h->tmap_rows, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(B), dims, strides, box_rows, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -449,11 +450,11 @@ static int spmm_impl(vnm_handle_t h, const void *B, int64_t ldb, int N, int b_nk
             h->tmap_tile2 = h->tmap_tile;
             h->tm_wide = false;
             if (r == CUDA_SUCCESS && pair) {
-                // pair kernel: a CTA's half of a stage is {64 columns, 32 rows, 2 slices} starting at any multiple of 8 columns
+                // pair kernel: a CTA's half of a stage is {64 columns, 64 rows, 2 slices} starting at any multiple of 8 columns
                 // (pair tiles start at multiples of 240, the peer's half 120 columns further)
                 cuuint64_t dims4[4] = {64, (cuuint64_t)h->K, 2, (cuuint64_t)((N - 128) / 8 + 1)};
                 cuuint64_t strides4[3] = {(cuuint64_t)ldb * 2, 128, 16};
-                cuuint32_t box4[4] = {64, 32, 2, 1};
+                cuuint32_t box4[4] = {64, 64, 2, 1};
                 cuuint32_t estr4[4] = {1, 1, 1, 1};
                 CUtensorMap wide;
                 if (enc(&wide, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void *>(B), dims4, strides4, box4, estr4,
@@ -499,7 +500,6 @@ static int spmm_impl(vnm_handle_t h, const void *B, int64_t ldb, int N, int b_nk
     p.ldb = ldb;
     p.out32 = h->out32;
     p.hybrid_rows = h->hybrid_rows;
-    p.pair_relay = h->pair_mode == 2 ? 0 : 1;  // mode 2 (ablation): a second commit to the peer instead of the forwarding thread
     p.b_nk = b_nk;
     p.b_wide_ok = h->tm_wide ? 1 : 0;
     if (h->dense_b) {

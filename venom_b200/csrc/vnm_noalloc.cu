@@ -144,7 +144,6 @@ extern "C" int vnm_spmm_f16_noalloc(const void *values, const uint32_t *meta, co
     p.ldb = ldb;
     p.out32 = 0;
     p.hybrid_rows = 0;
-    p.pair_relay = 0;
     p.b_nk = 0;
     p.b_wide_ok = 0;
     e = launch_spmm(cfg, tmap_rows, tmap_tile, p, s);

@@ -14,10 +14,10 @@
 //     exactly as in the single-CTA kernel -- anything more on the issuing thread leaves the tensor pipe idle;
 //   * only the leader issues tensor-core work: tcgen05.cp.cta_group::2 copies each CTA's metadata image into that
 //     CTA's tensor memory, tcgen05.mma.sp.cta_group::2 reads A and B from both CTAs' shared memory;
-//   * the leader's tcgen05.commit.cta_group::2 arrives on the leader's stage-free / accumulator-full barriers and a
-//     spare thread of the leader forwards each arrival to the peer's barriers (p.pair_relay = 0 instead issues a
-//     second commit to the peer's barrier through its shared::cluster address); the peer's epilogue warps arrive
-//     remotely on the leader's accumulator-empty barrier.
+//   * the leader's tcgen05.commit.cta_group::2 arrives on the stage-free / accumulator-full barriers of BOTH CTAs
+//     (two commits: the local barrier and the peer's barrier through its shared::cluster address; a spare thread
+//     forwarding the arrivals instead measured 1-2 % slower), and the peer's epilogue warps arrive remotely on the
+//     leader's accumulator-empty barrier.
 // No copy with cluster multicast is used anywhere.  Every wait is bounded (status bit, drain, return), and the two CTAs
 // meet at a cluster barrier before tensor memory is freed, so neither leaves while the other may still touch it.
 #include "vnm_internal.h"
@@ -32,12 +32,14 @@ constexpr int RT = 2;            // row tiles (accumulators) per CTA; a pair til
 constexpr int BN = 240;          // output columns per pair tile
 constexpr int PART = 40;         // columns per epilogue part / TMA store
 constexpr int SA = 3;            // A ring: k-tiles (each RT blocks)
-constexpr int SB = 12;           // B ring: stages of 32 rows x 128 columns (this CTA's half of one K=32 block of the MMAs)
-constexpr int SF = 24;           // stage "free" barriers (more than stages, so that a late waiter never sees a wrapped phase)
+constexpr int SB = 6;            // B ring: stages of 64 rows x 128 columns (this CTA's half of two K=32 blocks of the MMAs)
+constexpr int SF = 12;           // stage "free" barriers (twice the stages, so that a late waiter never sees a wrapped phase)
 constexpr int SR = 4;            // k-tile "ready" barriers
 constexpr int META_SETS = 3;     // metadata column sets in tensor memory (4 columns per row tile each)
-constexpr int B_CHUNK_BYTES = 32 * 128;            // 32 rows x 64 columns
-constexpr int B_STAGE_BYTES = 2 * B_CHUNK_BYTES;    // 8 KiB: two 64-column slices of which 120 columns are used (or 128 n-rows of 32 k)
+constexpr int KB_PER_STAGE = 2;                     // K=32 blocks per B stage: one 16 KiB TMA box (smaller boxes keep the copy engine less busy)
+constexpr int STAGES_PER_KT = 4 / KB_PER_STAGE;
+constexpr int B_CHUNK_BYTES = KB_PER_STAGE * 32 * 128;  // 64 rows x 64 columns
+constexpr int B_STAGE_BYTES = 2 * B_CHUNK_BYTES;    // 16 KiB: two 64-column slices of which 120 columns are used (or 128 n-rows of 64 k)
 constexpr int A_STAGE_BYTES = RT * AM_BLOCK_BYTES;  // 36 KiB
 constexpr int A_RING_BYTES = SA * A_STAGE_BYTES;
 constexpr int B_RING_BYTES = SB * B_STAGE_BYTES;
@@ -55,7 +57,8 @@ constexpr int TMEM_COLS = 512;
 __device__ __forceinline__ uint32_t acc_col(int rt) { return (uint32_t)rt * 256u; }
 __device__ __forceinline__ uint32_t meta_col(int set) { return set == 0 ? 240u : (set == 1 ? 248u : 496u); }
 static_assert(SB % NBP == 0 && NBP <= 4, "B producers");
-static_assert(SF >= 4 * SA && SF >= 4 * META_SETS && SF >= 2 * SB && SF % SB == 0, "too few stage barriers: a waiter could miss a phase");
+constexpr int KT_RING = SB / STAGES_PER_KT;  // k-tiles the B ring holds
+static_assert(SB % STAGES_PER_KT == 0 && KT_RING == SA && KT_RING == META_SETS && SF == 2 * SB, "the rings and the metadata sets advance one k-tile at a time");
 static_assert(BN <= 240 && META_SETS == 3 && RT == 2 && BN % 16 == 0 && BN == 6 * PART, "tensor-memory column plan");
 static_assert((SA + SB + SF + SR + 2) * 8 + 16 <= BAR_BYTES, "barrier area too small");
 constexpr int HALF_N = BN / 2;   // columns of a B stage held by each CTA of the pair
@@ -150,10 +153,12 @@ __device__ __forceinline__ bool wait_warp(uint64_t *bar, uint32_t parity, volati
 
 // Warp roles (512 threads per CTA, as in the single-CTA kernel):
 //   warp 0      A producer: two bulk copies per k-tile (this CTA's two row tiles).
-//   warp 1      leader: sequencer (waits for both CTAs' A blocks, copies both metadata images to tensor memory);
+//   warp 1      leader: sequencer (waits for both CTAs' A blocks, copies both metadata images to tensor memory, waits
+//               for the four B stages of the k-tile, then flips the k-tile's "ready" barrier);
 //               peer: forwards "A blocks landed" to the leader.
-//   warp 3      tensor-memory owner in both CTAs; leader: MMA issuer; peer: forwards "B half landed" to the leader.
-//   warps 4..6  B producers: one 8 KiB TMA box per stage (this CTA's 128-column half).
+//   warp 3      tensor-memory owner in both CTAs; leader: MMA issuer (one wait, eight MMAs and two commits per k-tile);
+//               peer: forwards "B half landed" to the leader.
+//   warps 4..6  B producers: one 16 KiB TMA box per stage (64 rows of this CTA's 128-column half).
 //   warps 8..15 epilogue of this CTA's two accumulators.
 __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_pair_kernel(const __grid_constant__ CUtensorMap tmap_tile, const __grid_constant__ CUtensorMap tmap_tile2,
                                                                            const __grid_constant__ CUtensorMap tmap_out, const SpmmParams p)
@@ -189,7 +194,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_pair_kernel(const
         for (int s = 0; s < SA; s++) mbar_init(&a_full[s], leader_cta ? 2 : 1);
         for (int s = 0; s < SB; s++) mbar_init(&b_full[s], leader_cta ? 2 : 1);
         for (int s = 0; s < SF; s++) mbar_init(&b_free[s], 1);
-        for (int s = 0; s < SR; s++) mbar_init(&kready[s], 1);
+        for (int s = 0; s < SR; s++) mbar_init(&kready[s], 2);  // metadata copied to tensor memory + all operands landed
         mbar_init(acc_full_bar, 1);
         mbar_init(acc_empty_bar, 2 * 4 * R);  // the epilogue warps of both CTAs
         *abort_flag = 0;
@@ -218,7 +223,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_pair_kernel(const
                 for (int kt = 0; kt < p.ktiles; ++kt, ++it) {
                     const int s = it % SA;
                     if (it >= SA) {
-                        const int jd = 4 * (it - SA) + 3;  // last B stage of the k-tile that used this slot
+                        const int jd = STAGES_PER_KT * (it - SA) + STAGES_PER_KT - 1;  // last B stage of the k-tile that used this slot
                         if (!wait_one(&b_free[jd % SF], (uint32_t)(jd / SF) & 1u, abort_flag, p.status, DEV_TIMEOUT_PRODUCER)) { alive = false; break; }
                     }
                     mbar_arrive_expect_tx(&a_full[s], R * AM_BLOCK_BYTES);
@@ -242,7 +247,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_pair_kernel(const
         if (lane == 0 && warp - 4 < NBP) {
             tma_prefetch_desc(&tmap_tile);
             tma_prefetch_desc(&tmap_tile2);
-            const int per_tile = 4 * p.ktiles;
+            const int per_tile = STAGES_PER_KT * p.ktiles;
             int j = warp - 4;
             int tile_i = j / per_tile, jl = j - tile_i * per_tile;
             const int total_j = my_tiles * per_tile;
@@ -261,14 +266,14 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_pair_kernel(const
                     while (jl >= per_tile) { jl -= per_tile; ++tile_i; }
                     continue;
                 }
-                // 128 columns come along per stage; the MMA reads the first 120 of them
+                // 64 rows x 128 columns come along per stage; the MMAs read the first 120 columns
                 mbar_arrive_expect_tx(&b_full[s], B_STAGE_BYTES);
                 if (p.b_nk) {
-                    tma_load_2d(dst, &tmap_tile, jl * 32, n0, &b_full[s]);  // 128 rows (n) x 32 k, 64-byte swizzle
+                    tma_load_2d(dst, &tmap_tile, jl * 64, n0, &b_full[s]);  // 128 rows (n) x 64 k, 128-byte swizzle
                 } else if (p.b_wide_ok && n0 + 128 <= p.N) {
-                    tma_load_4d(dst, &tmap_tile, 0, jl * 32, 0, n0 / 8, &b_full[s]);  // {64 columns, 32 rows, 2 slices} from column n0
+                    tma_load_4d(dst, &tmap_tile, 0, jl * 64, 0, n0 / 8, &b_full[s]);  // {64 columns, 64 rows, 2 slices} from column n0
                 } else {  // ragged right edge: two boxes that clip (and zero-fill) at N
-                    for (int c = 0; c < 2; c++) tma_load_2d(dst + c * B_CHUNK_BYTES, &tmap_tile2, n0 + c * 64, jl * 32, &b_full[s]);
+                    for (int c = 0; c < 2; c++) tma_load_2d(dst + c * B_CHUNK_BYTES, &tmap_tile2, n0 + c * 64, jl * 64, &b_full[s]);
                 }
                 jl += NBP;
                 while (jl >= per_tile) { jl -= per_tile; ++tile_i; }
@@ -286,7 +291,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_pair_kernel(const
             for (int it = 0; it < total_it; ++it) {
                 const int sa = it % SA;
                 if (it >= META_SETS) {  // column set it % META_SETS was last read by the MMAs of k-tile it - META_SETS
-                    const int jd = 4 * (it - META_SETS) + 3;
+                    const int jd = STAGES_PER_KT * (it - META_SETS) + STAGES_PER_KT - 1;
                     if (!wait_one(&b_free[jd % SF], (uint32_t)(jd / SF) & 1u, abort_flag, p.status, DEV_TIMEOUT_MMA)) break;
                 }
                 if (!wait_one(&a_full[sa], (uint32_t)(it / SA) & 1u, abort_flag, p.status, DEV_TIMEOUT_MMA)) break;  // both CTAs' blocks
@@ -295,7 +300,18 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_pair_kernel(const
 #pragma unroll
                 for (int rt = 0; rt < R; rt++)
                     tc_cp2_128x128b(mcol + rt * 4, mdesc0 + ((uint32_t)(sa * A_STAGE_BYTES + rt * AM_BLOCK_BYTES) >> 4));
-                tc_commit2(smem_u32(&kready[it % SR]));
+                tc_commit2(smem_u32(&kready[it % SR]));  // first arrival: the metadata copies are done
+                // The B stages of the k-tile are waited for here, not by the MMA issuer: every probe of a barrier
+                // costs the issuing thread about as much as one MMA takes to execute, and the tensor pipe queues next to
+                // nothing, so a wait between two MMAs is a bubble in the pipe.
+                bool alive = true;
+#pragma unroll
+                for (int st = 0; st < STAGES_PER_KT; st++) {
+                    const int j = STAGES_PER_KT * it + st;
+                    if (!wait_one(&b_full[j % SB], (uint32_t)(j / SB) & 1u, abort_flag, p.status, DEV_TIMEOUT_MMA)) { alive = false; break; }  // both halves
+                }
+                if (!alive) break;
+                mbar_arrive(&kready[it % SR]);  // second arrival: every operand of the k-tile is in shared memory
             }
         } else if (lane == 0) {
             // ---------------- peer: forward "A blocks landed" ----------------
@@ -314,49 +330,58 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_pair_kernel(const
             const bool b_nk = p.b_nk != 0;
             const uint32_t idesc0 = make_idesc_f16(2 * TILE_M, BN, true, 0u, !b_nk);
             const uint64_t adesc0 = make_smem_desc(smem_u32(a_ring), 16, 1024, 2);
-            // this CTA's half of a stage: N-major (two 64-column slices of 32 rows x 128 bytes, 128-byte swizzle) or K-major
-            // (128 n-rows of 64 bytes of which 120 are used, 64-byte swizzle, 8-row groups 512 bytes apart)
-            const uint64_t bdesc0 = b_nk ? make_smem_desc(smem_u32(b_ring), 16, 512, 4) : make_smem_desc(smem_u32(b_ring), B_CHUNK_BYTES, 1024, 2);
+            // this CTA's half of a stage: N-major (two 64-column slices of 64 rows x 128 bytes, 128-byte swizzle; a K=32 block is
+            // 32 rows = 4096 bytes further) or K-major (128 n-rows of 128 bytes = 64 k of which 120 rows are used, 128-byte swizzle,
+            // 8-row groups 1024 bytes apart; a K=32 block is 64 bytes further inside the row)
+            const uint64_t bdesc0 = b_nk ? make_smem_desc(smem_u32(b_ring), 16, 1024, 2) : make_smem_desc(smem_u32(b_ring), B_CHUNK_BYTES, 1024, 2);
+            const uint32_t kb_step = b_nk ? 64u : 32u * 128u;  // bytes between the K=32 blocks of a stage
             const uint32_t free_local = smem_u32(b_free), free_peer = mapa_shared(smem_u32(b_free), 1);
             const uint32_t full_local = smem_u32(acc_full_bar), full_peer = mapa_shared(smem_u32(acc_full_bar), 1);
-            const bool relay_commits = p.pair_relay != 0;  // a spare thread forwards the arrivals to the peer
-            int it = 0;
-            bool alive = true;
+            // The thread runs about one MMA ahead of the tensor pipe, so whatever it does between two MMAs must take less
+            // than one MMA (about 140 clocks).  A k-tile is therefore one wait, eight MMAs and two commits, and the wait for
+            // the NEXT k-tile sits in front of the last two MMAs, where the pipe still has work queued.
+            int it = 0, slot = 0;  // slot = it % KT_RING
+            bool alive = total_it > 0 && wait_one(&kready[0], 0u, abort_flag, p.status, DEV_TIMEOUT_MMA);
+            tc_fence_after();
             for (int ti = 0; alive && ti < my_tiles; ++ti) {
                 for (int kt = 0; alive && kt < p.ktiles; ++kt, ++it) {
-                    if (!wait_one(&kready[it % SR], (uint32_t)(it / SR) & 1u, abort_flag, p.status, DEV_TIMEOUT_MMA)) { alive = false; break; }
-                    tc_fence_after();
                     if (kt == 0) {
                         if (!wait_one(acc_empty_bar, ((uint32_t)ti & 1u) ^ 1u, abort_flag, p.status, DEV_TIMEOUT_MMA)) { alive = false; break; }
                         tc_fence_after();
                     }
-                    const uint32_t mcol = tmem_base + meta_col(it % META_SETS);
-                    const uint32_t aoff = (uint32_t)((it % SA) * A_STAGE_BYTES) >> 4;
+                    const uint32_t mcol = tmem_base + meta_col(slot);
+                    const uint32_t aoff = (uint32_t)(slot * A_STAGE_BYTES) >> 4;
+                    const uint32_t boff0 = (uint32_t)(slot * STAGES_PER_KT * B_STAGE_BYTES) >> 4;
 #pragma unroll
-                    for (int kb = 0; kb < 4; kb++) {  // K=32 blocks of the k-tile, one B stage each
-                        const int j = 4 * it + kb;
-                        if (!wait_one(&b_full[j % SB], (uint32_t)(j / SB) & 1u, abort_flag, p.status, DEV_TIMEOUT_MMA)) { alive = false; break; }  // both halves
-                        tc_fence_after();
-                        const uint32_t boff = (uint32_t)((j % SB) * B_STAGE_BYTES) >> 4;
+                    for (int kb = 0; kb < 4; kb++) {  // K=32 blocks of the k-tile, KB_PER_STAGE of them per B stage
+                        if (kb == 3 && it + 1 < total_it) {
+                            if (!wait_one(&kready[(it + 1) % SR], (uint32_t)((it + 1) / SR) & 1u, abort_flag, p.status, DEV_TIMEOUT_MMA)) { alive = false; break; }
+                            tc_fence_after();
+                        }
+                        const uint32_t boff = boff0 + (((uint32_t)(kb / KB_PER_STAGE) * B_STAGE_BYTES + (uint32_t)(kb % KB_PER_STAGE) * kb_step) >> 4);
 #pragma unroll
                         for (int rt = 0; rt < R; rt++)
                             tc_mma2_sp_f16(tmem_base + acc_col(rt), adesc0 + aoff + (uint32_t)((rt * AM_BLOCK_BYTES + kb * 32) >> 4), bdesc0 + boff,
                                            mcol + rt * 4 + (uint32_t)(kb & ~1), idesc0 | (uint32_t)(kb & 1), (kt | kb) != 0 ? 1u : 0u);
-                        // the stage (and, after the fourth, the A blocks and metadata set) may be refilled in both CTAs
-                        tc_commit2(free_local + (uint32_t)(j % SF) * 8u);
-                        if (!relay_commits) tc_commit2(free_peer + (uint32_t)(j % SF) * 8u);
+                        if (kb % KB_PER_STAGE == KB_PER_STAGE - 1) {
+                            // the stage (and, after the last, the A blocks and the metadata set) may be refilled in both CTAs
+                            const int j = STAGES_PER_KT * it + kb / KB_PER_STAGE;
+                            tc_commit2(free_local + (uint32_t)(j % SF) * 8u);
+                            tc_commit2(free_peer + (uint32_t)(j % SF) * 8u);
+                        }
                     }
                     if (!alive) break;
                     if (kt == p.ktiles - 1) {
                         tc_commit2(full_local);
-                        if (!relay_commits) tc_commit2(full_peer);
+                        tc_commit2(full_peer);
                     }
+                    slot = slot + 1 == KT_RING ? 0 : slot + 1;
                 }
             }
         } else if (lane == 0) {
             // ---------------- peer: forward "my half of stage j landed" ----------------
             const uint32_t remote0 = mapa_shared(smem_u32(b_full), 0);
-            const int total_j = 4 * total_it;
+            const int total_j = STAGES_PER_KT * total_it;
             for (int j = 0; j < total_j; ++j) {
                 if (!wait_one(&b_full[j % SB], (uint32_t)(j / SB) & 1u, abort_flag, p.status, DEV_TIMEOUT_MMA)) break;
                 mbar_arrive_cluster(remote0 + (uint32_t)(j % SB) * 8u);
@@ -364,25 +389,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_pair_kernel(const
         }
         __syncwarp();
     } else if (warp == 2) {
-        setmaxnreg_dec<64>();
-        if (lane == 0 && leader_cta && p.pair_relay) {
-            // ---------------- leader: forward "stage free" and "accumulators full" to the peer ----------------
-            // (variant in which the MMA issuer commits to its own barriers only)
-            const uint32_t free_peer = mapa_shared(smem_u32(b_free), 1), full_peer = mapa_shared(smem_u32(acc_full_bar), 1);
-            const int per_tile = 4 * p.ktiles;
-            int j = 0;
-            bool alive = true;
-            for (int ti = 0; alive && ti < my_tiles; ++ti) {
-                for (int l = 0; l < per_tile; ++l, ++j) {
-                    if (!wait_one(&b_free[j % SF], (uint32_t)(j / SF) & 1u, abort_flag, p.status, DEV_TIMEOUT_MMA)) { alive = false; break; }
-                    mbar_arrive_cluster(free_peer + (uint32_t)(j % SF) * 8u);
-                }
-                if (!alive) break;
-                if (!wait_one(acc_full_bar, (uint32_t)ti & 1u, abort_flag, p.status, DEV_TIMEOUT_MMA)) break;
-                mbar_arrive_cluster(full_peer);
-            }
-        }
-        __syncwarp();
+        setmaxnreg_dec<64>();  // idle warp of the first warpgroup
     } else {
         // ---------------- epilogue (both CTAs, own accumulators) ----------------
         setmaxnreg_inc<192>();
