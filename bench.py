@@ -458,6 +458,9 @@ def main():
     flops_step = useful_flops(M, K, m, N)          # the whole job
     value = flops_step / (ms_step * 1e-3) / 1e12
     form = "dense-B" if prep.dense_b_form() else "gather"
+    kcfg = prep.config(ns)
+    kernel_name = ("vnm::spmm_dense_b_pair_kernel (clusters of two CTAs, tcgen05 cta_group::2)" if kcfg["tile_m"] == 512 else
+                   "vnm::spmm_dense_b_kernel" if form == "dense-B" else "vnm::spmm_kernel")
 
     if args.kernel_only:
         if rank == 0:
@@ -561,7 +564,7 @@ def main():
         per_gpu = value / world
         roofline = {"bound": "tensor", "achieved": per_gpu, "peak": peaks["tflops_sustained"], "unit": "TFLOP/s", "frac": per_gpu / peaks["tflops_sustained"],
                     "traffic": NCU_TRAFFIC["bytes_per_launch"], "traffic_source": NCU_TRAFFIC["source"], "peak_source": peaks["source"] + " (sustained dense bf16; useful FLOPs of a 2:4 MMA run at most at the dense rate)",
-                    "kernel": "vnm::spmm_dense_b_kernel" if form == "dense-B" else "vnm::spmm_kernel", "operand_form": form,
+                    "kernel": kernel_name, "operand_form": form, "grid": kcfg["grid"],
                     "useful_flops_per_launch": flops_step / world, "launch_ms": ms_step,
                     "frac_of_burst_peak": per_gpu / peaks["tflops_burst"],
                     "algorithmic_bytes_per_launch": algorithmic_bytes(M, K, V, m, ns),

@@ -58,6 +58,20 @@ constexpr int AM_BLOCK_BYTES = A_IMG_BYTES + META_IMG_BYTES;  // 18432
 __host__ __device__ inline int mma_row_to_actual(int i) { int w = i & 15; return (i & ~15) + ((w & 7) << 1) + (w >> 3); }
 __host__ __device__ inline int actual_to_mma_row(int a) { int x = a & 15; return (a & ~15) + ((x & 1) << 3) + (x >> 1); }
 
+// Tile order of the persistent dense-B kernels: row groups (units of one CTA tile's rows) are taken `group` at a time
+// and, inside such a band, column tiles advance slowest.  The CTAs that run together then share `group` row groups of
+// A and a few column panels of B, a working set that stays in L2, instead of streaming all of A past every column
+// tile (which re-reads A from HBM once per column tile as soon as A is larger than L2).
+__host__ __device__ inline void tile_coords(int tile, int row_groups, int ntiles, int group, int *rg, int *nt)
+{
+    const int band = tile / (group * ntiles);
+    const int first = band * group;
+    const int size = row_groups - first < group ? row_groups - first : group;
+    const int within = tile - band * group * ntiles;
+    *nt = within / size;
+    *rg = first + within % size;
+}
+
 #if defined(__CUDACC__)
 // ------------------------------------------------------------------------------------------------
 // PTX wrappers

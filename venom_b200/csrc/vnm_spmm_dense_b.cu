@@ -115,7 +115,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_kernel(const __gr
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    // tiles: pairs of row tiles (fastest) x column tiles
+    // tiles: pairs of row tiles x column tiles, in the banded order of tile_coords()
     static_assert(R == 1 || R == RT, "row tiles per CTA tile");
     const int mpairs = (p.mtiles + R - 1) / R;
     const int total_tiles = mpairs * p.ntiles;
@@ -150,7 +150,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_kernel(const __gr
             int it = 0;
             bool alive = true;
             for (int tile = blockIdx.x; alive && tile < total_tiles; tile += gridDim.x) {
-                const int mp = tile % mpairs;
+                int mp, nt_unused;
+                tile_coords(tile, mpairs, p.ntiles, p.group_m, &mp, &nt_unused);
                 for (int kt = 0; kt < p.ktiles; ++kt, ++it) {
                     const int s = it % SA;
                     if (it >= SA) {
@@ -186,7 +187,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_kernel(const __gr
             const int total_j = my_tiles * per_tile;
             for (; j < total_j; j += NBP) {
                 const int tile = (int)blockIdx.x + tile_i * (int)gridDim.x;
-                const int n0 = (tile / mpairs) * BN;
+                int mp_unused, nt;
+                tile_coords(tile, mpairs, p.ntiles, p.group_m, &mp_unused, &nt);
+                const int n0 = nt * BN;
                 const int s = j % SB;
                 if (j >= SB) {
                     const int jd = j - SB;
@@ -289,8 +292,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_kernel(const __gr
         int ti = 0;
         // with one row tile per CTA tile the second group of four warps has no accumulator to drain
         for (int tile = ((warp - EPI_WARP0) >> 2) < R ? (int)blockIdx.x : total_tiles; tile < total_tiles; tile += gridDim.x, ++ti) {
-            const int mp = tile % mpairs;
-            const int n0 = (tile / mpairs) * BN;
+            int mp, nt;
+            tile_coords(tile, mpairs, p.ntiles, p.group_m, &mp, &nt);
+            const int n0 = nt * BN;
             // the four warps of a group leave the loop together (they meet at named barriers below)
             const bool got = wait_warp(acc_full_bar, (uint32_t)ti & 1u, abort_flag, p.status, DEV_TIMEOUT_EPILOGUE);
             if (!named_barrier_and(1 + ((warp - EPI_WARP0) >> 2), 128, got)) break;

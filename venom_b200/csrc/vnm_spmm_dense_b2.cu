@@ -183,7 +183,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_pair_kernel(const
     const uint32_t crank = cluster_ctarank();
     const bool leader_cta = crank == 0;
     const int pair = (int)blockIdx.x >> 1, npairs = (int)gridDim.x >> 1;
-    // tiles of the pair: groups of 2 * R row tiles (fastest) x column tiles
+    // tiles of the pair: groups of 2 * R row tiles x column tiles, in the banded order of tile_coords()
     const int mquads = (p.mtiles + 2 * R - 1) / (2 * R);
     const int total_tiles = mquads * p.ntiles;
     const int my_tiles = (pair < total_tiles) ? (total_tiles - pair + npairs - 1) / npairs : 0;
@@ -219,7 +219,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_pair_kernel(const
             int it = 0;
             bool alive = true;
             for (int tile = pair; alive && tile < total_tiles; tile += npairs) {
-                const int mq = tile % mquads;
+                int mq, nt_unused;
+                tile_coords(tile, mquads, p.ntiles, p.group_m, &mq, &nt_unused);
                 for (int kt = 0; kt < p.ktiles; ++kt, ++it) {
                     const int s = it % SA;
                     if (it >= SA) {
@@ -253,7 +254,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_pair_kernel(const
             const int total_j = my_tiles * per_tile;
             for (; j < total_j; j += NBP) {
                 const int tile = pair + tile_i * npairs;
-                const int n0 = (tile / mquads) * BN + (int)crank * HALF_N;  // first column of this CTA's half
+                int mq_unused, nt;
+                tile_coords(tile, mquads, p.ntiles, p.group_m, &mq_unused, &nt);
+                const int n0 = nt * BN + (int)crank * HALF_N;  // first column of this CTA's half
                 const int s = j % SB;
                 if (j >= SB) {
                     const int jd = j - SB;
@@ -399,8 +402,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_pair_kernel(const
         const uint32_t empty_leader = mapa_shared(smem_u32(acc_empty_bar), 0);
         int ti = 0;
         for (int tile = pair; tile < total_tiles; tile += npairs, ++ti) {
-            const int mq = tile % mquads;
-            const int n0 = (tile / mquads) * BN;
+            int mq, nt;
+            tile_coords(tile, mquads, p.ntiles, p.group_m, &mq, &nt);
+            const int n0 = nt * BN;
             // the four warps of a group leave the loop together (they meet at named barriers below)
             const bool got = wait_warp(acc_full_bar, (uint32_t)ti & 1u, abort_flag, p.status, DEV_TIMEOUT_EPILOGUE);
             if (!named_barrier_and(1 + ((warp - EPI_WARP0) >> 2), 128, got)) break;

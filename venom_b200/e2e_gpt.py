@@ -128,9 +128,14 @@ def main(argv=None):
     gathered = torch.empty_like(x_all) if world > 1 else None
 
     hooks = []
+    mgpu_ctx = None
 
     def install_gather_hooks():
-        # the replicated copy of every linear's output, as a caller that does not shard the following op would need it
+        """The replicated copy of every linear's output, as a caller that does not shard the following op would need it.
+        Sparse linears go through the library's chunked gathered product (the exchange of one column chunk travels while
+        the next chunk is multiplied); dense linears use a plain all-gather after the product."""
+        nonlocal mgpu_ctx
+        from . import capi
         bufs = {}
 
         def hook(mod, inp, out):
@@ -139,12 +144,32 @@ def main(argv=None):
             if key not in bufs:
                 bufs[key] = torch.empty((flat.shape[0] * world, flat.shape[1]), dtype=flat.dtype, device=flat.device)
             dist.all_gather_into_tensor(bufs[key], flat.contiguous())
+
+        class GatheredSparseLinear(torch.nn.Module):
+            def __init__(self, sp):
+                super().__init__()
+                self.sp = sp
+                self.prep = capi.Prepared(sp.values, sp.metadata, sp.columns, sp.nrows_sp, sp.ncols_sp, sp.v, sp.m, sp.n)
+
+            def forward(self, x):
+                flat = x.reshape(-1, x.shape[-1])
+                ns = flat.shape[0]
+                key = (ns * world, self.sp.nrows_sp)
+                if key not in bufs:
+                    bufs[key] = torch.empty(key, dtype=flat.dtype, device=flat.device)
+                full = mgpu_ctx.spmm_gathered(self.prep, flat.t().contiguous(), ns * world, bias=self.sp.bias, out=bufs[key], chunks=4)
+                return full[rank * ns:(rank + 1) * ns].reshape(*x.shape[:-1], -1)
+
         for h in hooks:
             h.remove()
         hooks.clear()
         for layer in block:
-            for child in layer.children():
-                if hasattr(child, "nrows_sp") or isinstance(child, torch.nn.Linear):
+            for name, child in list(layer.named_children()):
+                if hasattr(child, "nrows_sp"):
+                    if mgpu_ctx is None:
+                        mgpu_ctx = capi.Mgpu.create_torch()
+                    setattr(layer, name, GatheredSparseLinear(child))
+                elif isinstance(child, torch.nn.Linear):
                     hooks.append(child.register_forward_hook(hook))
 
     if args.gather_every_layer and world > 1:
