@@ -500,9 +500,9 @@ static int spmm_impl(vnm_handle_t h, const void *B, int64_t ldb, int N, int b_nk
     p.ldb = ldb;
     p.out32 = h->out32;
     {
-        // band height of the dense-B tile order: as many row groups as keep their A blocks (18 KiB per row tile and k-tile)
+        // band height of the tile order (tile_coords): as many row groups as keep their A blocks (18 KiB per row tile and k-tile)
         // within about 48 MB, so that A and the few B panels in flight stay in L2
-        const int64_t rows_per_group = (int64_t)cfg.nb * TILE_M;   // 256 (one SM per tile, two row tiles), 128 or 512 (pairs)
+        const int64_t rows_per_group = h->dense_b ? (int64_t)cfg.nb * TILE_M : TILE_M;   // dense-B: 256 / 128 (one SM per tile) or 512 (pairs); gather: 128
         const int64_t bytes_per_group = (rows_per_group / TILE_M) * (int64_t)h->ktiles * AM_BLOCK_BYTES;
         int64_t g = bytes_per_group > 0 ? ((int64_t)48 << 20) / bytes_per_group : 1;
         p.group_m = (int)(g < 1 ? 1 : (g > 4096 ? 4096 : g));

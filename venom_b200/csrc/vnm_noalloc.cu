@@ -143,7 +143,7 @@ extern "C" int vnm_spmm_f16_noalloc(const void *values, const uint32_t *meta, co
     p.B = (const __half *)B;
     p.ldb = ldb;
     p.out32 = 0;
-    p.group_m = 1;
+    p.group_m = mtiles;  // operands this small fit in L2 whole: row tiles fastest
     p.hybrid_rows = 0;
     p.b_nk = 0;
     p.b_wide_ok = 0;

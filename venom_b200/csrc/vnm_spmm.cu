@@ -1,7 +1,7 @@
 // V:N:M SpMM for sm_100a: C[M,N] = A_vnm[M,K] * B[K,N], fp16 in, fp32 accumulate in tensor memory.
 //
-// Persistent kernel: one CTA per SM walks over 128 x BN output tiles (row tiles fastest, so the CTAs
-// that run together share a column panel of B in L2).  The 128 rows of a tile hold NB = 128/V vector
+// Persistent kernel: one CTA per SM walks over 128 x BN output tiles (in the banded order of tile_coords(): the
+// CTAs that run together share a few column panels of B and a band of row tiles of A that stays in L2).  The 128 rows of a tile hold NB = 128/V vector
 // blocks; each block has its own column-loc, hence its own gathered rows of B.
 //
 // Two shared-memory rings feed the tensor core:
@@ -180,7 +180,8 @@ __global__ void __launch_bounds__(Traits<BN, NB, SA, SB, PB>::NUM_THREADS, 1)
         if (lane == 0) {
             bool alive = true;
             for (int tile = blockIdx.x; alive && tile < p.total_tiles; tile += gridDim.x) {
-                const int mt = tile % p.mtiles;
+                int mt, nt_unused;
+                tile_coords(tile, p.mtiles, p.ntiles, p.group_m, &mt, &nt_unused);
                 for (int kt = 0; kt < p.ktiles; ++kt, ++it) {
                     const int s = it % SA;
                     if (it >= SA) {
@@ -247,7 +248,8 @@ __global__ void __launch_bounds__(Traits<BN, NB, SA, SB, PB>::NUM_THREADS, 1)
             int rcur[PASSES], rnxt[PASSES];
             int4 gcur = make_int4(0, 0, 0, 0), gnxt = make_int4(0, 0, 0, 0);
             auto load_rows = [&](int tl, int l, int(&dst)[PASSES], int4 &g4) {
-                const int mt = tl % p.mtiles;
+                int mt, nt_unused;
+                tile_coords(tl, p.mtiles, p.ntiles, p.group_m, &mt, &nt_unused);
 #pragma unroll
                 for (int i = 0; i < PASSES; i++)
                     if (i < passes) dst[i] = __ldg(rows_i32 + ((size_t)(mt * NB + blk[i]) * p.ktiles * KT_GROUPS) * 4 + (size_t)l * BS_ROWS + rsel[i]);
@@ -269,7 +271,9 @@ __global__ void __launch_bounds__(Traits<BN, NB, SA, SB, PB>::NUM_THREADS, 1)
                 }
                 uint8_t *stp = b_ring + s * T::B_STAGE_BYTES;
                 const uint32_t st = smem_u32(stp);
-                const int n0 = (tile / p.mtiles) * BN;
+                int mt_unused, nt_cur;
+                tile_coords(tile, p.mtiles, p.ntiles, p.group_m, &mt_unused, &nt_cur);
+                const int n0 = nt_cur * BN;
                 if (HT) {
                     if (leader) mbar_arrive_expect_tx(&b_full[s], (uint32_t)(HT * 512));  // NB * BN = 256 columns of HT rows
                     if (tma_lane) tma_gather4(stp + gb * T::B_BLOCK_BYTES + gc * T::B_CHUNK_BYTES + gg * 512, &tmap_rows, n0 + gc * 64, gcur, &b_full[s]);
@@ -314,7 +318,8 @@ __global__ void __launch_bounds__(Traits<BN, NB, SA, SB, PB>::NUM_THREADS, 1)
             int tile = blockIdx.x, jl = 0;
             bool valid = tile < p.total_tiles;
             auto rows_of = [&](int tl, int l) -> const int4 * {
-                const int mt = tl % p.mtiles;
+                int mt, nt_unused;
+                tile_coords(tl, p.mtiles, p.ntiles, p.group_m, &mt, &nt_unused);
                 const int b = gather_lane ? gb : tb;
                 return p.rows + ((size_t)(mt * NB + b) * p.ktiles) * KT_GROUPS + (size_t)l * BS_GROUPS + (gather_lane ? gg : 0);
             };
@@ -333,7 +338,9 @@ __global__ void __launch_bounds__(Traits<BN, NB, SA, SB, PB>::NUM_THREADS, 1)
                     if (!wait_one(&kdone[kd % T::SP], (uint32_t)(kd / T::SP) & 1u, abort_flag, p.status, DEV_TIMEOUT_PRODUCER)) break;
                 }
                 uint8_t *st = b_ring + s * T::B_STAGE_BYTES;
-                const int n0 = (tile / p.mtiles) * BN;
+                int mt_unused, nt_cur;
+                tile_coords(tile, p.mtiles, p.ntiles, p.group_m, &mt_unused, &nt_cur);
+                const int n0 = nt_cur * BN;
                 if (leader) {
                     if (gmode == GATHER_NONE) mbar_arrive(&b_full[s]);
                     else mbar_arrive_expect_tx(&b_full[s], T::B_STAGE_BYTES);
@@ -446,8 +453,9 @@ __global__ void __launch_bounds__(Traits<BN, NB, SA, SB, PB>::NUM_THREADS, 1)
         const int arow = mma_row_to_actual(i);
         int ti = 0;
         for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x, ++ti) {
-            const int mt = tile % p.mtiles;
-            const int n0 = (tile / p.mtiles) * BN;
+            int mt, nt_cur;
+            tile_coords(tile, p.mtiles, p.ntiles, p.group_m, &mt, &nt_cur);
+            const int n0 = nt_cur * BN;
             if (!wait_bounded(acc_full_bar, (uint32_t)ti & 1u, abort_flag, p.status, DEV_TIMEOUT_EPILOGUE)) break;
             tc_fence_after();
             // The tile is drained in parts of 64 columns to bound the register footprint; the
