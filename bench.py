@@ -359,6 +359,7 @@ def main():
     ap.add_argument("--no-extras", action="store_true", help="skip the cfg1 sweep, compressor and BERT records")
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--kernel-only", action="store_true", help="only the headline product (used for ncu captures)")
+    ap.add_argument("--sweep-only", action="store_true", help="only the cfg1 sweep record (used for ncu launch lists); one GPU")
     ap.add_argument("--n-cols", type=int, default=CFG4["N"], help="total N of the headline product (smaller values are for ncu captures only)")
     ap.add_argument("--m-rows", type=int, default=CFG4["M"], help="M of the headline product (smaller values are for ncu captures only)")
     args = ap.parse_args()
@@ -389,6 +390,10 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
     orc = Oracle()
     orc.set_num_threads(host_cores())
+
+    if args.sweep_only:
+        print(json.dumps({"cfg1_sweep": extra_cfg1_sweep(torch, capi, orc, dev, args.steps)}), flush=True)
+        return
 
     M, K, V, m = args.m_rows, CFG4["K"], CFG4["V"], CFG4["m"]
     N = args.n_cols
