@@ -119,3 +119,31 @@ def test_compress_strided_dense(capi, oracle):
     v, me, bad = capi.compress(big[:, :K], torch.from_numpy(cols.view(np.int32)).cuda(), V, m)
     ov, om, _ = oracle.compress(dense, cols, V, m)
     assert bad == 0 and np.array_equal(_u16(v.cpu().numpy()), _u16(ov)) and np.array_equal(me.cpu().numpy().view(np.uint32), om)
+
+
+@pytest.mark.parametrize("use_mask", [False, True])
+def test_column_offsets_outside_their_group_count_as_violations(capi, use_mask):
+    """A corrupt column-loc entry (offset >= m) is never dereferenced: the (row, group) pairs it touches are reported as
+    violations and every other group still compresses to the same bits (register form without a mask, tiled form with one)."""
+    import torch
+    from venom_b200.synth import random_vnm_dense
+    M, K, V, m = 128, 512, 64, 8
+    dense, cols, mask = random_vnm_dense(M, K, V, m, seed=21)
+    d = torch.from_numpy(dense).cuda()
+    mk = torch.from_numpy(mask).cuda() if use_mask else None
+    good_v, good_m, bad0 = capi.compress(d, torch.from_numpy(cols.view(np.int32)).cuda(), V, m, mask=mk)
+    assert bad0 == 0
+    broken = cols.copy().reshape(M // V, -1, 4)
+    broken[1, 5, 3] = 4000000000                      # second vector block, group 5: far outside the group
+    v, me, bad = capi.compress(d, torch.from_numpy(broken.reshape(-1).view(np.int32)).cuda(), V, m, mask=mk)
+    assert bad == V                                   # one violation per row of the vector block
+    gv, bv = good_v.cpu().numpy().view(np.uint16).copy(), v.cpu().numpy().view(np.uint16).copy()
+    from venom_b200.synth import vnm_sizes
+    ksp = vnm_sizes(M, K, V, m)[0]
+    # compare everything except the compressed columns of group 5 (2 halves per row) of rows V .. 2V-1
+    rows = np.arange(M)[:, None]
+    j = np.arange(ksp)[None, :]
+    idx = (rows // 16) * 16 * ksp + (j // 8) * 128 + ((rows % 16) // 4) * 32 + ((j // 2) % 4) * 8 + (rows % 4) * 2 + (j % 2)
+    keep = ~((rows >= V) & (rows < 2 * V) & (j // 2 == 5))
+    assert np.array_equal(gv[idx[keep]], bv[idx[keep]])
+    assert np.all(bv[idx[~keep]] == 0)                # the affected slots are zero-filled
