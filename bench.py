@@ -46,9 +46,10 @@ METRIC = "vnm_spmm_useful_tflops"
 UNIT = "TFLOP/s (useful = 2*M*N*K*n/m)"
 CONFIG = {"workload": "cfg4", "M": CFG4["M"], "K": CFG4["K"], "N": CFG4["N"], "V": CFG4["V"], "n:m": "2:%d" % CFG4["m"],
           "l2": "inputs larger than L2: every step reads 0.8 GB of B and writes 3.2 GB of C (per job)"}
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the headline kernel, from the ncu capture summarised under
-# profiles/ (a smaller case of the same kernel, scaled by the output tiles a full launch processes); None = not captured.
-NCU_TRAFFIC = {"bytes_per_launch": None, "source": None}
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the headline kernel at full size on one GPU, from the
+# one-pass ncu capture summarised under profiles/ (re-capture whenever the kernel or its tile order changes).
+NCU_TRAFFIC = {"bytes_per_launch": 22193078016 + 3277997824,
+               "source": "profiles/spmm_dense_b_pair_kernel_cfg4_launch.md: one-pass ncu capture of a full-size launch (1 GPU, N = 32768)"}
 CPU_SAMPLE_ROWS = 256
 CPU_SAMPLE_DESC = ("first %d of the %d rows of the cfg4 sparse operand (2 vector blocks), full K and N: reference to_dense + restated "
                    "fp32 host GEMM (OpenMP) + elementwise compare; rate on the sample, the whole product is %dx this work"
@@ -568,7 +569,7 @@ def main():
         peaks = measured_peaks()
         per_gpu = value / world
         roofline = {"bound": "tensor", "achieved": per_gpu, "peak": peaks["tflops_sustained"], "unit": "TFLOP/s", "frac": per_gpu / peaks["tflops_sustained"],
-                    "traffic": NCU_TRAFFIC["bytes_per_launch"], "traffic_source": NCU_TRAFFIC["source"], "peak_source": peaks["source"] + " (sustained dense bf16; useful FLOPs of a 2:4 MMA run at most at the dense rate)",
+                    "traffic": NCU_TRAFFIC["bytes_per_launch"] if (world == 1 and full_size) else None, "traffic_source": NCU_TRAFFIC["source"], "peak_source": peaks["source"] + " (sustained dense bf16; useful FLOPs of a 2:4 MMA run at most at the dense rate)",
                     "kernel": kernel_name, "operand_form": form, "grid": kcfg["grid"],
                     "useful_flops_per_launch": flops_step / world, "launch_ms": ms_step,
                     "frac_of_burst_peak": per_gpu / peaks["tflops_burst"],

@@ -203,7 +203,8 @@ int vnm_prepare_as(const void *values, const uint32_t *meta, const uint32_t *col
 int vnm_set_producer_warps(vnm_handle_t handle, int warps);
 /* Dense-B form only: 1 (default) = products with at least one full wave of 512 x 240 tiles and M a multiple of 512 run on
  * pairs of SMs (thread-block clusters of two CTAs, tcgen05 cta_group::2: each CTA loads half of every B stage), 0 = always
- * the single-SM kernel.  An ablation switch; both give identical bits. */
+ * the single-SM kernel, 2 = pairs without the L2 eviction-priority hints that ask the banded operand to stay cached.
+ * Ablation switches; all give identical bits. */
 int vnm_set_pair_mode(vnm_handle_t handle, int mode);
 /* Caps the number of persistent CTAs (one per SM) the product of this handle launches; 0 = all SMs (default).  A caller
  * that runs something else beside the product (the multi-GPU launcher's all-gather, another stream's kernels) keeps SMs

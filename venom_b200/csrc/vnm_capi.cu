@@ -5,6 +5,7 @@
 #include <mutex>
 
 #include <cstdio>
+#include <cstdlib>
 #include <cstdarg>
 #include <cstring>
 #include <new>
@@ -152,6 +153,7 @@ struct vnm_prepared_s {
     int dense_b;       // 1: A re-expressed as 2:4 over all K columns, B read as plain tiles
     int out32;         // ablation: 32-bit epilogue stores (gather form, layout MN)
     int hybrid_rows;   // gather form: rows of every 64-row stage fetched by TMA gather4 beside the per-thread copies
+    int l2_hints;      // pair kernel: 1 = ask L2 to keep the banded operand (default), 0 = no eviction-priority hints
     int pair_mode;     // dense-B form: 1 = use the two-SM (cta_group::2) kernel where it applies (default), 0 = never
     int max_ctas;      // 0 = one persistent CTA per SM, else the cap set by vnm_set_max_ctas
 };
@@ -260,6 +262,7 @@ int vnm_prepare_as(const void *values, const uint32_t *meta, const uint32_t *col
     h->vblocks_padded = h->mtiles * h->nb;
     h->producer_warps = 8;
     h->pair_mode = 1;
+    h->l2_hints = 1;
     h->device = dev_now;
     cudaError_t e = cudaMalloc(&h->am, (size_t)h->mtiles * h->ktiles * AM_BLOCK_BYTES);
     if (e == cudaSuccess) e = cudaMalloc(&h->rows, (size_t)h->vblocks_padded * h->ktiles * KT_GROUPS * sizeof(int4));
@@ -323,8 +326,9 @@ int vnm_set_gather_split(vnm_handle_t h, int tma_rows)
 int vnm_set_pair_mode(vnm_handle_t h, int mode)
 {
     if (!h) return fail(VNM_ERR_BAD_ARG, "null handle");
-    if (mode != 0 && mode != 1) return fail(VNM_ERR_BAD_ARG, "pair mode must be 0 or 1 (got %d)", mode);
-    h->pair_mode = mode;
+    if (mode < 0 || mode > 2) return fail(VNM_ERR_BAD_ARG, "pair mode must be 0, 1 or 2 (got %d)", mode);
+    h->pair_mode = mode != 0;
+    h->l2_hints = mode != 2;
     return VNM_OK;
 }
 
@@ -500,12 +504,27 @@ static int spmm_impl(vnm_handle_t h, const void *B, int64_t ldb, int N, int b_nk
     p.ldb = ldb;
     p.out32 = h->out32;
     {
-        // band height of the tile order (tile_coords): as many row groups as keep their A blocks (18 KiB per row tile and k-tile)
-        // within about 48 MB, so that A and the few B panels in flight stay in L2
+        // Band of the tile order (tile_coords) and, for the pair kernel, which operand is asked to stay in L2.  A band
+        // keeps either `g` row groups of A (18 KiB per row tile and k-tile) or `q` column panels of B (K x tile-N fp16)
+        // within about 32 MB while the other operand streams past; the cheaper of the two in bytes re-read from HBM wins:
+        //   row bands: A once + B once per band;   column bands: B once + A once per band.
         const int64_t rows_per_group = h->dense_b ? (int64_t)cfg.nb * TILE_M : TILE_M;   // dense-B: 256 / 128 (one SM per tile) or 512 (pairs); gather: 128
+        const int64_t row_groups = (h->M + rows_per_group - 1) / rows_per_group;
         const int64_t bytes_per_group = (rows_per_group / TILE_M) * (int64_t)h->ktiles * AM_BLOCK_BYTES;
-        int64_t g = bytes_per_group > 0 ? ((int64_t)48 << 20) / bytes_per_group : 1;
-        p.group_m = (int)(g < 1 ? 1 : (g > 4096 ? 4096 : g));
+        const int64_t bytes_per_panel = (int64_t)h->K * cfg.bn * 2;
+        const int64_t budget = (int64_t)32 << 20;  // measured flat between 28 and 64 MB on B200, worse at 16 and 96
+        int64_t g = bytes_per_group > 0 ? budget / bytes_per_group : 1;
+        g = g < 1 ? 1 : (g > 4096 ? 4096 : g);
+        int64_t q = bytes_per_panel > 0 ? budget / bytes_per_panel : 1;
+        q = q < 1 ? 1 : (q > 4096 ? 4096 : q);
+        const double a_total = (double)row_groups * bytes_per_group, b_total = (double)p.ntiles * bytes_per_panel;
+        const double cost_rows = a_total + b_total * (double)((row_groups + g - 1) / g);
+        const double cost_cols = b_total + a_total * (double)((p.ntiles + q - 1) / q);
+        const bool col_bands = pair && cost_cols < cost_rows;   // the one-SM and gather kernels keep row bands
+        p.group_m = col_bands ? -(int)q : (int)g;
+        p.hint_a = col_bands ? L2_EVICT_NORMAL : L2_EVICT_LAST;
+        p.hint_b = col_bands ? L2_EVICT_LAST : L2_EVICT_NORMAL;
+        if (h->l2_hints == 0) p.hint_a = p.hint_b = L2_EVICT_NORMAL;
     }
     p.hybrid_rows = h->hybrid_rows;
     p.b_nk = b_nk;

@@ -58,18 +58,30 @@ constexpr int AM_BLOCK_BYTES = A_IMG_BYTES + META_IMG_BYTES;  // 18432
 __host__ __device__ inline int mma_row_to_actual(int i) { int w = i & 15; return (i & ~15) + ((w & 7) << 1) + (w >> 3); }
 __host__ __device__ inline int actual_to_mma_row(int a) { int x = a & 15; return (a & ~15) + ((x & 1) << 3) + (x >> 1); }
 
-// Tile order of the persistent dense-B kernels: row groups (units of one CTA tile's rows) are taken `group` at a time
-// and, inside such a band, column tiles advance slowest.  The CTAs that run together then share `group` row groups of
-// A and a few column panels of B, a working set that stays in L2, instead of streaming all of A past every column
-// tile (which re-reads A from HBM once per column tile as soon as A is larger than L2).
+// Tile order of the persistent kernels.  group > 0: row groups (units of one CTA tile's rows) are taken `group` at a
+// time and, inside such a band, column tiles advance slowest: the CTAs that run together share `group` row groups
+// of A, which can stay in L2 while the column panels of B stream past.  group < 0: the transposed order, bands of
+// -group column tiles inside which row groups advance slowest: the band's B panels stay in L2 while A streams past
+// (cheaper whenever A is the smaller operand).  Either way A is no longer re-read from HBM once per column tile, which
+// is what "row groups fastest over the whole matrix" costs as soon as A is larger than L2.
 __host__ __device__ inline void tile_coords(int tile, int row_groups, int ntiles, int group, int *rg, int *nt)
 {
-    const int band = tile / (group * ntiles);
-    const int first = band * group;
-    const int size = row_groups - first < group ? row_groups - first : group;
-    const int within = tile - band * group * ntiles;
-    *nt = within / size;
-    *rg = first + within % size;
+    if (group >= 0) {
+        const int band = tile / (group * ntiles);
+        const int first = band * group;
+        const int size = row_groups - first < group ? row_groups - first : group;
+        const int within = tile - band * group * ntiles;
+        *nt = within / size;
+        *rg = first + within % size;
+    } else {
+        const int g = -group;
+        const int band = tile / (g * row_groups);
+        const int first = band * g;
+        const int size = ntiles - first < g ? ntiles - first : g;
+        const int within = tile - band * g * row_groups;
+        *rg = within / size;
+        *nt = first + within % size;
+    }
 }
 
 #if defined(__CUDACC__)
@@ -124,6 +136,31 @@ __device__ __forceinline__ void bulk_g2s(void *smem_dst, const void *gsrc, uint3
 {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(smem_dst)),
                  "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+// L2 eviction-priority policies for the hinted copies below (the encodings createpolicy.fractional produces for a
+// fraction of 1.0): lines loaded with EVICT_LAST are the last candidates for replacement, EVICT_FIRST the first.
+constexpr uint64_t L2_EVICT_NORMAL = 0x1000000000000000ull;
+constexpr uint64_t L2_EVICT_FIRST = 0x12F0000000000000ull;
+constexpr uint64_t L2_EVICT_LAST = 0x14F0000000000000ull;
+__device__ __forceinline__ void bulk_g2s_hint(void *smem_dst, const void *gsrc, uint32_t bytes, uint64_t *bar, uint64_t policy)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(smem_u32(smem_dst)),
+                 "l"(gsrc), "r"(bytes), "r"(smem_u32(bar)), "l"(policy)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_hint(void *smem_dst, const void *tmap, int col, int row, uint64_t *bar, uint64_t policy)
+{
+    asm volatile("cp.async.bulk.tensor.2d.shared::cta.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3}], [%4], %5;" ::"r"(
+                     smem_u32(smem_dst)),
+                 "l"(tmap), "r"(col), "r"(row), "r"(smem_u32(bar)), "l"(policy)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_load_4d_hint(void *smem_dst, const void *tmap, int c0, int c1, int c2, int c3, uint64_t *bar, uint64_t policy)
+{
+    asm volatile("cp.async.bulk.tensor.4d.shared::cta.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3, %4, %5}], [%6], %7;" ::"r"(
+                     smem_u32(smem_dst)),
+                 "l"(tmap), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(smem_u32(bar)), "l"(policy)
                  : "memory");
 }
 // TMA gather: four rows (r.x..r.w) of a 2-D tensor, `col` = first element of the inner box.

@@ -31,7 +31,8 @@ struct SpmmParams {
     const __half *B;      // gather kernel, GATHER_CPASYNC: the dense operand [K, N] itself (row pieces are copied by address)
     int64_t ldb;
     int hybrid_rows;      // gather kernel, GATHER_CPASYNC: rows per block and stage fetched by TMA gather4 beside the copies (0, 16, 32, 48)
-    int group_m;          // dense-B kernels: row groups per band of the tile order (tile_coords), >= 1
+    int group_m;          // band of the tile order (tile_coords): > 0 row groups per band, < 0 column tiles per band
+    uint64_t hint_a, hint_b;  // pair kernel: L2 eviction-priority policies of the A and B loads (L2_EVICT_*)
     int out32;            // gather kernel, layout MN: 32-bit stores from registers instead of staged 128-bit stores (ablation)
     int b_nk;             // dense-B kernel only: the dense operand is given as [N, K] row-major (K contiguous)
     int b_wide_ok;        // dense-B kernel only: the 4-D tensor map exists (column tiles with 256 columns inside N use one box per stage)

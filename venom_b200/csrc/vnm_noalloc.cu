@@ -143,6 +143,7 @@ extern "C" int vnm_spmm_f16_noalloc(const void *values, const uint32_t *meta, co
     p.B = (const __half *)B;
     p.ldb = ldb;
     p.out32 = 0;
+    p.hint_a = p.hint_b = L2_EVICT_NORMAL;
     p.group_m = mtiles;  // operands this small fit in L2 whole: row tiles fastest
     p.hybrid_rows = 0;
     p.b_nk = 0;

@@ -232,8 +232,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_pair_kernel(const
                     for (int rt = 0; rt < R; rt++) {
                         // a row tile past the end of the matrix re-reads the last one; its rows are never stored
                         const int mt = row_tile(mq, rt) < p.mtiles ? row_tile(mq, rt) : p.mtiles - 1;
-                        bulk_g2s(a_ring + s * A_STAGE_BYTES + rt * AM_BLOCK_BYTES, p.am + ((size_t)mt * p.ktiles + kt) * AM_BLOCK_BYTES, AM_BLOCK_BYTES,
-                                 &a_full[s]);
+                        bulk_g2s_hint(a_ring + s * A_STAGE_BYTES + rt * AM_BLOCK_BYTES, p.am + ((size_t)mt * p.ktiles + kt) * AM_BLOCK_BYTES, AM_BLOCK_BYTES,
+                                      &a_full[s], p.hint_a);
                     }
                 }
             }
@@ -272,11 +272,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_pair_kernel(const
                 // 64 rows x 128 columns come along per stage; the MMAs read the first 120 columns
                 mbar_arrive_expect_tx(&b_full[s], B_STAGE_BYTES);
                 if (p.b_nk) {
-                    tma_load_2d(dst, &tmap_tile, jl * 64, n0, &b_full[s]);  // 128 rows (n) x 64 k, 128-byte swizzle
+                    tma_load_2d_hint(dst, &tmap_tile, jl * 64, n0, &b_full[s], p.hint_b);  // 128 rows (n) x 64 k, 128-byte swizzle
                 } else if (p.b_wide_ok && n0 + 128 <= p.N) {
-                    tma_load_4d(dst, &tmap_tile, 0, jl * 64, 0, n0 / 8, &b_full[s]);  // {64 columns, 64 rows, 2 slices} from column n0
+                    tma_load_4d_hint(dst, &tmap_tile, 0, jl * 64, 0, n0 / 8, &b_full[s], p.hint_b);  // {64 columns, 64 rows, 2 slices} from column n0
                 } else {  // ragged right edge: two boxes that clip (and zero-fill) at N
-                    for (int c = 0; c < 2; c++) tma_load_2d(dst + c * B_CHUNK_BYTES, &tmap_tile2, n0 + c * 64, jl * 64, &b_full[s]);
+                    for (int c = 0; c < 2; c++) tma_load_2d_hint(dst + c * B_CHUNK_BYTES, &tmap_tile2, n0 + c * 64, jl * 64, &b_full[s], p.hint_b);
                 }
                 jl += NBP;
                 while (jl >= per_tile) { jl -= per_tile; ++tile_i; }
