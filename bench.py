@@ -465,7 +465,7 @@ def main():
     value = flops_step / (ms_step * 1e-3) / 1e12
     form = "dense-B" if prep.dense_b_form() else "gather"
     kcfg = prep.config(ns)
-    kernel_name = ("vnm::spmm_dense_b_pair_kernel (clusters of two CTAs, tcgen05 cta_group::2)" if kcfg["tile_m"] == 512 else
+    kernel_name = ("vnm::spmm_dense_b_pair_kernel (clusters of two CTAs, tcgen05 cta_group::2)" if (form == "dense-B" and kcfg["stages"] == 2) else
                    "vnm::spmm_dense_b_kernel" if form == "dense-B" else "vnm::spmm_kernel")
 
     if args.kernel_only:

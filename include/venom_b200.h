@@ -214,7 +214,8 @@ int vnm_set_max_ctas(vnm_handle_t handle, int max_ctas);
 /* Shape and settings of a prepared operand (any output pointer may be NULL). */
 int vnm_handle_info(vnm_handle_t handle, int *M, int *K, int *V, int *m, int *max_ctas);
 
-/* Kernel configuration that vnm_spmm_f16 would launch for this handle and N (for reporting). */
+/* Kernel configuration that vnm_spmm_f16 would launch for this handle and N (for reporting).  `stages`: for the dense-B
+ * form 2 = the kernel on pairs of SMs, 1 = the one-SM kernel; for the gather form the number of producer warps. */
 int vnm_spmm_config(vnm_handle_t handle, int N, int *tile_m, int *tile_n, int *stages, int *grid, int *smem_bytes);
 
 /* ---------------------------------------------------------------------------------------------------------

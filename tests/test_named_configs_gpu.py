@@ -133,7 +133,9 @@ def test_gpt3_layer_shapes_one_sequence_shard(capi, oracle, mk):
     _check_column_sums(dense, B, outT, 1, bias=bias)
 
 
-PAIR_CASES = [(1024, 1024, 64, 8, 17000), (2048, 512, 128, 4, 9000), (512, 4096, 32, 16, 18000), (4096, 1024, 128, 8, 4808)]
+PAIR_CASES = [(1024, 1024, 64, 8, 17000), (2048, 512, 128, 4, 9000), (512, 4096, 32, 16, 18000), (4096, 1024, 128, 8, 4808),
+              (1024, 4096, 64, 8, 4096),      # the single-SpMM configuration: 256-row pair tiles (one row tile per CTA)
+              (768, 1024, 128, 8, 8200)]      # six row tiles: 256-row pair tiles, ragged N
 
 
 @pytest.mark.parametrize("shape", PAIR_CASES, ids=lambda p: "%dx%d_V%d_2:%d_N%d" % p)
@@ -146,14 +148,14 @@ def test_two_sm_kernel_matches_single_sm_kernel_and_oracle(capi, oracle, shape):
     dense, colloc, values, meta, B = _operands(capi, M, K, V, m, N, seed=M + 2 * K + N)
     prep = capi.Prepared(values, meta, colloc, M, K, V, m, strategy=capi.STRATEGY_DENSE_B)
     assert prep.dense_b_form()
-    assert prep.config(N)["tile_m"] == 512, "the pair kernel was expected to be chosen for this shape"
+    assert prep.config(N)["stages"] == 2, "the pair kernel was expected to be chosen for this shape"   # stages: 2 = SM pairs
     bias = (torch.rand(M, device="cuda") - 0.5).half()
     bt = B.t().contiguous()
     pair = [prep.spmm(B), prep.spmm(B, bias=bias, layout=capi.VNM_LAYOUT_NM), prep.spmm_nk(bt, bias=bias, layout=capi.VNM_LAYOUT_NM),
             prep.spmm_nk(bt, layout=capi.VNM_LAYOUT_MN)]
     assert prep.device_status() == 0
     prep.set_pair_mode(0)
-    assert prep.config(N)["tile_m"] in (128, 256)
+    assert prep.config(N)["stages"] == 1
     single = [prep.spmm(B), prep.spmm(B, bias=bias, layout=capi.VNM_LAYOUT_NM), prep.spmm_nk(bt, bias=bias, layout=capi.VNM_LAYOUT_NM),
               prep.spmm_nk(bt, layout=capi.VNM_LAYOUT_MN)]
     assert prep.device_status() == 0

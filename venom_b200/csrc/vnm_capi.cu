@@ -376,7 +376,7 @@ int vnm_spmm_config(vnm_handle_t h, int N, int *tile_m, int *tile_n, int *stages
     if (pair) { /* cfg filled */ }
     else if (h->dense_b) spmm_dense_b_config(h->M, N, h->max_ctas, &cfg);
     else if (!spmm_select_config(h->V, N, h->M, h->producer_warps, h->max_ctas, &cfg)) return fail(VNM_ERR_UNSUPPORTED, "unsupported V");
-    if (tile_m) *tile_m = pair ? 4 * TILE_M : h->dense_b ? cfg.nb * TILE_M : TILE_M;
+    if (tile_m) *tile_m = h->dense_b ? cfg.nb * TILE_M : TILE_M;  // pairs: 512 or 256, one SM per tile: 256 or 128
     if (tile_n) *tile_n = cfg.bn;
     if (stages) *stages = cfg.stages;
     if (grid) *grid = cfg.grid;

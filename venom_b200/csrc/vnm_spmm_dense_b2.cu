@@ -160,10 +160,11 @@ __device__ __forceinline__ bool wait_warp(uint64_t *bar, uint32_t parity, volati
 //               peer: forwards "B half landed" to the leader.
 //   warps 4..6  B producers: one 16 KiB TMA box per stage (64 rows of this CTA's 128-column half).
 //   warps 8..15 epilogue of this CTA's two accumulators.
+template <int R>
 __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_pair_kernel(const __grid_constant__ CUtensorMap tmap_tile, const __grid_constant__ CUtensorMap tmap_tile2,
                                                                            const __grid_constant__ CUtensorMap tmap_out, const SpmmParams p)
 {
-    constexpr int R = RT;
+    static_assert(R == 1 || R == RT, "row tiles per CTA");  // R = 1: pair tiles of 256 x 240 for problems with few row tiles
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t *a_ring = smem;
@@ -401,7 +402,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_pair_kernel(const
         const int arow = mma_row_to_actual(i);
         const uint32_t empty_leader = mapa_shared(smem_u32(acc_empty_bar), 0);
         int ti = 0;
-        for (int tile = pair; tile < total_tiles; tile += npairs, ++ti) {
+        // with one row tile per CTA the second group of four warps has no accumulator to drain
+        for (int tile = ((warp - EPI_WARP0) >> 2) < R ? pair : total_tiles; tile < total_tiles; tile += npairs, ++ti) {
             int mq, nt;
             tile_coords(tile, mquads, p.ntiles, p.group_m, &mq, &nt);
             const int n0 = nt * BN;
@@ -500,8 +502,9 @@ int g_pair_clusters = 0;  // co-resident clusters of two CTAs on this device (0 
 
 cudaError_t spmm_dense_b_pair_init()
 {
-    cudaError_t e = cudaFuncSetAttribute(spmm_dense_b_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(spmm_dense_b_pair_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     if (e != cudaSuccess) return e;
+    if ((e = cudaFuncSetAttribute(spmm_dense_b_pair_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES)) != cudaSuccess) return e;
     int dev = 0, sms = 0;
     if ((e = cudaGetDevice(&dev)) != cudaSuccess) return e;
     if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return e;
@@ -517,27 +520,32 @@ cudaError_t spmm_dense_b_pair_init()
     lc.attrs = attr;
     lc.numAttrs = 1;
     int clusters = 0;
-    e = cudaOccupancyMaxActiveClusters(&clusters, spmm_dense_b_pair_kernel, &lc);
+    e = cudaOccupancyMaxActiveClusters(&clusters, spmm_dense_b_pair_kernel<2>, &lc);
     if (e != cudaSuccess) { (void)cudaGetLastError(); clusters = 0; }
     g_pair_clusters = clusters;
     return cudaSuccess;
 }
 
-// Pair tiles are 512 rows x 240 columns.  Returns false when the pair kernel should not be used for this problem
-// (too few pair tiles to occupy the clusters, or clusters unavailable): the caller then launches the single-CTA kernel.
+// Pair tiles are 512 x 240 (two row tiles per CTA) or, where that would leave SM pairs without a tile, 256 x 240 (one
+// row tile per CTA: 34 KiB per CTA and k-tile).  Returns false when the pair kernel should not be used for this problem
+// (row tiles do not group evenly, too few tiles to occupy the clusters, or clusters unavailable): the caller then
+// launches the single-CTA kernel.
 bool spmm_dense_b_pair_config(int M, int N, int max_ctas, SpmmConfig *cfg)
 {
     if (g_pair_clusters <= 0) return false;
     const int mtiles = (M + TILE_M - 1) / TILE_M;
     const long long ntiles = (N + BN - 1) / BN;
-    const long long tiles = (long long)((mtiles + 2 * RT - 1) / (2 * RT)) * ntiles;
     int clusters = g_pair_clusters;
     if (max_ctas > 0 && max_ctas / 2 < clusters) clusters = max_ctas / 2;
     if (clusters < 1) return false;
-    // worth it only with at least one full wave of pair tiles and whole groups of four row tiles
-    if (mtiles % (2 * RT) != 0 || tiles < clusters) return false;
+    const long long t2 = (long long)(mtiles / (2 * RT)) * ntiles, t1 = (long long)(mtiles / 2) * ntiles;
+    int rt = 0;
+    if (mtiles % (2 * RT) == 0 && t2 >= clusters) rt = RT;          // at least one full wave of 512-row tiles
+    else if (mtiles % 2 == 0 && 4 * t1 >= 3 * clusters) rt = 1;      // most SM pairs get a 256-row tile
+    if (rt == 0) return false;
+    const long long tiles = rt == RT ? t2 : t1;
     cfg->bn = BN;
-    cfg->nb = 2 * RT;
+    cfg->nb = 2 * rt;  // row tiles per pair tile
     cfg->stages = 2;
     cfg->smem_bytes = SMEM_BYTES;
     cfg->threads = NUM_THREADS;
@@ -560,7 +568,8 @@ cudaError_t launch_spmm_dense_b_pair(const SpmmConfig &cfg, const CUtensorMap &t
     attr[0].val.clusterDim.z = 1;
     lc.attrs = attr;
     lc.numAttrs = 1;
-    return cudaLaunchKernelEx(&lc, spmm_dense_b_pair_kernel, tmap_tile, tmap_tile2, tmap_out, p);
+    if (cfg.nb == 2) return cudaLaunchKernelEx(&lc, spmm_dense_b_pair_kernel<1>, tmap_tile, tmap_tile2, tmap_out, p);
+    return cudaLaunchKernelEx(&lc, spmm_dense_b_pair_kernel<2>, tmap_tile, tmap_tile2, tmap_out, p);
 }
 
 }  // namespace vnm
