@@ -490,17 +490,36 @@ def main():
             rec[name] = float(tt.item())
             barrier()
         # every rank's rows must have arrived everywhere: compare the copy on this rank with each owner's checksum
-        sums = full.float().sum(dim=1).reshape(world, ns).sum(dim=1).double()
-        ref = sums.clone()
-        dist.broadcast(ref, src=0)
-        if not torch.allclose(sums, ref, rtol=0, atol=0):
-            raise SystemExit("bench.py: the gathered result differs between ranks")
+        def check_replicas(what):
+            sums = full.float().sum(dim=1).reshape(world, ns).sum(dim=1).double()
+            ref = sums.clone()
+            dist.broadcast(ref, src=0)
+            if not torch.allclose(sums, ref, rtol=0, atol=0) or not bool((sums != 0).all()):
+                raise SystemExit("bench.py: the gathered result (%s) differs between ranks" % what)
+        check_replicas("NCCL exchange")
+        # peer-store form: one launch whose epilogue stores every tile to all ranks' buffers (registered through CUDA IPC)
+        try:
+            full.zero_()
+            sh.gathered_p2p(B, N, full)
+            barrier()
+            t_ms = time_events(lambda: sh.gathered_p2p(B, N, full), max(3, args.steps // 4), torch)
+            tt = torch.tensor([t_ms], device=dev, dtype=torch.float64)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            rec["peer_store_ms"] = float(tt.item())
+            barrier()
+            check_replicas("peer stores")
+            sh.release_outputs()
+        except capi.VenomError as exc:   # the same verdict on every rank: registration is agreed collectively
+            rec["peer_store_unavailable"] = str(exc)
         bytes_in = (world - 1) * ns * M * 2
         exposed_plain = max(rec["plain_ms"] - ms_step, 1e-6)
         rec.update({"chunks": 4, "spmm_only_ms": ms_step, "bytes_received_per_rank": bytes_in,
                     "allgather_gbs_per_rank_in": bytes_in / (exposed_plain * 1e-3) / 1e9,
-                    "exposed_ms": {"plain": rec["plain_ms"] - ms_step, "overlapped": rec["overlapped_ms"] - ms_step},
-                    "collective": "plain: one in-place ncclAllGather after the product; overlapped: grouped ncclSend/ncclRecv per chunk on a second stream"})
+                    "exposed_ms": dict({"plain": rec["plain_ms"] - ms_step, "overlapped": rec["overlapped_ms"] - ms_step},
+                                       **({"peer_store": rec["peer_store_ms"] - ms_step} if "peer_store_ms" in rec else {})),
+                    "collective": "plain: one in-place ncclAllGather after the product; overlapped: grouped ncclSend/ncclRecv per chunk on a second "
+                                  "stream; peer_store: no collective, the product's epilogue stores every tile to all ranks' buffers over NVLink "
+                                  "(two 4-byte all-gathers order the ranks)"})
         gathered = rec
         del full
         torch.cuda.empty_cache()

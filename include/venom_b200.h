@@ -104,6 +104,14 @@ int vnm_destroy(vnm_handle_t handle);
 int vnm_spmm_f16(vnm_handle_t handle, const void *B, int64_t ldb, int N,
                  const void *bias, void *out, int64_t ldo, int layout, void *stream);
 
+/* The same product stored to n_outs buffers of one geometry (1 <= n_outs <= VNM_MAX_OUTS; same ldo, layout and
+ * alignment rules as `out` above): every output tile leaves shared memory through one TMA store per destination, so
+ * the operands are read and multiplied once.  The destinations may be peer-mapped buffers of other GPUs -- this is the
+ * store side of vnm_mgpu_spmm_gathered_p2p.  Only for operands held in dense-B form (VNM_ERR_UNSUPPORTED otherwise). */
+#define VNM_MAX_OUTS 8
+int vnm_spmm_f16_multi(vnm_handle_t handle, const void *B, int64_t ldb, int N, const void *bias,
+                       void *const *outs, int n_outs, int64_t ldo, int layout, void *stream);
+
 /* Same product with the dense operand given as Bt = B^T, i.e. [N, K] row-major with leading dimension ldbt
  * (the activation in its natural [tokens, features] layout), so the caller does not have to materialise the
  * transpose the reference's scripts make before every call (end2end/bert_pytorch.py:85-87,133).
@@ -203,8 +211,10 @@ int vnm_prepare_as(const void *values, const uint32_t *meta, const uint32_t *col
 int vnm_set_producer_warps(vnm_handle_t handle, int warps);
 /* Dense-B form only: 1 (default) = products with at least one full wave of 512 x 240 tiles and M a multiple of 512 run on
  * pairs of SMs (thread-block clusters of two CTAs, tcgen05 cta_group::2: each CTA loads half of every B stage), 0 = always
- * the single-SM kernel, 2 = pairs without the L2 eviction-priority hints that ask the banded operand to stay cached.
- * Ablation switches; all give identical bits. */
+ * the single-SM kernel, 2 = pairs without the L2 eviction-priority hints that ask the banded operand to stay cached,
+ * 3 / 4 = pairs with one / two row tiles per CTA forced where the shape allows (default: two wherever 512-row tiles
+ * fill the SM pairs, else one, whose two accumulators alternate between consecutive tiles).  Ablation switches; all
+ * give identical bits. */
 int vnm_set_pair_mode(vnm_handle_t handle, int mode);
 /* Caps the number of persistent CTAs (one per SM) the product of this handle launches; 0 = all SMs (default).  A caller
  * that runs something else beside the product (the multi-GPU launcher's all-gather, another stream's kernels) keeps SMs
@@ -258,6 +268,21 @@ int vnm_mgpu_spmm_shard(vnm_mgpu_t ctx, vnm_handle_t handle, const void *B_shard
  * chunk has arrived.  N_total must be a multiple of 8 x world. */
 int vnm_mgpu_spmm_gathered(vnm_mgpu_t ctx, vnm_handle_t handle, const void *B_shard, int64_t ldb, int N_total,
                            const void *bias, void *out_full, int64_t ldo, int chunks, void *stream);
+
+/* Peer-store form of the gathered product: no exchange step at all.  Every rank registers its [N_total, M] result
+ * buffer once (collective: CUDA IPC handles of the allocation travel over the communicator and every peer's buffer is
+ * mapped into this process; the buffer must come from cudaMalloc, e.g. a PyTorch tensor of the default allocator, and
+ * all ranks must be processes on one node with peer access).  vnm_mgpu_spmm_gathered_p2p then runs ONE product launch
+ * whose epilogue stores every output tile of this rank's rows to the same rows of all `world` buffers (its own first,
+ * the peers' over NVLink), so the transfer of a tile overlaps the MMAs of the next ones; a small ncclAllGather on
+ * `stream` before the launch (nobody still reads last call's result) and after it (every rank's rows have landed)
+ * orders the ranks.  Needs the operand in dense-B form, world <= VNM_MAX_OUTS, ldo == M, N_total % (8 x world) == 0;
+ * VNM_ERR_UNSUPPORTED otherwise, and callers fall back to vnm_mgpu_spmm_gathered.  unregister is collective too
+ * (it synchronises the device and the ranks before it unmaps). */
+int vnm_mgpu_register_output(vnm_mgpu_t ctx, void *out_full, size_t bytes);
+int vnm_mgpu_unregister_output(vnm_mgpu_t ctx, void *out_full);
+int vnm_mgpu_spmm_gathered_p2p(vnm_mgpu_t ctx, vnm_handle_t handle, const void *B_shard, int64_t ldb, int N_total,
+                               const void *bias, void *out_full, int64_t ldo, void *stream);
 
 #ifdef __cplusplus
 }

@@ -51,3 +51,28 @@ def test_cpu_tensors_are_rejected():
     from venom_b200 import capi
     with pytest.raises(capi.VenomError, match="no CPU path"):
         capi.compress(torch.zeros(64, 64, dtype=torch.float16), torch.zeros(64, dtype=torch.int32), 32, 8)
+
+
+def test_handle_setters_and_launcher_entry_points_reject_bad_arguments_without_a_gpu(lib):
+    """Every switch and every vnm_mgpu_* entry point checks its arguments before touching CUDA or NCCL."""
+    import ctypes as C
+    for name in ("vnm_set_gather_mode", "vnm_set_gather_split", "vnm_set_pair_mode", "vnm_set_epilogue", "vnm_set_max_ctas",
+                 "vnm_set_producer_warps"):
+        fn = getattr(lib, name)
+        fn.argtypes = [C.c_void_p, C.c_int]
+        fn.restype = C.c_int
+        assert fn(None, 0) == 1 and b"null handle" in lib.vnm_last_error_string(), name
+    lo, hi = C.c_int(), C.c_int()
+    assert lib.vnm_mgpu_shard(64, 2, 1, 8, C.byref(lo), C.byref(hi)) == 0 and (lo.value, hi.value) == (32, 64)
+    assert lib.vnm_mgpu_shard(60, 2, 1, 8, C.byref(lo), C.byref(hi)) == 1
+    ctx = C.c_void_p()
+    assert lib.vnm_mgpu_create(None, 2, 0, C.byref(ctx)) == 1
+    assert lib.vnm_mgpu_create_from_comm(None, C.byref(ctx)) == 1
+    assert lib.vnm_mgpu_unique_id(None) == 1
+    assert lib.vnm_mgpu_destroy(None) == 0
+    assert lib.vnm_mgpu_spmm_gathered(None, None, None, 0, 64, None, None, 0, 4, None) == 1
+    assert lib.vnm_mgpu_broadcast_operand(None, None, None, None, 64, 64, 32, 2, 8, 0, None) == 1
+    assert lib.vnm_mgpu_register_output(None, None, 0) == 1
+    assert lib.vnm_mgpu_unregister_output(None, None) == 1
+    assert lib.vnm_mgpu_spmm_gathered_p2p(None, None, None, 0, 64, None, None, 0, None) == 1
+    assert lib.vnm_spmm_f16_multi(None, None, 0, 64, None, None, 0, 0, 0, None) == 1

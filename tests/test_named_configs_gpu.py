@@ -154,6 +154,13 @@ def test_two_sm_kernel_matches_single_sm_kernel_and_oracle(capi, oracle, shape):
     pair = [prep.spmm(B), prep.spmm(B, bias=bias, layout=capi.VNM_LAYOUT_NM), prep.spmm_nk(bt, bias=bias, layout=capi.VNM_LAYOUT_NM),
             prep.spmm_nk(bt, layout=capi.VNM_LAYOUT_MN)]
     assert prep.device_status() == 0
+    # one and two row tiles per CTA (256- and 512-row pair tiles; the first alternates two accumulators between tiles)
+    for mode, tile_m in ((3, 256), (4, 512)):
+        prep.set_pair_mode(mode)
+        if prep.config(N)["stages"] == 2 and prep.config(N)["tile_m"] == tile_m:
+            assert torch.equal(prep.spmm(B, bias=bias, layout=capi.VNM_LAYOUT_NM), pair[1])
+            assert torch.equal(prep.spmm_nk(bt, layout=capi.VNM_LAYOUT_MN), pair[3])
+            assert prep.device_status() == 0
     prep.set_pair_mode(0)
     assert prep.config(N)["stages"] == 1
     single = [prep.spmm(B), prep.spmm(B, bias=bias, layout=capi.VNM_LAYOUT_NM), prep.spmm_nk(bt, bias=bias, layout=capi.VNM_LAYOUT_NM),
@@ -164,3 +171,34 @@ def test_two_sm_kernel_matches_single_sm_kernel_and_oracle(capi, oracle, shape):
     _check_rows(oracle, pair[0], 0, values, meta, colloc, M, K, V, m, B)
     _check_rows(oracle, pair[1], 1, values, meta, colloc, M, K, V, m, B, bias=bias)
     _check_column_sums(dense, B, pair[0], 0)
+
+
+@pytest.mark.parametrize("shape", [(1024, 1024, 64, 8, 17000), (768, 1024, 128, 8, 8200), (384, 512, 128, 4, 1000)],
+                         ids=lambda p: "%dx%d_V%d_2:%d_N%d" % p)
+def test_product_stored_to_several_destinations(capi, shape):
+    """vnm_spmm_f16_multi: every output tile is stored to each destination (the store side of the peer-store gathered
+    product, here with all destinations on one GPU).  Both dense-B kernels, both layouts; every copy must carry the bits
+    of the single-destination product, and memory outside the destinations' rows must stay untouched."""
+    import torch
+    M, K, V, m, N = shape
+    dense, colloc, values, meta, B = _operands(capi, M, K, V, m, N, seed=5 * M + K + N)
+    prep = capi.Prepared(values, meta, colloc, M, K, V, m, strategy=capi.STRATEGY_DENSE_B)
+    bias = (torch.rand(M, device="cuda") - 0.5).half()
+    for pair_mode in (1, 0):
+        prep.set_pair_mode(pair_mode)
+        for layout, b in ((capi.VNM_LAYOUT_MN, None), (capi.VNM_LAYOUT_NM, bias)):
+            want = prep.spmm(B, bias=b, layout=layout)
+            rows = want.shape[0]
+            # destinations are row blocks of larger buffers, as a rank's rows are inside the gathered result
+            bufs = [torch.full((rows + 16, want.shape[1]), 7.0, dtype=torch.float16, device="cuda") for _ in range(3)]
+            outs = [buf[8:8 + rows] for buf in bufs]
+            prep.spmm_multi(B, outs, bias=b, layout=layout)
+            assert prep.device_status() == 0
+            for buf, o in zip(bufs, outs):
+                assert torch.equal(o, want)
+                assert bool((buf[:8] == 7.0).all()) and bool((buf[8 + rows:] == 7.0).all())
+    with pytest.raises(capi.VenomError):
+        prep.spmm_multi(B, [torch.empty_like(want)] * 9, layout=capi.VNM_LAYOUT_NM)
+    gather = capi.Prepared(values, meta, colloc, M, K, V, m, strategy=capi.STRATEGY_GATHER)
+    with pytest.raises(capi.VenomError):
+        gather.spmm_multi(B, [torch.empty((M, N), dtype=torch.float16, device="cuda")] * 2)

@@ -49,10 +49,28 @@ def _worker(rank, world, port, q):
             bad, _, w = orc.check(full.cpu().numpy(), want, mode=1, tol=1e-2)
             bad_total += bad
             worst = max(worst, w)
+        # peer-store form: the epilogue writes this rank's rows into both ranks' registered buffers; no exchange step.
+        # Same kernel and operands as the NCCL forms, so the bits must agree.  Two calls: the second overwrites the first.
+        p2p = "ok"
+        shared = torch.zeros((N, M), dtype=torch.float16, device="cuda")
+        try:
+            for _ in range(2):
+                got = op.gathered_p2p(Bs, N, shared)
+                torch.cuda.synchronize()
+                bad, _, w = orc.check(got.cpu().numpy(), want, mode=1, tol=1e-2)
+                bad_total += bad
+                worst = max(worst, w)
+                if not torch.equal(got, full):
+                    bad_total += 1
+            op.release_outputs()
+        except Exception as exc:   # CUDA IPC between the ranks' processes is the one thing a box may not allow
+            if "could not be shared" not in str(exc):
+                raise
+            p2p = str(exc)
         local = op.ctx.spmm_shard(op.prepared, Bs)     # [M, n_shard], no communication
         bad, _, w = orc.check(local.cpu().numpy(), np.ascontiguousarray(want[lo:hi].T), mode=1, tol=1e-2)
         assert op.prepared.device_status() == 0
-        q.put((rank, bad_total + bad, max(worst, w)))
+        q.put((rank, bad_total + bad, max(worst, w), p2p))
     finally:
         dist.destroy_process_group()
 
@@ -72,4 +90,6 @@ def test_two_rank_nccl_sharded_spmm():
     for p in procs:
         p.join(timeout=60)
         assert p.exitcode == 0
-    assert all(bad == 0 for _, bad, _ in res), res
+    assert all(r[1] == 0 for r in res), res
+    if any(r[3] != "ok" for r in res):
+        pytest.skip("NCCL forms pass; peer-store form not available on this box: %s" % [r[3] for r in res])

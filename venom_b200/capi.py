@@ -87,8 +87,15 @@ def lib():
                                           C.c_int, C.c_void_p]
         L.vnm_mgpu_spmm_gathered.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_void_p, C.c_void_p, C.c_int64,
                                              C.c_int, C.c_void_p]
+        L.vnm_mgpu_register_output.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t]
+        L.vnm_mgpu_unregister_output.argtypes = [C.c_void_p, C.c_void_p]
+        L.vnm_mgpu_spmm_gathered_p2p.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]
+        L.vnm_spmm_f16_multi.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_void_p, C.POINTER(C.c_void_p), C.c_int, C.c_int64, C.c_int,
+                                         C.c_void_p]
+        L.vnm_spmm_f16_multi.restype = C.c_int
         for name in ("vnm_mgpu_shard", "vnm_mgpu_unique_id", "vnm_mgpu_create", "vnm_mgpu_create_from_comm", "vnm_mgpu_destroy",
-                     "vnm_mgpu_info", "vnm_mgpu_set_comm_sms", "vnm_mgpu_broadcast_operand", "vnm_mgpu_spmm_shard", "vnm_mgpu_spmm_gathered"):
+                     "vnm_mgpu_info", "vnm_mgpu_set_comm_sms", "vnm_mgpu_broadcast_operand", "vnm_mgpu_spmm_shard", "vnm_mgpu_spmm_gathered",
+                     "vnm_mgpu_register_output", "vnm_mgpu_unregister_output", "vnm_mgpu_spmm_gathered_p2p"):
             getattr(L, name).restype = C.c_int
         for name in ("vnm_sizes", "vnm_compress_f16", "vnm_decompress_f16", "vnm_prepare", "vnm_prepared_bytes",
                      "vnm_destroy", "vnm_spmm_f16", "vnm_spmm_f16_host", "vnm_device_status", "vnm_spmm_config"):
@@ -234,6 +241,21 @@ class Prepared:
                                      out.data_ptr(), out.stride(0), layout, _stream()))
         return out
 
+    def spmm_multi(self, B, outs, bias=None, layout=VNM_LAYOUT_MN):
+        """One product stored to every tensor of `outs` (1 .. 8 tensors of one shape and stride; dense-B form only)."""
+        _need_cuda(B, bias, *outs)
+        if B.dtype != torch.float16 or B.dim() != 2 or B.shape[0] != self.K or B.stride(1) != 1:
+            raise VenomError("B must be a [K,N] fp16 tensor with unit inner stride (K=%d)" % self.K)
+        N = B.shape[1]
+        shape = (self.M, N) if layout == VNM_LAYOUT_MN else (N, self.M)
+        for o in outs:
+            if o.dtype != torch.float16 or tuple(o.shape) != shape or o.stride() != outs[0].stride() or o.stride(1) != 1:
+                raise VenomError("every destination must be a %s fp16 tensor with the same strides" % (shape,))
+        ptrs = (C.c_void_p * len(outs))(*[o.data_ptr() for o in outs])
+        _check(lib().vnm_spmm_f16_multi(self._h, B.data_ptr(), B.stride(0), N, None if bias is None else bias.data_ptr(), ptrs, len(outs),
+                                        outs[0].stride(0), layout, _stream()))
+        return outs
+
     def spmm_host(self, B_host, out_host, bias_host=None, layout=VNM_LAYOUT_MN):
         """End-to-end call with HOST tensors (ideally pinned): H2D, kernel, D2H, synchronise."""
         N = B_host.shape[1]
@@ -275,7 +297,8 @@ class Prepared:
         _check(lib().vnm_set_gather_split(self._h, tma_rows))
 
     def set_pair_mode(self, mode):
-        """Dense-B form: 1 = two-SM (cta_group::2) kernel where it applies (default), 0 = single-SM kernel only."""
+        """Dense-B form: 1 = two-SM (cta_group::2) kernel where it applies (default), 0 = single-SM kernel only,
+        2 = pairs without L2 hints, 3 / 4 = pairs with one / two row tiles per CTA forced where the shape allows."""
         _check(lib().vnm_set_pair_mode(self._h, mode))
 
     def set_epilogue(self, mode):
@@ -371,4 +394,26 @@ class Mgpu:
             out = torch.empty((N_total, prep.M), dtype=torch.float16, device=B_shard.device)
         _check(lib().vnm_mgpu_spmm_gathered(self._c, prep._h, B_shard.data_ptr(), B_shard.stride(0), N_total,
                                             None if bias is None else bias.data_ptr(), out.data_ptr(), out.stride(0), chunks, _stream()))
+        return out
+
+    def register_output(self, out_full):
+        """Collective: maps every rank's [N_total, M] result buffer into every other rank (CUDA IPC), for spmm_gathered_p2p."""
+        _need_cuda(out_full)
+        if not out_full.is_contiguous():
+            raise VenomError("the gathered result buffer must be contiguous")
+        _check(lib().vnm_mgpu_register_output(self._c, out_full.data_ptr(), out_full.numel() * out_full.element_size()))
+        return out_full
+
+    def unregister_output(self, out_full):
+        """Collective: waits for this device and all ranks, then unmaps the peers' buffers."""
+        _check(lib().vnm_mgpu_unregister_output(self._c, out_full.data_ptr()))
+
+    def spmm_gathered_p2p(self, prep, B_shard, N_total, out, bias=None):
+        """Every rank ends with the full [N_total, M] result in its registered `out`: one product launch whose epilogue
+        stores each tile of this rank's rows to all ranks' buffers (own first, peers over NVLink); no exchange step."""
+        _need_cuda(B_shard, bias, out)
+        if B_shard.dtype != torch.float16 or B_shard.dim() != 2 or B_shard.stride(1) != 1 or B_shard.shape[1] * self.world != N_total:
+            raise VenomError("B shard must be [K, N_total / world] fp16 with unit inner stride")
+        _check(lib().vnm_mgpu_spmm_gathered_p2p(self._c, prep._h, B_shard.data_ptr(), B_shard.stride(0), N_total,
+                                                None if bias is None else bias.data_ptr(), out.data_ptr(), out.stride(0), _stream()))
         return out

@@ -153,6 +153,7 @@ struct vnm_prepared_s {
     int dense_b;       // 1: A re-expressed as 2:4 over all K columns, B read as plain tiles
     int out32;         // ablation: 32-bit epilogue stores (gather form, layout MN)
     int hybrid_rows;   // gather form: rows of every 64-row stage fetched by TMA gather4 beside the per-thread copies
+    int pair_rows;     // pair kernel: 0 = row tiles per CTA chosen per problem, 1 / 2 = forced where possible (ablation)
     int l2_hints;      // pair kernel: 1 = ask L2 to keep the banded operand (default), 0 = no eviction-priority hints
     int pair_mode;     // dense-B form: 1 = use the two-SM (cta_group::2) kernel where it applies (default), 0 = never
     int max_ctas;      // 0 = one persistent CTA per SM, else the cap set by vnm_set_max_ctas
@@ -326,9 +327,10 @@ int vnm_set_gather_split(vnm_handle_t h, int tma_rows)
 int vnm_set_pair_mode(vnm_handle_t h, int mode)
 {
     if (!h) return fail(VNM_ERR_BAD_ARG, "null handle");
-    if (mode < 0 || mode > 2) return fail(VNM_ERR_BAD_ARG, "pair mode must be 0, 1 or 2 (got %d)", mode);
+    if (mode < 0 || mode > 4) return fail(VNM_ERR_BAD_ARG, "pair mode must be 0 .. 4 (got %d)", mode);
     h->pair_mode = mode != 0;
     h->l2_hints = mode != 2;
+    h->pair_rows = mode == 3 ? 1 : mode == 4 ? 2 : 0;
     return VNM_OK;
 }
 
@@ -372,7 +374,7 @@ int vnm_spmm_config(vnm_handle_t h, int N, int *tile_m, int *tile_n, int *stages
 {
     if (!h) return fail(VNM_ERR_BAD_ARG, "null handle");
     SpmmConfig cfg;
-    const bool pair = h->dense_b && h->pair_mode && N >= 128 && spmm_dense_b_pair_config(h->M, N, h->max_ctas, &cfg);
+    const bool pair = h->dense_b && h->pair_mode && N >= 128 && spmm_dense_b_pair_config(h->M, N, h->K, h->max_ctas, h->pair_rows, &cfg);
     if (pair) { /* cfg filled */ }
     else if (h->dense_b) spmm_dense_b_config(h->M, N, h->max_ctas, &cfg);
     else if (!spmm_select_config(h->V, N, h->M, h->producer_warps, h->max_ctas, &cfg)) return fail(VNM_ERR_UNSUPPORTED, "unsupported V");
@@ -385,9 +387,15 @@ int vnm_spmm_config(vnm_handle_t h, int N, int *tile_m, int *tile_n, int *stages
 }
 
 static int spmm_impl(vnm_handle_t h, const void *B, int64_t ldb, int N, int b_nk, const void *bias, void *out, int64_t ldo, int layout,
-                     void *stream)
+                     void *stream, void *const *more_outs = nullptr, int n_more = 0)
 {
     if (!h || !B || !out) return fail(VNM_ERR_BAD_ARG, "vnm_spmm_f16: null pointer");
+    if (n_more < 0 || n_more > MAX_OUTS - 1 || (n_more > 0 && !more_outs))
+        return fail(VNM_ERR_BAD_ARG, "vnm_spmm_f16_multi: between 1 and %d destinations", MAX_OUTS);
+    if (n_more > 0 && !h->dense_b)
+        return fail(VNM_ERR_UNSUPPORTED, "vnm_spmm_f16_multi: several destinations need an operand prepared in dense-B form (TMA-store epilogue)");
+    for (int d = 0; d < n_more; d++)
+        if (!more_outs[d] || ((uintptr_t)more_outs[d] & 15)) return fail(VNM_ERR_BAD_ARG, "vnm_spmm_f16_multi: destination %d is null or not 16-byte aligned", d + 1);
     {
         // the handle's private copy, its status word and the kernel attributes belong to one device
         int dev = -1;
@@ -413,7 +421,7 @@ static int spmm_impl(vnm_handle_t h, const void *B, int64_t ldb, int N, int b_nk
         return fail(VNM_ERR_BAD_ARG, "vnm_spmm_f16: unknown layout %d", layout);
     }
     SpmmConfig cfg;
-    const bool pair = h->dense_b && h->pair_mode && (b_nk || N >= 128) && spmm_dense_b_pair_config(h->M, N, h->max_ctas, &cfg);
+    const bool pair = h->dense_b && h->pair_mode && (b_nk || N >= 128) && spmm_dense_b_pair_config(h->M, N, h->K, h->max_ctas, h->pair_rows, &cfg);
     if (pair) { /* cfg filled */ }
     else if (h->dense_b) spmm_dense_b_config(h->M, N, h->max_ctas, &cfg);
     else if (!spmm_select_config(h->V, N, h->M, h->producer_warps, h->max_ctas, &cfg)) return fail(VNM_ERR_UNSUPPORTED, "unsupported V");
@@ -529,29 +537,32 @@ static int spmm_impl(vnm_handle_t h, const void *B, int64_t ldb, int N, int b_nk
     p.hybrid_rows = h->hybrid_rows;
     p.b_nk = b_nk;
     p.b_wide_ok = h->tm_wide ? 1 : 0;
+    p.n_out = 1;
     if (h->dense_b) {
         // The result leaves through TMA stores: [M,N] as boxes of 40 columns x 128 rows, [N,M] as boxes of 128
         // columns (m) x 40 rows (n).
         if (layout == VNM_LAYOUT_NM && (ldo % 8 != 0 || ((uintptr_t)out & 15)))
             return fail(VNM_ERR_BAD_ARG, "vnm_spmm_f16: layout NM needs ldo %% 8 == 0 and a 16-byte aligned out for this operand");
         CUtensorMap tmap_out;
+        OutMaps more;
+        memset(&more, 0, sizeof(more));
         cuuint32_t oestr[2] = {1, 1};
         cuuint64_t ostrides[1] = {(cuuint64_t)ldo * 2};
-        CUresult r;
-        if (layout == VNM_LAYOUT_MN) {
-            cuuint64_t odims[2] = {(cuuint64_t)N, (cuuint64_t)h->M};
-            cuuint32_t obox[2] = {40, 128};
-            r = enc(&tmap_out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, out, odims, ostrides, obox, oestr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-        } else {
-            cuuint64_t odims[2] = {(cuuint64_t)h->M, (cuuint64_t)N};
-            cuuint32_t obox[2] = {128, 40};
-            r = enc(&tmap_out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, out, odims, ostrides, obox, oestr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        cuuint64_t odims[2] = {(cuuint64_t)N, (cuuint64_t)h->M};
+        cuuint32_t obox[2] = {40, 128};
+        if (layout == VNM_LAYOUT_NM) {
+            odims[0] = (cuuint64_t)h->M; odims[1] = (cuuint64_t)N;
+            obox[0] = 128; obox[1] = 40;
         }
-        if (r != CUDA_SUCCESS) return fail(VNM_ERR_CUDA, "cuTensorMapEncodeTiled (output) failed with CUresult %d", (int)r);
-        if (pair) VNM_CUDA(launch_spmm_dense_b_pair(cfg, h->tmap_tile, h->tmap_tile2, tmap_out, p, (cudaStream_t)stream), "spmm launch");
-        else VNM_CUDA(launch_spmm_dense_b(cfg, h->tmap_tile, h->tmap_tile2, tmap_out, p, (cudaStream_t)stream), "spmm launch");
+        for (int d = 0; d <= n_more; d++) {
+            CUresult r = enc(d == 0 ? &tmap_out : &more.m[d - 1], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, d == 0 ? out : more_outs[d - 1], odims, ostrides, obox,
+                             oestr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (r != CUDA_SUCCESS) return fail(VNM_ERR_CUDA, "cuTensorMapEncodeTiled (output %d) failed with CUresult %d", d, (int)r);
+        }
+        p.n_out = 1 + n_more;
+        if (pair) VNM_CUDA(launch_spmm_dense_b_pair(cfg, h->tmap_tile, h->tmap_tile2, tmap_out, more, p, (cudaStream_t)stream), "spmm launch");
+        else VNM_CUDA(launch_spmm_dense_b(cfg, h->tmap_tile, h->tmap_tile2, tmap_out, more, p, (cudaStream_t)stream), "spmm launch");
     } else {
         VNM_CUDA(launch_spmm(cfg, h->tmap_rows, h->tmap_tile, p, (cudaStream_t)stream), "spmm launch");
     }
@@ -566,6 +577,13 @@ int vnm_spmm_f16(vnm_handle_t h, const void *B, int64_t ldb, int N, const void *
 int vnm_spmm_f16_nk(vnm_handle_t h, const void *Bt, int64_t ldbt, int N, const void *bias, void *out, int64_t ldo, int layout, void *stream)
 {
     return spmm_impl(h, Bt, ldbt, N, 1, bias, out, ldo, layout, stream);
+}
+
+int vnm_spmm_f16_multi(vnm_handle_t h, const void *B, int64_t ldb, int N, const void *bias, void *const *outs, int n_outs, int64_t ldo, int layout,
+                       void *stream)
+{
+    if (!outs || n_outs < 1 || n_outs > MAX_OUTS) return fail(VNM_ERR_BAD_ARG, "vnm_spmm_f16_multi: between 1 and %d destinations", MAX_OUTS);
+    return spmm_impl(h, B, ldb, N, 0, bias, outs[0], ldo, layout, stream, outs + 1, n_outs - 1);
 }
 
 int vnm_operand_form(vnm_handle_t h, int *dense_b)

@@ -244,45 +244,71 @@ __global__ void __launch_bounds__(256) compress_tiled_kernel(const __half *__res
 
 // ------------------------------------------------------------------------------------------------
 // Compressor, register form, for the common shapes: no mask, m in {4, 8, 16}, K % (4 * m) == 0 (whole tiles, no
-// padded group) and 16-byte aligned rows.  One thread compresses one (row, tile) = four groups: it loads its 4 * m
-// halves with 16-byte loads straight into registers (no shared-memory staging: the tiled kernel spends most of its
-// instructions moving data in and out of shared memory), picks the four candidates of every group out of those
-// registers, and the 16 lanes that hold the 16 rows of a value strip transpose their four words among groups of four
-// lanes, so that every lane stores one 16-byte piece of the reference's value order.  A warp covers 16 rows x 2 tiles,
-// a CTA 16 rows x 16 tiles (1 KiB of every row for m = 8).
+// padded group), V a multiple of 16 and 16-byte aligned rows.  One thread compresses one (row, tile) = four groups: it
+// loads its 4 * m halves with 16-byte loads straight into registers (no shared-memory staging: the tiled kernel spends
+// most of its instructions moving data in and out of shared memory), picks the four candidates of every group out of
+// those registers, and the 16 lanes that hold the 16 rows of a value strip transpose their four words among groups of
+// four lanes, so that every lane stores one 16-byte piece of the reference's value order.  A warp covers 16 rows x 2
+// tiles, a CTA one chunk = 16 rows x 16 tiles (1 KiB of every row for m = 8).  The grid is one resident wave; a CTA
+// walks chunks blockIdx.x, + gridDim.x, ... so that neighbouring CTAs read neighbouring pieces of the same rows, and
+// all index arithmetic that involves a division is per chunk (uniform over the CTA).  With PREFETCH the loads of the
+// next chunk are issued before the current one is worked on.
 // ------------------------------------------------------------------------------------------------
-template <int M_>
-__global__ void __launch_bounds__(256) compress_direct_kernel(const __half *__restrict__ dense, int64_t ldd, const uint32_t *__restrict__ colloc,
-                                                              int M, int K, int V, int64_t Ksp, uint32_t *__restrict__ values,
+#ifndef VNM_COMPRESS_PREFETCH
+#define VNM_COMPRESS_PREFETCH 0
+#endif
+#ifndef VNM_COMPRESS_MINB
+#define VNM_COMPRESS_MINB 1
+#endif
+template <int M_, bool PREFETCH>
+__global__ void __launch_bounds__(256, VNM_COMPRESS_MINB) compress_direct_kernel(const __half *__restrict__ dense, int64_t ldd, const uint32_t *__restrict__ colloc,
+                                                              int V, int tiles, uint32_t tchunks, uint32_t chunks, uint32_t *__restrict__ values,
                                                               uint32_t *__restrict__ meta, unsigned long long *violations)
 {
     constexpr int NW = M_ / 2;   // 32-bit words per group
     const int lane = threadIdx.x & 31;
-    const int64_t tiles = Ksp / 8;
-    const int64_t total = (int64_t)(M / 16) * tiles * 16;
+    const int r16 = threadIdx.x & 15, tl = threadIdx.x >> 4;
+    const int64_t Ksp = (int64_t)tiles * 8;
     unsigned int bad = 0;
-    for (int64_t base = (int64_t)blockIdx.x * blockDim.x; base < total; base += (int64_t)gridDim.x * blockDim.x) {
-        // whole warps stay together for the shuffles: a thread past the end repeats the last item and stores nothing
-        const bool valid = base + threadIdx.x < total;
-        const int64_t idx = valid ? base + threadIdx.x : total - 1;
-        const int r16 = (int)(idx & 15);
-        const int64_t q = idx >> 4;
-        const int64_t strip = q / tiles;
-        const int64_t T = q - strip * tiles;
-        const int64_t r = strip * 16 + r16;
-        const uint4 *src = reinterpret_cast<const uint4 *>(dense + r * ldd + T * 4 * M_);
-        const uint4 *c4p = reinterpret_cast<const uint4 *>(colloc + (r / V) * (Ksp / 2) * 4 + T * 16);
-        uint32_t w[4 * NW];
+    uint32_t w[4 * NW], wn[PREFETCH ? 4 * NW : 1];
+    // (strip, tile) of this thread in chunk c; a thread past the last tile repeats the last one and stores nothing
+    auto locate = [&](uint32_t c, uint32_t *strip, int *T) {
+        *strip = c / tchunks;
+        const int t = (int)(c - *strip * tchunks) * 16 + tl;
+        *T = t < tiles ? t : tiles - 1;
+        return t < tiles;
+    };
+    auto load = [&](uint32_t c, uint32_t *dst) {
+        uint32_t strip;
+        int T;
+        locate(c, &strip, &T);
+        const uint4 *src = reinterpret_cast<const uint4 *>(dense + ((int64_t)strip * 16 + r16) * ldd + (int64_t)T * 4 * M_);
 #pragma unroll
         for (int i = 0; i < NW; i++) {   // 4 * NW words = NW loads of 16 bytes
             const uint4 v = __ldg(src + i);
-            w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
+            dst[4 * i] = v.x; dst[4 * i + 1] = v.y; dst[4 * i + 2] = v.z; dst[4 * i + 3] = v.w;
+        }
+    };
+    if (PREFETCH && blockIdx.x < chunks) load(blockIdx.x, w);
+    for (uint32_t c = blockIdx.x; c < chunks; c += gridDim.x) {
+        uint32_t strip;
+        int T;
+        const bool valid = locate(c, &strip, &T);
+        const int r = (int)strip * 16 + r16;
+        const uint4 *c4p = reinterpret_cast<const uint4 *>(colloc + (int64_t)(strip * 16u / (uint32_t)V) * (Ksp / 2) * 4 + (int64_t)T * 16);
+        uint4 c4s[4];
+#pragma unroll
+        for (int gi = 0; gi < 4; gi++) c4s[gi] = __ldg(c4p + gi);
+        if (PREFETCH) {
+            if (c + gridDim.x < chunks) load(c + gridDim.x, wn);
+        } else {
+            load(c, w);
         }
         uint32_t out[4];
         uint32_t hw = 0;
 #pragma unroll
         for (int gi = 0; gi < 4; gi++) {
-            const uint4 c4 = __ldg(c4p + gi);
+            const uint4 c4 = c4s[gi];
             const uint32_t cand[4] = {c4.x, c4.y, c4.z, c4.w};
             uint32_t o = 0;
             int pos = 0;
@@ -291,23 +317,23 @@ __global__ void __launch_bounds__(256) compress_direct_kernel(const __half *__re
             } else {
 #pragma unroll
                 for (int j = 0; j < 4; j++) {
-                    const uint32_t c = cand[j];
-                    // half c of the group's NW words: a binary select tree down to a pair of words, then one byte permute
+                    const uint32_t cc = cand[j];
+                    // half cc of the group's NW words: a binary select tree down to a pair of words, then one byte permute
                     uint32_t lo, hi;
                     if (NW == 2) {
                         lo = w[gi * NW]; hi = w[gi * NW + 1];
                     } else if (NW == 4) {
-                        const bool up = (c & 4u) != 0;
+                        const bool up = (cc & 4u) != 0;
                         lo = up ? w[gi * NW + 2] : w[gi * NW];
                         hi = up ? w[gi * NW + 3] : w[gi * NW + 1];
                     } else {
-                        const bool up8 = (c & 8u) != 0, up4 = (c & 4u) != 0;
+                        const bool up8 = (cc & 8u) != 0, up4 = (cc & 4u) != 0;
                         const uint32_t a0 = up8 ? w[gi * NW + 4] : w[gi * NW], a1 = up8 ? w[gi * NW + 5] : w[gi * NW + 1];
                         const uint32_t a2 = up8 ? w[gi * NW + 6] : w[gi * NW + 2], a3 = up8 ? w[gi * NW + 7] : w[gi * NW + 3];
                         lo = up4 ? a2 : a0;
                         hi = up4 ? a3 : a1;
                     }
-                    const uint32_t h2 = (c & 3u) * 2u;
+                    const uint32_t h2 = (cc & 3u) * 2u;
                     const uint32_t bits = __byte_perm(lo, hi, ((h2 + 1u) << 4) | h2) & 0xFFFFu;
                     if ((bits & 0x7FFFu) != 0) {   // kept entries are the non-zero values
                         if (pos < 2) {
@@ -333,15 +359,36 @@ __global__ void __launch_bounds__(256) compress_direct_kernel(const __half *__re
             if (qd & 1) { out[0] = u0; out[2] = u1; } else { out[1] = u0; out[3] = u1; }
         }
         // now out[k] of lane (sb, qd) = word of row 4*sb + k, group qd ... stored as [sub-block][group][row][slot]
-        uint4 *vdst = reinterpret_cast<uint4 *>(values + (strip * 16 * Ksp + T * 128) / 2) + (r16 >> 2) * 4 + qd;
+        uint4 *vdst = reinterpret_cast<uint4 *>(values + ((int64_t)strip * 16 * Ksp + (int64_t)T * 128) / 2) + (r16 >> 2) * 4 + qd;
         if (valid) *vdst = make_uint4(out[0], out[1], out[2], out[3]);
         const uint32_t other = __shfl_xor_sync(0xffffffffu, hw, 1);
-        if (valid && (r16 & 1) == 0) meta[(r / 32) * 16 * tiles + T * 16 + (r % 32) / 2] = hw | (other << 16);
+        if (valid && (r16 & 1) == 0) meta[(int64_t)(r / 32) * 16 * tiles + (int64_t)T * 16 + (r % 32) / 2] = hw | (other << 16);
+        if (PREFETCH) {
+#pragma unroll
+            for (int i = 0; i < 4 * NW; i++) w[i] = wn[i];
+        }
     }
     if (violations != nullptr) {
         for (int o = 16; o > 0; o >>= 1) bad += __shfl_xor_sync(0xffffffffu, bad, o);
         if (lane == 0 && bad) atomicAdd(violations, (unsigned long long)bad);
     }
+}
+
+// one resident wave of the register-form compressor on the current device (cached per kernel and device)
+template <int M_>
+static int compress_direct_wave()
+{
+    static int cached[64] = {0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) dev = 0;
+    if (cached[dev] == 0) {
+        int per_sm = 0, sms = 0;
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, compress_direct_kernel<M_, VNM_COMPRESS_PREFETCH != 0>, 256, 0);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        cached[dev] = (per_sm > 0 && sms > 0) ? per_sm * sms : 148 * 4;
+    }
+    return cached[dev];
 }
 
 cudaError_t launch_compress(const void *dense, int64_t ldd, const int32_t *mask, const uint32_t *colloc, int M, int K, int V, int m,
@@ -350,18 +397,20 @@ cudaError_t launch_compress(const void *dense, int64_t ldd, const int32_t *mask,
     const int64_t Ksp = ksp_of(K, m);
     const int threads = 256;
     // register form: no mask, whole tiles, 16-byte aligned rows and outputs
-    if (!mask && (m == 4 || m == 8 || m == 16) && K % (4 * m) == 0 && Ksp == (int64_t)K / m * 2 && M % 16 == 0 && ldd % 8 == 0 &&
-        ((uintptr_t)dense & 15) == 0 && ((uintptr_t)values & 15) == 0 && ((uintptr_t)colloc & 15) == 0) {
-        const int64_t total = (int64_t)M * (Ksp / 8);
-        int64_t blocks = (total + threads - 1) / threads;
-        const int64_t cap = (int64_t)148 * 32;
-        if (blocks > cap) blocks = cap;
+    if (!mask && (m == 4 || m == 8 || m == 16) && K % (4 * m) == 0 && Ksp == (int64_t)K / m * 2 && M % 16 == 0 && V % 16 == 0 && ldd % 8 == 0 &&
+        ((uintptr_t)dense & 15) == 0 && ((uintptr_t)values & 15) == 0 && ((uintptr_t)colloc & 15) == 0 &&
+        (int64_t)(M / 16) * ((Ksp / 8 + 15) / 16) < ((int64_t)1 << 31)) {
+        constexpr bool PF = VNM_COMPRESS_PREFETCH != 0;
+        const int tiles = (int)(Ksp / 8);
+        const uint32_t tchunks = (uint32_t)((tiles + 15) / 16), chunks = (uint32_t)(M / 16) * tchunks;
+        const int wave = m == 4 ? compress_direct_wave<4>() : m == 8 ? compress_direct_wave<8>() : compress_direct_wave<16>();
+        const unsigned blocks = chunks < (uint32_t)wave ? chunks : (unsigned)wave;
         if (m == 4)
-            compress_direct_kernel<4><<<(unsigned)blocks, threads, 0, stream>>>((const __half *)dense, ldd, colloc, M, K, V, Ksp, (uint32_t *)values, meta, violations);
+            compress_direct_kernel<4, PF><<<blocks, threads, 0, stream>>>((const __half *)dense, ldd, colloc, V, tiles, tchunks, chunks, (uint32_t *)values, meta, violations);
         else if (m == 8)
-            compress_direct_kernel<8><<<(unsigned)blocks, threads, 0, stream>>>((const __half *)dense, ldd, colloc, M, K, V, Ksp, (uint32_t *)values, meta, violations);
+            compress_direct_kernel<8, PF><<<blocks, threads, 0, stream>>>((const __half *)dense, ldd, colloc, V, tiles, tchunks, chunks, (uint32_t *)values, meta, violations);
         else
-            compress_direct_kernel<16><<<(unsigned)blocks, threads, 0, stream>>>((const __half *)dense, ldd, colloc, M, K, V, Ksp, (uint32_t *)values, meta, violations);
+            compress_direct_kernel<16, PF><<<blocks, threads, 0, stream>>>((const __half *)dense, ldd, colloc, V, tiles, tchunks, chunks, (uint32_t *)values, meta, violations);
         return cudaGetLastError();
     }
     const bool aligned = ldd % 4 == 0 && ((uintptr_t)dense & 7) == 0 && ((uintptr_t)mask & 7) == 0 && ((uintptr_t)meta & 15) == 0 &&

@@ -36,6 +36,14 @@ struct SpmmParams {
     int out32;            // gather kernel, layout MN: 32-bit stores from registers instead of staged 128-bit stores (ablation)
     int b_nk;             // dense-B kernel only: the dense operand is given as [N, K] row-major (K contiguous)
     int b_wide_ok;        // dense-B kernel only: the 4-D tensor map exists (column tiles with 256 columns inside N use one box per stage)
+    int n_out;            // dense-B kernels: destinations of every output tile (1 = `out` only; more: the OutMaps argument, e.g. peers' buffers)
+};
+
+// Destinations 2 .. MAX_OUTS of a product whose every output tile is stored to several buffers of one geometry
+// (a rank's own result buffer and the same rows of its peers' buffers): tensor maps like the first output map.
+constexpr int MAX_OUTS = 8;
+struct alignas(64) OutMaps {
+    CUtensorMap m[MAX_OUTS - 1];
 };
 
 // How the producer warps bring the selected rows of B into shared memory.
@@ -88,13 +96,13 @@ cudaError_t launch_spmm(const SpmmConfig &cfg, const CUtensorMap &tmap_rows, con
 cudaError_t spmm_dense_b_init();
 cudaError_t launch_wait_expiry_selftest(int *status, cudaStream_t stream);
 void spmm_dense_b_config(int M, int N, int max_ctas, SpmmConfig *cfg);  // max_ctas: 0 = one per SM
-cudaError_t launch_spmm_dense_b(const SpmmConfig &cfg, const CUtensorMap &tmap_tile, const CUtensorMap &tmap_tile2, const CUtensorMap &tmap_out,
+cudaError_t launch_spmm_dense_b(const SpmmConfig &cfg, const CUtensorMap &tmap_tile, const CUtensorMap &tmap_tile2, const CUtensorMap &tmap_out, const OutMaps &more_out,
                                 const SpmmParams &p, cudaStream_t stream);
 
 // Dense-B form on pairs of SMs (clusters of two CTAs, tcgen05 cta_group::2): 512 x 240 pair tiles (vnm_spmm_dense_b2.cu).
 cudaError_t spmm_dense_b_pair_init();
-bool spmm_dense_b_pair_config(int M, int N, int max_ctas, SpmmConfig *cfg);  // false: use the single-CTA kernel
-cudaError_t launch_spmm_dense_b_pair(const SpmmConfig &cfg, const CUtensorMap &tmap_tile, const CUtensorMap &tmap_tile2, const CUtensorMap &tmap_out,
+bool spmm_dense_b_pair_config(int M, int N, int K, int max_ctas, int force_rows, SpmmConfig *cfg);  // false: use the single-CTA kernel; force_rows: 0 auto, 1 / 2 row tiles per CTA
+cudaError_t launch_spmm_dense_b_pair(const SpmmConfig &cfg, const CUtensorMap &tmap_tile, const CUtensorMap &tmap_tile2, const CUtensorMap &tmap_out, const OutMaps &more_out,
                                      const SpmmParams &p, cudaStream_t stream);
 
 }  // namespace vnm

@@ -10,8 +10,12 @@
 // had to wait for one would run after all the others.
 //
 // NCCL is bound at run time (dlopen of libnccl.so.2, preferring a copy the process has already loaded, e.g.
-// PyTorch's): the library has no link-time dependency on it and single-GPU users never load it.  Only NCCL
-// collectives on LOCAL buffers are used -- no kernel of this library reads a peer's memory.
+// PyTorch's): the library has no link-time dependency on it and single-GPU users never load it.
+//
+// vnm_mgpu_spmm_gathered_p2p is the form without an exchange step: result buffers registered through CUDA IPC are
+// mapped into every rank, and the product's epilogue stores each output tile to all of them with plain (non-multicast)
+// TMA stores, its own buffer first and the peers' over NVLink.  No kernel of this library READS a peer's memory, and
+// ranks wait for one another only in NCCL collectives, never inside a kernel of this library.
 #include "../../include/venom_b200.h"
 #include "vnm_internal.h"
 
@@ -23,6 +27,7 @@
 #include <cstring>
 #include <mutex>
 #include <new>
+#include <vector>
 
 using namespace vnm;
 
@@ -99,6 +104,41 @@ const NcclApi *nccl()
 
 constexpr int kMaxChunks = 16;
 
+// what a rank tells the others about a result buffer: the IPC handle of the allocation that holds it and where in
+// that allocation the buffer starts
+struct IpcNote {
+    cudaIpcMemHandle_t handle;
+    unsigned long long offset, bytes;
+    int ok, device;
+};
+
+struct PeerMapping {      // one opened allocation of one peer (an allocation may hold several registered buffers)
+    int rank;
+    cudaIpcMemHandle_t handle;
+    void *base;
+    int refs;
+};
+
+struct Registered {
+    void *local;
+    size_t bytes;
+    void *peer[MAX_OUTS];  // [rank] the buffer of that rank in this process's address space (own rank: local)
+};
+
+typedef CUresult (*AddressRangeFn)(CUdeviceptr *, size_t *, CUdeviceptr);
+AddressRangeFn get_address_range_fn()
+{
+    static AddressRangeFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = (AddressRangeFn)p;
+    });
+    return fn;
+}
+
 }  // namespace
 
 struct vnm_mgpu_s {
@@ -109,6 +149,10 @@ struct vnm_mgpu_s {
     cudaStream_t comm_stream;  // the exchange runs here, beside the product on the caller's stream
     cudaEvent_t chunk_done[kMaxChunks];
     cudaEvent_t joined;
+    IpcNote *notes;            // device: [world] exchange buffer of register_output
+    int *sync_words;           // device: [world] payload of the small all-gathers that order the ranks around a peer-store product
+    std::vector<PeerMapping> mappings;
+    std::vector<Registered> registered;
 };
 
 extern "C" {
@@ -144,6 +188,9 @@ static int finish_create(vnm_mgpu_s *c, vnm_mgpu_t *ctx)
     if (e == cudaSuccess) e = cudaStreamCreateWithPriority(&c->comm_stream, cudaStreamNonBlocking, prio_high);
     for (int i = 0; e == cudaSuccess && i < kMaxChunks; i++) e = cudaEventCreateWithFlags(&c->chunk_done[i], cudaEventDisableTiming);
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->joined, cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaMalloc(&c->notes, sizeof(IpcNote) * (size_t)c->world);
+    if (e == cudaSuccess) e = cudaMalloc(&c->sync_words, sizeof(int) * (size_t)c->world);
+    if (e == cudaSuccess) e = cudaMemset(c->sync_words, 0, sizeof(int) * (size_t)c->world);
     if (e != cudaSuccess) {
         vnm_mgpu_destroy(c);
         return mfail(VNM_ERR_CUDA, "vnm_mgpu_create: %s", cudaGetErrorString(e));
@@ -198,6 +245,14 @@ int vnm_mgpu_destroy(vnm_mgpu_t c)
 {
     if (!c) return VNM_OK;
     if (c->comm_stream) cudaStreamSynchronize(c->comm_stream);
+    if (!c->mappings.empty()) {
+        // peers' buffers still mapped: the caller should have unregistered (collectively); unmap after this device is idle
+        cudaDeviceSynchronize();
+        for (PeerMapping &m : c->mappings) cudaIpcCloseMemHandle(m.base);
+        c->mappings.clear();
+    }
+    if (c->notes) cudaFree(c->notes);
+    if (c->sync_words) cudaFree(c->sync_words);
     for (cudaEvent_t e : c->chunk_done)
         if (e) cudaEventDestroy(e);
     if (c->joined) cudaEventDestroy(c->joined);
@@ -310,6 +365,184 @@ int vnm_mgpu_spmm_gathered(vnm_mgpu_t c, vnm_handle_t h, const void *B_shard, in
         cudaEventRecord(c->joined, c->comm_stream);
         cudaStreamWaitEvent(s, c->joined, 0);
         vnm_set_max_ctas(h, user_cap);
+    }
+    return rc;
+}
+
+// A small all-gather on `s`: returns (in stream order) on a rank only after every rank has reached the same point.
+static int rank_barrier(vnm_mgpu_s *c, const NcclApi *api, cudaStream_t s)
+{
+    VNM_NCCL(api->AllGather(c->sync_words + c->rank, c->sync_words, sizeof(int), ncclChar, c->comm, s), "ncclAllGather (rank barrier)");
+    return VNM_OK;
+}
+
+static void release_mapping(vnm_mgpu_s *c, int rank, void *peer_ptr)
+{
+    for (size_t i = 0; i < c->mappings.size(); ++i) {
+        PeerMapping &m = c->mappings[i];
+        if (m.rank != rank || (char *)peer_ptr < (char *)m.base) continue;
+        // the mapping that holds peer_ptr: the one with the closest base below it
+        bool closest = true;
+        for (const PeerMapping &o : c->mappings)
+            if (o.rank == rank && (char *)o.base > (char *)m.base && (char *)o.base <= (char *)peer_ptr) closest = false;
+        if (!closest) continue;
+        if (--m.refs == 0) {
+            cudaIpcCloseMemHandle(m.base);
+            c->mappings.erase(c->mappings.begin() + (long)i);
+        }
+        return;
+    }
+}
+
+int vnm_mgpu_register_output(vnm_mgpu_t c, void *out_full, size_t bytes)
+{
+    if (!c || !out_full || bytes == 0) return mfail(VNM_ERR_BAD_ARG, "vnm_mgpu_register_output: null pointer or empty buffer");
+    const NcclApi *api = nccl();
+    if (!api) return mfail(VNM_ERR_UNSUPPORTED, "NCCL (libnccl.so.2) could not be loaded");
+    const int W = c->world;
+    for (const Registered &r : c->registered)
+        if (r.local == out_full) return mfail(VNM_ERR_BAD_ARG, "vnm_mgpu_register_output: this buffer is already registered");
+    // every rank takes part in both exchanges below even if something failed locally, so that nobody waits forever
+    IpcNote mine;
+    memset(&mine, 0, sizeof(mine));
+    mine.device = c->device;
+    char why[256] = "";
+    if (W > MAX_OUTS) {
+        snprintf(why, sizeof(why), "at most %d ranks", MAX_OUTS);
+    } else {
+        AddressRangeFn range = get_address_range_fn();
+        CUdeviceptr base = 0;
+        size_t span = 0;
+        if (!range || range(&base, &span, (CUdeviceptr)out_full) != CUDA_SUCCESS) {
+            snprintf(why, sizeof(why), "the buffer is not inside a device allocation of this process");
+        } else if ((size_t)((char *)out_full - (char *)base) + bytes > span) {
+            snprintf(why, sizeof(why), "the buffer runs past the end of its allocation");
+        } else {
+            cudaError_t e = cudaIpcGetMemHandle(&mine.handle, (void *)base);
+            if (e != cudaSuccess) {
+                snprintf(why, sizeof(why), "cudaIpcGetMemHandle: %s (the buffer must come from cudaMalloc)", cudaGetErrorString(e));
+                cudaGetLastError();
+            } else {
+                mine.offset = (unsigned long long)((char *)out_full - (char *)base);
+                mine.bytes = bytes;
+                mine.ok = 1;
+            }
+        }
+    }
+    std::vector<IpcNote> all((size_t)W);
+    cudaStream_t xs = c->comm_stream;
+    VNM_CU(cudaMemcpyAsync(c->notes + c->rank, &mine, sizeof(mine), cudaMemcpyHostToDevice, xs), "cudaMemcpyAsync");
+    VNM_NCCL(api->AllGather(c->notes + c->rank, c->notes, sizeof(IpcNote), ncclChar, c->comm, xs), "ncclAllGather (IPC handles)");
+    VNM_CU(cudaMemcpyAsync(all.data(), c->notes, sizeof(IpcNote) * (size_t)W, cudaMemcpyDeviceToHost, xs), "cudaMemcpyAsync");
+    VNM_CU(cudaStreamSynchronize(xs), "cudaStreamSynchronize");
+    bool everyone = true;
+    for (int r = 0; r < W; ++r) everyone = everyone && all[(size_t)r].ok && all[(size_t)r].bytes == bytes;
+    Registered reg;
+    memset(&reg, 0, sizeof(reg));
+    reg.local = out_full;
+    reg.bytes = bytes;
+    int opened_ok = everyone ? 1 : 0;
+    if (everyone) {
+        for (int r = 0; r < W && opened_ok; ++r) {
+            if (r == c->rank) { reg.peer[r] = out_full; continue; }
+            const IpcNote &n = all[(size_t)r];
+            if (n.device == c->device) {
+                snprintf(why, sizeof(why), "rank %d uses the same device", r);
+                opened_ok = 0;
+                break;
+            }
+            PeerMapping *have = nullptr;
+            for (PeerMapping &m : c->mappings)
+                if (m.rank == r && memcmp(&m.handle, &n.handle, sizeof(n.handle)) == 0) have = &m;
+            if (!have) {
+                void *base = nullptr;
+                cudaError_t e = cudaIpcOpenMemHandle(&base, n.handle, cudaIpcMemLazyEnablePeerAccess);
+                if (e != cudaSuccess) {
+                    snprintf(why, sizeof(why), "cudaIpcOpenMemHandle (rank %d): %s", r, cudaGetErrorString(e));
+                    cudaGetLastError();
+                    opened_ok = 0;
+                    break;
+                }
+                PeerMapping m;
+                m.rank = r; m.handle = n.handle; m.base = base; m.refs = 0;
+                c->mappings.push_back(m);
+                have = &c->mappings.back();
+            }
+            have->refs++;
+            reg.peer[r] = (char *)have->base + n.offset;
+        }
+    }
+    // second round: did every rank map every peer?
+    IpcNote verdict;
+    memset(&verdict, 0, sizeof(verdict));
+    verdict.ok = opened_ok;
+    VNM_CU(cudaMemcpyAsync(c->notes + c->rank, &verdict, sizeof(verdict), cudaMemcpyHostToDevice, xs), "cudaMemcpyAsync");
+    VNM_NCCL(api->AllGather(c->notes + c->rank, c->notes, sizeof(IpcNote), ncclChar, c->comm, xs), "ncclAllGather (IPC verdict)");
+    VNM_CU(cudaMemcpyAsync(all.data(), c->notes, sizeof(IpcNote) * (size_t)W, cudaMemcpyDeviceToHost, xs), "cudaMemcpyAsync");
+    VNM_CU(cudaStreamSynchronize(xs), "cudaStreamSynchronize");
+    bool all_ok = true;
+    for (int r = 0; r < W; ++r) all_ok = all_ok && all[(size_t)r].ok;
+    if (!all_ok) {
+        for (int r = 0; r < W; ++r)
+            if (r != c->rank && reg.peer[r]) release_mapping(c, r, reg.peer[r]);
+        return mfail(VNM_ERR_UNSUPPORTED, "vnm_mgpu_register_output: the result buffers could not be shared between the ranks%s%s", why[0] ? ": " : " (another rank failed)",
+                     why);
+    }
+    c->registered.push_back(reg);
+    return VNM_OK;
+}
+
+int vnm_mgpu_unregister_output(vnm_mgpu_t c, void *out_full)
+{
+    if (!c || !out_full) return mfail(VNM_ERR_BAD_ARG, "vnm_mgpu_unregister_output: null pointer");
+    const NcclApi *api = nccl();
+    if (!api) return mfail(VNM_ERR_UNSUPPORTED, "NCCL (libnccl.so.2) could not be loaded");
+    size_t at = c->registered.size();
+    for (size_t i = 0; i < c->registered.size(); ++i)
+        if (c->registered[i].local == out_full) at = i;
+    if (at == c->registered.size()) return mfail(VNM_ERR_BAD_ARG, "vnm_mgpu_unregister_output: this buffer is not registered");
+    // nobody may still be storing into a buffer that is about to be unmapped: all work of this device, then all ranks
+    VNM_CU(cudaDeviceSynchronize(), "cudaDeviceSynchronize");
+    if (int rc = rank_barrier(c, api, c->comm_stream)) return rc;
+    VNM_CU(cudaStreamSynchronize(c->comm_stream), "cudaStreamSynchronize");
+    for (int r = 0; r < c->world; ++r)
+        if (r != c->rank) release_mapping(c, r, c->registered[at].peer[r]);
+    c->registered.erase(c->registered.begin() + (long)at);
+    return VNM_OK;
+}
+
+int vnm_mgpu_spmm_gathered_p2p(vnm_mgpu_t c, vnm_handle_t h, const void *B_shard, int64_t ldb, int N_total, const void *bias, void *out_full,
+                               int64_t ldo, void *stream)
+{
+    if (!c || !h || !B_shard || !out_full) return mfail(VNM_ERR_BAD_ARG, "vnm_mgpu_spmm_gathered_p2p: null pointer");
+    const int W = c->world;
+    if (W > MAX_OUTS) return mfail(VNM_ERR_UNSUPPORTED, "vnm_mgpu_spmm_gathered_p2p: at most %d ranks", MAX_OUTS);
+    if (N_total <= 0 || N_total % (8 * W) != 0)
+        return mfail(VNM_ERR_UNSUPPORTED, "vnm_mgpu_spmm_gathered_p2p: N (%d) must be a multiple of 8 x ranks (%d)", N_total, 8 * W);
+    int M = 0, dense_b = 0;
+    if (int rc = vnm_handle_info(h, &M, nullptr, nullptr, nullptr, nullptr)) return rc;
+    if (int rc = vnm_operand_form(h, &dense_b)) return rc;
+    if (!dense_b) return mfail(VNM_ERR_UNSUPPORTED, "vnm_mgpu_spmm_gathered_p2p: the operand is not held in dense-B form (its epilogue has no TMA stores)");
+    if (ldo != M) return mfail(VNM_ERR_UNSUPPORTED, "vnm_mgpu_spmm_gathered_p2p: the gathered [N, M] result must be dense (ldo == M = %d, got %lld)", M, (long long)ldo);
+    const Registered *reg = nullptr;
+    for (const Registered &r : c->registered)
+        if (r.local == out_full) reg = &r;
+    if (!reg) return mfail(VNM_ERR_BAD_ARG, "vnm_mgpu_spmm_gathered_p2p: out_full was not registered with vnm_mgpu_register_output");
+    if ((size_t)N_total * (size_t)M * 2 > reg->bytes) return mfail(VNM_ERR_BAD_ARG, "vnm_mgpu_spmm_gathered_p2p: the registered buffer is smaller than [N, M]");
+    const NcclApi *api = nccl();
+    if (!api) return mfail(VNM_ERR_UNSUPPORTED, "NCCL (libnccl.so.2) could not be loaded");
+    cudaStream_t s = (cudaStream_t)stream;
+    const int ns = N_total / W;
+    const size_t row0 = (size_t)c->rank * (size_t)ns * (size_t)ldo * 2;  // byte offset of this rank's rows in every buffer
+    void *outs[MAX_OUTS];
+    for (int i = 0; i < W; ++i) outs[i] = (char *)reg->peer[(c->rank + i) % W] + row0;  // own buffer first, then the peers in ring order
+    if (W > 1)
+        if (int rc = rank_barrier(c, api, s)) return rc;   // nobody still reads the previous contents of any buffer
+    int rc = vnm_spmm_f16_multi(h, B_shard, ldb, ns, bias, outs, W, ldo, VNM_LAYOUT_NM, s);
+    // the closing barrier is issued even after a failed launch: the other ranks are going to wait in theirs
+    if (W > 1) {
+        int rb = rank_barrier(c, api, s);                   // every rank's rows have landed everywhere
+        if (rc == VNM_OK) rc = rb;
     }
     return rc;
 }

@@ -129,6 +129,7 @@ extern "C" int vnm_spmm_f16_noalloc(const void *values, const uint32_t *meta, co
     if (r != CUDA_SUCCESS) return nfail(VNM_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
 
     SpmmParams p;
+    p.n_out = 1;
     p.am = (const uint8_t *)am;
     p.rows = (const int4 *)rows;
     p.bias = (const __half *)bias;

@@ -96,7 +96,7 @@ __device__ __forceinline__ void drain_slot(uint64_t *bar, uint32_t parity, int *
 
 template <int R>
 __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_kernel(const __grid_constant__ CUtensorMap tmap_tile, const __grid_constant__ CUtensorMap tmap_tile2,
-                                                                      const __grid_constant__ CUtensorMap tmap_out,
+                                                                      const __grid_constant__ CUtensorMap tmap_out, const __grid_constant__ OutMaps more_out,
                                                                       const SpmmParams p)
 {
     extern __shared__ uint8_t smem_raw[];
@@ -353,8 +353,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_kernel(const __gr
                     fence_proxy_async();
                     named_barrier_sync(1 + rt, 128);
                     if (leader && in_range) {
-                        if (p.layout == 0) tma_store_2d(&tmap_out, stg, n0 + part * PART, mt * TILE_M);
-                        else tma_store_2d(&tmap_out, stg, mt * TILE_M, n0 + part * PART);
+                        const int cx = p.layout == 0 ? n0 + part * PART : mt * TILE_M, cy = p.layout == 0 ? mt * TILE_M : n0 + part * PART;
+                        tma_store_2d(&tmap_out, stg, cx, cy);
+                        // further destinations of the same tile (the same rows of the peers' result buffers), one group with the first
+                        for (int d = 1; d < p.n_out; d++) tma_store_2d(&more_out.m[d - 1], stg, cx, cy);
                         bulk_commit_group();
                     }
                 };
@@ -446,13 +448,13 @@ void spmm_dense_b_config(int M, int N, int max_ctas, SpmmConfig *cfg)
     cfg->grid = (int)(tiles < sms ? tiles : sms);
 }
 
-cudaError_t launch_spmm_dense_b(const SpmmConfig &cfg, const CUtensorMap &tmap_tile, const CUtensorMap &tmap_tile2, const CUtensorMap &tmap_out,
+cudaError_t launch_spmm_dense_b(const SpmmConfig &cfg, const CUtensorMap &tmap_tile, const CUtensorMap &tmap_tile2, const CUtensorMap &tmap_out, const OutMaps &more_out,
                                 const SpmmParams &p, cudaStream_t stream)
 {
     if (cfg.nb == 1)
-        spmm_dense_b_kernel<1><<<(unsigned)cfg.grid, NUM_THREADS, SMEM_BYTES, stream>>>(tmap_tile, tmap_tile2, tmap_out, p);
+        spmm_dense_b_kernel<1><<<(unsigned)cfg.grid, NUM_THREADS, SMEM_BYTES, stream>>>(tmap_tile, tmap_tile2, tmap_out, more_out, p);
     else
-        spmm_dense_b_kernel<2><<<(unsigned)cfg.grid, NUM_THREADS, SMEM_BYTES, stream>>>(tmap_tile, tmap_tile2, tmap_out, p);
+        spmm_dense_b_kernel<2><<<(unsigned)cfg.grid, NUM_THREADS, SMEM_BYTES, stream>>>(tmap_tile, tmap_tile2, tmap_out, more_out, p);
     return cudaGetLastError();
 }
 

@@ -60,7 +60,7 @@ static_assert(SB % NBP == 0 && NBP <= 4, "B producers");
 constexpr int KT_RING = SB / STAGES_PER_KT;  // k-tiles the B ring holds
 static_assert(SB % STAGES_PER_KT == 0 && KT_RING == SA && KT_RING == META_SETS && SF == 2 * SB, "the rings and the metadata sets advance one k-tile at a time");
 static_assert(BN <= 240 && META_SETS == 3 && RT == 2 && BN % 16 == 0 && BN == 6 * PART, "tensor-memory column plan");
-static_assert((SA + SB + SF + SR + 2) * 8 + 16 <= BAR_BYTES, "barrier area too small");
+static_assert((SA + SB + SF + SR + 4) * 8 + 16 <= BAR_BYTES, "barrier area too small");
 constexpr int HALF_N = BN / 2;   // columns of a B stage held by each CTA of the pair
 
 __device__ __forceinline__ bool wait_one(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int *status, int code)
@@ -162,7 +162,8 @@ __device__ __forceinline__ bool wait_warp(uint64_t *bar, uint32_t parity, volati
 //   warps 8..15 epilogue of this CTA's two accumulators.
 template <int R>
 __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_pair_kernel(const __grid_constant__ CUtensorMap tmap_tile, const __grid_constant__ CUtensorMap tmap_tile2,
-                                                                           const __grid_constant__ CUtensorMap tmap_out, const SpmmParams p)
+                                                                           const __grid_constant__ CUtensorMap tmap_out, const __grid_constant__ OutMaps more_out,
+                                                                           const SpmmParams p)
 {
     static_assert(R == 1 || R == RT, "row tiles per CTA");  // R = 1: pair tiles of 256 x 240 for problems with few row tiles
     extern __shared__ uint8_t smem_raw[];
@@ -174,9 +175,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_pair_kernel(const
     uint64_t *b_full = a_full + SA;
     uint64_t *b_free = b_full + SB;   // b_free[j % SF]: the MMAs that read B stage j have completed (arrives in both CTAs)
     uint64_t *kready = b_free + SF;
-    uint64_t *acc_full_bar = kready + SR;
-    uint64_t *acc_empty_bar = acc_full_bar + 1;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty_bar + 1);
+    // accumulator hand-off.  R = 2: one barrier pair, both accumulators of a CTA belong to the same tile.  R = 1: a CTA has one
+    // row tile, so its two accumulators alternate between consecutive tiles (barrier pair ti & 1) and the epilogue of one
+    // tile runs beside the MMAs of the next.
+    uint64_t *acc_full_bar = kready + SR;      // [2]
+    uint64_t *acc_empty_bar = acc_full_bar + 2;  // [2]
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty_bar + 2);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5;
@@ -196,8 +200,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_pair_kernel(const
         for (int s = 0; s < SB; s++) mbar_init(&b_full[s], leader_cta ? 2 : 1);
         for (int s = 0; s < SF; s++) mbar_init(&b_free[s], 1);
         for (int s = 0; s < SR; s++) mbar_init(&kready[s], 2);  // metadata copied to tensor memory + all operands landed
-        mbar_init(acc_full_bar, 1);
-        mbar_init(acc_empty_bar, 2 * 4 * R);  // the epilogue warps of both CTAs
+        for (int a = 0; a < 2; a++) {
+            mbar_init(&acc_full_bar[a], 1);
+            mbar_init(&acc_empty_bar[a], 2 * 4);  // R = 1: the four warps of one epilogue group in both CTAs
+        }
+        if (R == 2) mbar_init(&acc_empty_bar[0], 2 * 4 * R);  // every epilogue warp of both CTAs
         *abort_flag = 0;
         fence_barrier_init();
     }
@@ -349,8 +356,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_pair_kernel(const
             tc_fence_after();
             for (int ti = 0; alive && ti < my_tiles; ++ti) {
                 for (int kt = 0; alive && kt < p.ktiles; ++kt, ++it) {
+                    // accumulator set of this tile: R = 2 always set 0 (phase ti), R = 1 set ti & 1 (phase ti / 2)
+                    const int aset = R == 1 ? (ti & 1) : 0;
+                    const uint32_t aphase = R == 1 ? (uint32_t)(ti >> 1) & 1u : (uint32_t)ti & 1u;
                     if (kt == 0) {
-                        if (!wait_one(acc_empty_bar, ((uint32_t)ti & 1u) ^ 1u, abort_flag, p.status, DEV_TIMEOUT_MMA)) { alive = false; break; }
+                        if (!wait_one(&acc_empty_bar[aset], aphase ^ 1u, abort_flag, p.status, DEV_TIMEOUT_MMA)) { alive = false; break; }
                         tc_fence_after();
                     }
                     const uint32_t mcol = tmem_base + meta_col(slot);
@@ -365,7 +375,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_pair_kernel(const
                         const uint32_t boff = boff0 + (((uint32_t)(kb / KB_PER_STAGE) * B_STAGE_BYTES + (uint32_t)(kb % KB_PER_STAGE) * kb_step) >> 4);
 #pragma unroll
                         for (int rt = 0; rt < R; rt++)
-                            tc_mma2_sp_f16(tmem_base + acc_col(rt), adesc0 + aoff + (uint32_t)((rt * AM_BLOCK_BYTES + kb * 32) >> 4), bdesc0 + boff,
+                            tc_mma2_sp_f16(tmem_base + acc_col(R == 1 ? aset : rt), adesc0 + aoff + (uint32_t)((rt * AM_BLOCK_BYTES + kb * 32) >> 4), bdesc0 + boff,
                                            mcol + rt * 4 + (uint32_t)(kb & ~1), idesc0 | (uint32_t)(kb & 1), (kt | kb) != 0 ? 1u : 0u);
                         if (kb % KB_PER_STAGE == KB_PER_STAGE - 1) {
                             // the stage (and, after the last, the A blocks and the metadata set) may be refilled in both CTAs
@@ -376,8 +386,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_pair_kernel(const
                     }
                     if (!alive) break;
                     if (kt == p.ktiles - 1) {
-                        tc_commit2(full_local);
-                        tc_commit2(full_peer);
+                        tc_commit2(full_local + (uint32_t)aset * 8u);
+                        tc_commit2(full_peer + (uint32_t)aset * 8u);
                     }
                     slot = slot + 1 == KT_RING ? 0 : slot + 1;
                 }
@@ -400,27 +410,29 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_pair_kernel(const
         const int q = warp & 3;
         const int i = q * 32 + lane;
         const int arow = mma_row_to_actual(i);
-        const uint32_t empty_leader = mapa_shared(smem_u32(acc_empty_bar), 0);
+        const int grp = (warp - EPI_WARP0) >> 2;  // R = 2: the accumulator (row tile) this group drains; R = 1: the tiles ti with ti & 1 == grp
+        const uint32_t empty_leader = mapa_shared(smem_u32(&acc_empty_bar[R == 1 ? grp : 0]), 0);
         int ti = 0;
-        // with one row tile per CTA the second group of four warps has no accumulator to drain
-        for (int tile = ((warp - EPI_WARP0) >> 2) < R ? pair : total_tiles; tile < total_tiles; tile += npairs, ++ti) {
+        for (int tile = pair; tile < total_tiles; tile += npairs, ++ti) {
+            if (R == 1 && (ti & 1) != grp) continue;
             int mq, nt;
             tile_coords(tile, mquads, p.ntiles, p.group_m, &mq, &nt);
             const int n0 = nt * BN;
             // the four warps of a group leave the loop together (they meet at named barriers below)
-            const bool got = wait_warp(acc_full_bar, (uint32_t)ti & 1u, abort_flag, p.status, DEV_TIMEOUT_EPILOGUE);
-            if (!named_barrier_and(1 + ((warp - EPI_WARP0) >> 2), 128, got)) break;
+            const bool got = wait_warp(&acc_full_bar[R == 1 ? grp : 0], R == 1 ? (uint32_t)(ti >> 1) & 1u : (uint32_t)ti & 1u, abort_flag, p.status,
+                                       DEV_TIMEOUT_EPILOGUE);
+            if (!named_barrier_and(1 + grp, 128, got)) break;
             tc_fence_after();
             {
-                const int rt = (warp - EPI_WARP0) >> 2;  // which accumulator this warp drains
+                const int rt = R == 1 ? 0 : grp;  // row tile of this CTA
                 const int mt = row_tile(mq, rt);
                 const int64_t row = (int64_t)mt * TILE_M + arow;
                 const bool row_ok = mt < p.mtiles && row < p.M;
                 const bool has_bias = p.layout == 1 && p.bias != nullptr;
                 const __half bias = (has_bias && row_ok) ? p.bias[row] : __ushort_as_half((unsigned short)0);
-                uint8_t *stg = out_ring + rt * OUT_STAGE_BYTES;
-                const bool leader = (warp == EPI_WARP0 + 4 * rt) && lane == 0;
-                const uint32_t trow = tmem_base + ((uint32_t)(q * 32) << 16) + acc_col(rt);
+                uint8_t *stg = out_ring + grp * OUT_STAGE_BYTES;
+                const bool leader = (warp == EPI_WARP0 + 4 * grp) && lane == 0;
+                const uint32_t trow = tmem_base + ((uint32_t)(q * 32) << 16) + acc_col(grp);
                 // 40 accumulator columns of this thread's row -> 20 registers of packed halves
                 auto drain = [&](int part, uint32_t *pk) {
                     uint32_t v0[32], v1[8];
@@ -442,7 +454,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_pair_kernel(const
                 auto store_part = [&](int part, const uint32_t *pk) {
                     const bool in_range = mt < p.mtiles && n0 + part * PART < p.N;
                     if (leader) bulk_wait_group_read0();  // the previous store has finished reading the staging buffer
-                    named_barrier_sync(1 + rt, 128);
+                    named_barrier_sync(1 + grp, 128);
                     if (p.layout == 0) {
 #pragma unroll
                         for (int c = 0; c < PART / 8; c++)
@@ -460,10 +472,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_pair_kernel(const
                         }
                     }
                     fence_proxy_async();
-                    named_barrier_sync(1 + rt, 128);
+                    named_barrier_sync(1 + grp, 128);
                     if (leader && in_range) {
-                        if (p.layout == 0) tma_store_2d(&tmap_out, stg, n0 + part * PART, mt * TILE_M);
-                        else tma_store_2d(&tmap_out, stg, mt * TILE_M, n0 + part * PART);
+                        const int cx = p.layout == 0 ? n0 + part * PART : mt * TILE_M, cy = p.layout == 0 ? mt * TILE_M : n0 + part * PART;
+                        tma_store_2d(&tmap_out, stg, cx, cy);
+                        // further destinations of the same tile (the same rows of the peers' result buffers), one group with the first
+                        for (int d = 1; d < p.n_out; d++) tma_store_2d(&more_out.m[d - 1], stg, cx, cy);
                         bulk_commit_group();
                     }
                 };
@@ -527,21 +541,28 @@ cudaError_t spmm_dense_b_pair_init()
 }
 
 // Pair tiles are 512 x 240 (two row tiles per CTA) or, where that would leave SM pairs without a tile, 256 x 240 (one
-// row tile per CTA: 34 KiB per CTA and k-tile).  Returns false when the pair kernel should not be used for this problem
+// row tile per CTA: 34 KiB per CTA and k-tile, two alternating accumulators).  Returns false when the pair kernel should not be used for this problem
 // (row tiles do not group evenly, too few tiles to occupy the clusters, or clusters unavailable): the caller then
 // launches the single-CTA kernel.
-bool spmm_dense_b_pair_config(int M, int N, int max_ctas, SpmmConfig *cfg)
+bool spmm_dense_b_pair_config(int M, int N, int K, int max_ctas, int force_rows, SpmmConfig *cfg)
 {
     if (g_pair_clusters <= 0) return false;
     const int mtiles = (M + TILE_M - 1) / TILE_M;
+    (void)K;
     const long long ntiles = (N + BN - 1) / BN;
     int clusters = g_pair_clusters;
     if (max_ctas > 0 && max_ctas / 2 < clusters) clusters = max_ctas / 2;
     if (clusters < 1) return false;
     const long long t2 = (long long)(mtiles / (2 * RT)) * ntiles, t1 = (long long)(mtiles / 2) * ntiles;
+    const bool ok2 = mtiles % (2 * RT) == 0 && t2 >= clusters;   // at least one full wave of 512-row tiles
+    const bool ok1 = mtiles % 2 == 0 && 4 * t1 >= 3 * clusters;   // most SM pairs get a 256-row tile
     int rt = 0;
-    if (mtiles % (2 * RT) == 0 && t2 >= clusters) rt = RT;          // at least one full wave of 512-row tiles
-    else if (mtiles % 2 == 0 && 4 * t1 >= 3 * clusters) rt = 1;      // most SM pairs get a 256-row tile
+    if (force_rows == 1 && ok1) rt = 1;
+    else if (force_rows == 2 && ok2) rt = RT;
+    // 512-row tiles read every B stage once per 512 rows and win wherever they fill the SM pairs (measured at K = 1024 .. 12288,
+    // although 256-row tiles alternate two accumulators and so run a tile's epilogue beside the next tile's MMAs)
+    else if (ok2) rt = RT;
+    else if (ok1) rt = 1;
     if (rt == 0) return false;
     const long long tiles = rt == RT ? t2 : t1;
     cfg->bn = BN;
@@ -553,7 +574,7 @@ bool spmm_dense_b_pair_config(int M, int N, int max_ctas, SpmmConfig *cfg)
     return true;
 }
 
-cudaError_t launch_spmm_dense_b_pair(const SpmmConfig &cfg, const CUtensorMap &tmap_tile, const CUtensorMap &tmap_tile2, const CUtensorMap &tmap_out,
+cudaError_t launch_spmm_dense_b_pair(const SpmmConfig &cfg, const CUtensorMap &tmap_tile, const CUtensorMap &tmap_tile2, const CUtensorMap &tmap_out, const OutMaps &more_out,
                                      const SpmmParams &p, cudaStream_t stream)
 {
     cudaLaunchConfig_t lc = {};
@@ -568,8 +589,8 @@ cudaError_t launch_spmm_dense_b_pair(const SpmmConfig &cfg, const CUtensorMap &t
     attr[0].val.clusterDim.z = 1;
     lc.attrs = attr;
     lc.numAttrs = 1;
-    if (cfg.nb == 2) return cudaLaunchKernelEx(&lc, spmm_dense_b_pair_kernel<1>, tmap_tile, tmap_tile2, tmap_out, p);
-    return cudaLaunchKernelEx(&lc, spmm_dense_b_pair_kernel<2>, tmap_tile, tmap_tile2, tmap_out, p);
+    if (cfg.nb == 2) return cudaLaunchKernelEx(&lc, spmm_dense_b_pair_kernel<1>, tmap_tile, tmap_tile2, tmap_out, more_out, p);
+    return cudaLaunchKernelEx(&lc, spmm_dense_b_pair_kernel<2>, tmap_tile, tmap_tile2, tmap_out, more_out, p);
 }
 
 }  // namespace vnm

@@ -71,6 +71,29 @@ class ShardedSpmm:
     ctx = None        # capi.Mgpu when the ranks run on GPUs
     prepared = None
 
+    def gathered_p2p(self, B_shard, N, out, bias=None):
+        """Replicated output [N, M] without an exchange step (GPUs only, dense-B operand form): `out` is registered on
+        first use (collective: every rank calls this with its own buffer of the same size at the same time), and the
+        product's epilogue stores this rank's rows to every rank's buffer -- vnm_mgpu_spmm_gathered_p2p.  Keep passing
+        the same `out`; release_outputs() (collective) unmaps it."""
+        if self.ctx is None:
+            raise RuntimeError("gathered_p2p needs the GPU launcher (capi.Mgpu)")
+        lo, hi = shard_bounds(N, self.world, self.rank)
+        if B_shard.shape[1] != hi - lo:
+            raise ValueError("B shard has %d columns, expected %d" % (B_shard.shape[1], hi - lo))
+        shared = self.__dict__.setdefault("_shared_outputs", {})
+        if out.data_ptr() not in shared:
+            self.ctx.register_output(out)
+            shared[out.data_ptr()] = out   # the tensor stays alive while peers may store into it
+        return self.ctx.spmm_gathered_p2p(self.prepared, B_shard, N, out, bias=bias)
+
+    def release_outputs(self):
+        """Collective: unmaps every buffer gathered_p2p registered."""
+        shared = self.__dict__.get("_shared_outputs", {})
+        for ptr in sorted(shared):
+            self.ctx.unregister_output(shared[ptr])
+        shared.clear()
+
     def gathered(self, B_shard, N, bias=None, chunks=4, out=None):
         """Replicated output [N, M]: every rank computes its rows and receives the rest.  The shard of rank r is rows
         shard_bounds(N, world, r) of the result.  On GPUs with equal shards this is vnm_mgpu_spmm_gathered: the shard
