@@ -244,128 +244,162 @@ __global__ void __launch_bounds__(256) compress_tiled_kernel(const __half *__res
 
 // ------------------------------------------------------------------------------------------------
 // Compressor, register form, for the common shapes: no mask, m in {4, 8, 16}, K % (4 * m) == 0 (whole tiles, no
-// padded group), V a multiple of 16 and 16-byte aligned rows.  One thread compresses one (row, tile) = four groups: it
-// loads its 4 * m halves with 16-byte loads straight into registers (no shared-memory staging: the tiled kernel spends
-// most of its instructions moving data in and out of shared memory), picks the four candidates of every group out of
-// those registers, and the 16 lanes that hold the 16 rows of a value strip transpose their four words among groups of
-// four lanes, so that every lane stores one 16-byte piece of the reference's value order.  A warp covers 16 rows x 2
-// tiles, a CTA one chunk = 16 rows x 16 tiles (1 KiB of every row for m = 8).  The grid is one resident wave; a CTA
-// walks chunks blockIdx.x, + gridDim.x, ... so that neighbouring CTAs read neighbouring pieces of the same rows, and
-// all index arithmetic that involves a division is per chunk (uniform over the CTA).  With PREFETCH the loads of the
-// next chunk are issued before the current one is worked on.
+// padded group), V a multiple of 16 and 16-byte aligned rows.  The lanes of a warp lie ALONG a row: a thread owns 16
+// bytes of the row or one group, whichever is larger (two groups for m = 4, one for m = 8 and 16), so a load instruction
+// of a warp reads 512 contiguous bytes (1 KiB for m = 16).  The thread walks the 16 rows of a value strip four at a
+// time: for its group the kept pairs of four consecutive rows are exactly one 16-byte piece of the reference's value
+// order [sub-block][group][row][slot], so it is stored straight from registers, without any exchange between lanes; the
+// candidates' select predicates depend on the column-loc entry only and are shared by the 16 rows.  The lanes of a tile
+// (4, or 2 for m = 4) OR their metadata nibbles together with shuffles and write the strip's 32 bytes of the tile's
+// metadata as one sector.  A CTA (8 warps) covers 16 rows x 4 KiB (8 KiB for m = 16); the grid is one resident wave
+// and walks the items in row-major order, so neighbouring CTAs read neighbouring pieces of the same rows.
 // ------------------------------------------------------------------------------------------------
-#ifndef VNM_COMPRESS_PREFETCH
-#define VNM_COMPRESS_PREFETCH 0
-#endif
-#ifndef VNM_COMPRESS_MINB
-#define VNM_COMPRESS_MINB 1
-#endif
-template <int M_, bool PREFETCH>
-__global__ void __launch_bounds__(256, VNM_COMPRESS_MINB) compress_direct_kernel(const __half *__restrict__ dense, int64_t ldd, const uint32_t *__restrict__ colloc,
-                                                              int V, int tiles, uint32_t tchunks, uint32_t chunks, uint32_t *__restrict__ values,
+// m = 8 fits 64 registers without spilling (four CTAs per SM: measured 11 % faster than three); m = 4 and 16 do not
+template <int M_>
+__global__ void __launch_bounds__(256, M_ == 8 ? 4 : 1) compress_direct_kernel(const __half *__restrict__ dense, int64_t ldd, const uint32_t *__restrict__ colloc,
+                                                              int V, int tiles, uint32_t spans, uint32_t items, uint32_t *__restrict__ values,
                                                               uint32_t *__restrict__ meta, unsigned long long *violations)
 {
-    constexpr int NW = M_ / 2;   // 32-bit words per group
-    const int lane = threadIdx.x & 31;
-    const int r16 = threadIdx.x & 15, tl = threadIdx.x >> 4;
+    constexpr int NW = M_ / 2;             // 32-bit words per group
+    constexpr int GPT = M_ == 4 ? 2 : 1;   // groups per thread
+    constexpr int TW = GPT * NW;           // words per thread and row (4, 4, 8)
+    constexpr int LPR = TW / 4;            // 16-byte loads per thread and row
+    constexpr int TL = 4 / GPT;            // lanes per tile
+    constexpr int TPW = 32 / TL;           // tiles per warp
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int tli = lane % TL, g0 = tli * GPT;   // this thread's first group inside its tile
     const int64_t Ksp = (int64_t)tiles * 8;
     unsigned int bad = 0;
-    uint32_t w[4 * NW], wn[PREFETCH ? 4 * NW : 1];
-    // (strip, tile) of this thread in chunk c; a thread past the last tile repeats the last one and stores nothing
-    auto locate = [&](uint32_t c, uint32_t *strip, int *T) {
-        *strip = c / tchunks;
-        const int t = (int)(c - *strip * tchunks) * 16 + tl;
-        *T = t < tiles ? t : tiles - 1;
-        return t < tiles;
+    // where the thread's 16 rows start for an item (lanes past the last tile repeat it: they take part in the shuffles)
+    auto row0_of = [&](uint32_t item) {
+        const uint32_t strip = item / spans;
+        const int t = (int)(item - strip * spans) * (8 * TPW) + warp * TPW + lane / TL;
+        const int T = t < tiles ? t : tiles - 1;
+        return dense + (int64_t)strip * 16 * ldd + ((int64_t)T * 4 + g0) * M_;
     };
-    auto load = [&](uint32_t c, uint32_t *dst) {
-        uint32_t strip;
-        int T;
-        locate(c, &strip, &T);
-        const uint4 *src = reinterpret_cast<const uint4 *>(dense + ((int64_t)strip * 16 + r16) * ldd + (int64_t)T * 4 * M_);
+    auto load4 = [&](const __half *row0, int sb, uint32_t (&w)[4][TW]) {   // rows 4*sb .. 4*sb+3
 #pragma unroll
-        for (int i = 0; i < NW; i++) {   // 4 * NW words = NW loads of 16 bytes
-            const uint4 v = __ldg(src + i);
-            dst[4 * i] = v.x; dst[4 * i + 1] = v.y; dst[4 * i + 2] = v.z; dst[4 * i + 3] = v.w;
-        }
-    };
-    if (PREFETCH && blockIdx.x < chunks) load(blockIdx.x, w);
-    for (uint32_t c = blockIdx.x; c < chunks; c += gridDim.x) {
-        uint32_t strip;
-        int T;
-        const bool valid = locate(c, &strip, &T);
-        const int r = (int)strip * 16 + r16;
-        const uint4 *c4p = reinterpret_cast<const uint4 *>(colloc + (int64_t)(strip * 16u / (uint32_t)V) * (Ksp / 2) * 4 + (int64_t)T * 16);
-        uint4 c4s[4];
+        for (int r = 0; r < 4; r++) {
+            const uint4 *src = reinterpret_cast<const uint4 *>(row0 + (int64_t)(sb * 4 + r) * ldd);
 #pragma unroll
-        for (int gi = 0; gi < 4; gi++) c4s[gi] = __ldg(c4p + gi);
-        if (PREFETCH) {
-            if (c + gridDim.x < chunks) load(c + gridDim.x, wn);
-        } else {
-            load(c, w);
-        }
-        uint32_t out[4];
-        uint32_t hw = 0;
-#pragma unroll
-        for (int gi = 0; gi < 4; gi++) {
-            const uint4 c4 = c4s[gi];
-            const uint32_t cand[4] = {c4.x, c4.y, c4.z, c4.w};
-            uint32_t o = 0;
-            int pos = 0;
-            if (max(max(c4.x, c4.y), max(c4.z, c4.w)) >= (uint32_t)M_) {
-                pos = 3;  // a column offset outside its group (corrupt column-loc): counted as a violation, nothing is picked
-            } else {
-#pragma unroll
-                for (int j = 0; j < 4; j++) {
-                    const uint32_t cc = cand[j];
-                    // half cc of the group's NW words: a binary select tree down to a pair of words, then one byte permute
-                    uint32_t lo, hi;
-                    if (NW == 2) {
-                        lo = w[gi * NW]; hi = w[gi * NW + 1];
-                    } else if (NW == 4) {
-                        const bool up = (cc & 4u) != 0;
-                        lo = up ? w[gi * NW + 2] : w[gi * NW];
-                        hi = up ? w[gi * NW + 3] : w[gi * NW + 1];
-                    } else {
-                        const bool up8 = (cc & 8u) != 0, up4 = (cc & 4u) != 0;
-                        const uint32_t a0 = up8 ? w[gi * NW + 4] : w[gi * NW], a1 = up8 ? w[gi * NW + 5] : w[gi * NW + 1];
-                        const uint32_t a2 = up8 ? w[gi * NW + 6] : w[gi * NW + 2], a3 = up8 ? w[gi * NW + 7] : w[gi * NW + 3];
-                        lo = up4 ? a2 : a0;
-                        hi = up4 ? a3 : a1;
-                    }
-                    const uint32_t h2 = (cc & 3u) * 2u;
-                    const uint32_t bits = __byte_perm(lo, hi, ((h2 + 1u) << 4) | h2) & 0xFFFFu;
-                    if ((bits & 0x7FFFu) != 0) {   // kept entries are the non-zero values
-                        if (pos < 2) {
-                            o |= bits << (16 * pos);
-                            hw |= (uint32_t)j << (gi * 4 + pos * 2);
-                        }
-                        pos++;
-                    }
-                }
+            for (int i = 0; i < LPR; i++) {
+                const uint4 v = __ldg(src + i);
+                w[r][4 * i] = v.x; w[r][4 * i + 1] = v.y; w[r][4 * i + 2] = v.z; w[r][4 * i + 3] = v.w;
             }
-            bad += (valid && pos != 2);
-            out[gi] = o;
         }
-        // 4 x 4 transpose among the four lanes that hold rows 4*sb .. 4*sb+3: lane qd ends with the words of group qd
-        const int qd = lane & 3;
+    };
+    // The loads run one step (four rows) ahead of the arithmetic, across item boundaries: two register buffers
+    uint32_t wa[4][TW], wb[4][TW];
+    const __half *row0 = blockIdx.x < items ? row0_of(blockIdx.x) : dense;
+    if (blockIdx.x < items) load4(row0, 0, wa);
+    for (uint32_t item = blockIdx.x; item < items; item += gridDim.x) {
+        const uint32_t strip = item / spans;
+        const int t = (int)(item - strip * spans) * (8 * TPW) + warp * TPW + lane / TL;
+        const bool valid = t < tiles;          // whole tiles: the lanes of a tile are valid together
+        const int T = valid ? t : tiles - 1;
+        const int64_t G = (int64_t)T * 4 + g0; // first group of this thread in its row
+        const __half *next_row0 = item + gridDim.x < items ? row0_of(item + gridDim.x) : row0;
+        // candidates of the thread's groups: the same for the 16 rows (V % 16 == 0)
+        uint32_t cand[GPT][4];
+        uint32_t okmask[GPT];   // 0 for a group whose column-loc entry is corrupt (an offset outside the group): every row counts a violation
         {
-            // exchange 2 x 2 blocks, then single words
-            const uint32_t s0 = (qd & 2) ? out[0] : out[2], s1 = (qd & 2) ? out[1] : out[3];
-            const uint32_t r0 = __shfl_xor_sync(0xffffffffu, s0, 2), r1 = __shfl_xor_sync(0xffffffffu, s1, 2);
-            if (qd & 2) { out[0] = r0; out[1] = r1; } else { out[2] = r0; out[3] = r1; }
-            const uint32_t t0 = (qd & 1) ? out[0] : out[1], t1 = (qd & 1) ? out[2] : out[3];
-            const uint32_t u0 = __shfl_xor_sync(0xffffffffu, t0, 1), u1 = __shfl_xor_sync(0xffffffffu, t1, 1);
-            if (qd & 1) { out[0] = u0; out[2] = u1; } else { out[1] = u0; out[3] = u1; }
-        }
-        // now out[k] of lane (sb, qd) = word of row 4*sb + k, group qd ... stored as [sub-block][group][row][slot]
-        uint4 *vdst = reinterpret_cast<uint4 *>(values + ((int64_t)strip * 16 * Ksp + (int64_t)T * 128) / 2) + (r16 >> 2) * 4 + qd;
-        if (valid) *vdst = make_uint4(out[0], out[1], out[2], out[3]);
-        const uint32_t other = __shfl_xor_sync(0xffffffffu, hw, 1);
-        if (valid && (r16 & 1) == 0) meta[(int64_t)(r / 32) * 16 * tiles + (int64_t)T * 16 + (r % 32) / 2] = hw | (other << 16);
-        if (PREFETCH) {
+            const uint4 *c4p = reinterpret_cast<const uint4 *>(colloc + ((int64_t)(strip * 16u / (uint32_t)V) * (Ksp / 2) + G) * 4);
 #pragma unroll
-            for (int i = 0; i < 4 * NW; i++) w[i] = wn[i];
+            for (int j = 0; j < GPT; j++) {
+                const uint4 c4 = __ldg(c4p + j);
+                const bool corrupt = max(max(c4.x, c4.y), max(c4.z, c4.w)) >= (uint32_t)M_;
+                okmask[j] = corrupt ? 0u : 0xFFFFFFFFu;
+                cand[j][0] = c4.x & okmask[j]; cand[j][1] = c4.y & okmask[j]; cand[j][2] = c4.z & okmask[j]; cand[j][3] = c4.w & okmask[j];
+            }
+        }
+        uint4 *vdst = reinterpret_cast<uint4 *>(values) + ((int64_t)strip * 16 * Ksp + (int64_t)T * 128) / 8 + g0;
+        uint32_t keep[4] = {0, 0, 0, 0};   // metadata words this lane stores at the end: 2 (TL = 4) or 4 (TL = 2)
+        auto work = [&](int sb, const uint32_t (&w)[4][TW]) {
+            uint32_t hw[4] = {0, 0, 0, 0};   // per row: the metadata nibbles of this thread's groups, at their place in the tile's 16 bits
+#pragma unroll
+            for (int j = 0; j < GPT; j++) {
+                uint32_t out[4];
+#pragma unroll
+                for (int r = 0; r < 4; r++) {
+                    const uint32_t *wg = &w[r][j * NW];
+                    uint32_t h[4];
+                    bool nz[4];
+#pragma unroll
+                    for (int c = 0; c < 4; c++) {
+                        const uint32_t cc = cand[j][c];
+                        // half cc of the group's NW words: a binary select tree down to a pair of words, then one byte permute
+                        uint32_t lo, hi;
+                        if (NW == 2) {
+                            lo = wg[0]; hi = wg[1];
+                        } else if (NW == 4) {
+                            const bool up = (cc & 4u) != 0;
+                            lo = up ? wg[2] : wg[0];
+                            hi = up ? wg[3] : wg[1];
+                        } else {
+                            const bool up8 = (cc & 8u) != 0, up4 = (cc & 4u) != 0;
+                            const uint32_t a0 = up8 ? wg[4] : wg[0], a1 = up8 ? wg[5] : wg[1];
+                            const uint32_t a2 = up8 ? wg[6] : wg[2], a3 = up8 ? wg[7] : wg[3];
+                            lo = up4 ? a2 : a0;
+                            hi = up4 ? a3 : a1;
+                        }
+                        const uint32_t h2 = (cc & 3u) * 2u;
+                        h[c] = __byte_perm(lo, hi, ((h2 + 1u) << 4) | h2);   // the half in the low 16 bits (the upper 16 are not used)
+                        nz[c] = (h[c] & 0x7FFFu) != 0;                                // kept entries are the non-zero values
+                    }
+                    // exactly two candidates are non-zero in a valid matrix: the first from the front and the first from the back
+                    const uint32_t v0 = nz[0] ? h[0] : (nz[1] ? h[1] : h[2]), i0 = nz[0] ? 0u : (nz[1] ? 1u : 2u);
+                    const uint32_t v1 = nz[3] ? h[3] : (nz[2] ? h[2] : h[1]), i1 = nz[3] ? 3u : (nz[2] ? 2u : 1u);
+                    const int cnt = (int)nz[0] + (int)nz[1] + (int)nz[2] + (int)nz[3];
+                    const bool good = cnt == 2 && okmask[j] != 0;
+                    bad += (valid && !good);
+                    // fewer than two kept entries leave zeros in the open slots, more than two keep the first two (as the scalar form does)
+                    uint32_t o, nib;
+                    if (cnt == 2) {
+                        o = __byte_perm(v0, v1, 0x5410u);   // low halves of both
+                        nib = i0 | (i1 << 2);
+                    } else {
+                        o = 0; nib = 0;
+                        int pos = 0;
+#pragma unroll
+                        for (int c = 0; c < 4; c++)
+                            if (nz[c]) {
+                                if (pos < 2) { o |= (h[c] & 0xFFFFu) << (16 * pos); nib |= (uint32_t)c << (pos * 2); }
+                                pos++;
+                            }
+                    }
+                    out[r] = o & okmask[j];
+                    hw[r] |= (nib & okmask[j]) << ((g0 + j) * 4);
+                }
+                // rows 4*sb .. 4*sb+3 of group g0 + j: one 16-byte piece of [sub-block][group][row][slot]
+                if (valid) vdst[sb * 4 + j] = make_uint4(out[0], out[1], out[2], out[3]);
+            }
+            // the tile's 16 metadata bits per row, two rows per word: OR over the lanes of the tile
+            uint32_t m01 = hw[0] | (hw[1] << 16), m23 = hw[2] | (hw[3] << 16);
+#pragma unroll
+            for (int o = 1; o < TL; o <<= 1) {
+                m01 |= __shfl_xor_sync(0xffffffffu, m01, o);
+                m23 |= __shfl_xor_sync(0xffffffffu, m23, o);
+            }
+            if (TL == 4) {
+                if (tli == sb) { keep[0] = m01; keep[1] = m23; }
+            } else {
+                if (tli == (sb >> 1)) { keep[(sb & 1) * 2] = m01; keep[(sb & 1) * 2 + 1] = m23; }
+            }
+        };
+        load4(row0, 1, wb);
+        work(0, wa);
+        load4(row0, 2, wa);
+        work(1, wb);
+        load4(row0, 3, wb);
+        work(2, wa);
+        load4(next_row0, 0, wa);   // the next item's first rows (the last item loads its own again: in bounds, unused)
+        work(3, wb);
+        row0 = next_row0;
+        // the strip's half of the tile's 16 metadata words (rows 16*(strip & 1) ..): 32 bytes, one sector per tile
+        uint32_t *mdst = meta + (int64_t)(strip >> 1) * 16 * tiles + (int64_t)T * 16 + (strip & 1u) * 8;
+        if (valid) {
+            if (TL == 4) *reinterpret_cast<uint2 *>(mdst + tli * 2) = make_uint2(keep[0], keep[1]);
+            else *reinterpret_cast<uint4 *>(mdst + tli * 4) = make_uint4(keep[0], keep[1], keep[2], keep[3]);
         }
     }
     if (violations != nullptr) {
@@ -384,7 +418,7 @@ static int compress_direct_wave()
     if (dev < 0 || dev >= 64) dev = 0;
     if (cached[dev] == 0) {
         int per_sm = 0, sms = 0;
-        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, compress_direct_kernel<M_, VNM_COMPRESS_PREFETCH != 0>, 256, 0);
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, compress_direct_kernel<M_>, 256, 0);
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         cached[dev] = (per_sm > 0 && sms > 0) ? per_sm * sms : 148 * 4;
     }
@@ -398,20 +432,21 @@ cudaError_t launch_compress(const void *dense, int64_t ldd, const int32_t *mask,
     const int threads = 256;
     // register form: no mask, whole tiles, 16-byte aligned rows and outputs
     if (!mask && (m == 4 || m == 8 || m == 16) && K % (4 * m) == 0 && Ksp == (int64_t)K / m * 2 && M % 16 == 0 && V % 16 == 0 && ldd % 8 == 0 &&
-        ((uintptr_t)dense & 15) == 0 && ((uintptr_t)values & 15) == 0 && ((uintptr_t)colloc & 15) == 0 &&
-        (int64_t)(M / 16) * ((Ksp / 8 + 15) / 16) < ((int64_t)1 << 31)) {
-        constexpr bool PF = VNM_COMPRESS_PREFETCH != 0;
+        ((uintptr_t)dense & 15) == 0 && ((uintptr_t)values & 15) == 0 && ((uintptr_t)colloc & 15) == 0 && ((uintptr_t)meta & 15) == 0) {
         const int tiles = (int)(Ksp / 8);
-        const uint32_t tchunks = (uint32_t)((tiles + 15) / 16), chunks = (uint32_t)(M / 16) * tchunks;
-        const int wave = m == 4 ? compress_direct_wave<4>() : m == 8 ? compress_direct_wave<8>() : compress_direct_wave<16>();
-        const unsigned blocks = chunks < (uint32_t)wave ? chunks : (unsigned)wave;
-        if (m == 4)
-            compress_direct_kernel<4, PF><<<blocks, threads, 0, stream>>>((const __half *)dense, ldd, colloc, V, tiles, tchunks, chunks, (uint32_t *)values, meta, violations);
-        else if (m == 8)
-            compress_direct_kernel<8, PF><<<blocks, threads, 0, stream>>>((const __half *)dense, ldd, colloc, V, tiles, tchunks, chunks, (uint32_t *)values, meta, violations);
-        else
-            compress_direct_kernel<16, PF><<<blocks, threads, 0, stream>>>((const __half *)dense, ldd, colloc, V, tiles, tchunks, chunks, (uint32_t *)values, meta, violations);
-        return cudaGetLastError();
+        const int tiles_per_item = m == 4 ? 8 * 16 : 8 * 8;   // 8 warps x tiles per warp
+        const int64_t spans = (tiles + tiles_per_item - 1) / tiles_per_item, items = (int64_t)(M / 16) * spans;
+        if (items < ((int64_t)1 << 31)) {
+            const int wave = m == 4 ? compress_direct_wave<4>() : m == 8 ? compress_direct_wave<8>() : compress_direct_wave<16>();
+            const unsigned blocks = items < wave ? (unsigned)items : (unsigned)wave;
+            if (m == 4)
+                compress_direct_kernel<4><<<blocks, threads, 0, stream>>>((const __half *)dense, ldd, colloc, V, tiles, (uint32_t)spans, (uint32_t)items, (uint32_t *)values, meta, violations);
+            else if (m == 8)
+                compress_direct_kernel<8><<<blocks, threads, 0, stream>>>((const __half *)dense, ldd, colloc, V, tiles, (uint32_t)spans, (uint32_t)items, (uint32_t *)values, meta, violations);
+            else
+                compress_direct_kernel<16><<<blocks, threads, 0, stream>>>((const __half *)dense, ldd, colloc, V, tiles, (uint32_t)spans, (uint32_t)items, (uint32_t *)values, meta, violations);
+            return cudaGetLastError();
+        }
     }
     const bool aligned = ldd % 4 == 0 && ((uintptr_t)dense & 7) == 0 && ((uintptr_t)mask & 7) == 0 && ((uintptr_t)meta & 15) == 0 &&
                          m <= 128 && M % 32 == 0 && V % 32 == 0;
