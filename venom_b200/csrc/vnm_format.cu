@@ -582,10 +582,119 @@ __global__ void __launch_bounds__(256) decompress_tiled_kernel(const uint32_t *_
     }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Decompressor, register form: the mirror image of compress_direct_kernel (used for m in {4, 8}, whole
+// tiles, V % 16 == 0, aligned rows).  Lanes lie along the row; a thread owns one group (two for m = 4) of the 16 rows of
+// a strip.  For four consecutive rows its kept pairs are one 16-byte piece of the value array and its metadata nibbles
+// sit in the tile's two metadata words of those rows; it rebuilds the m halves of the group in registers (zeros, slot 0,
+// then slot 1, so a padded slot overwrites as in the reference's loop order) and stores them with 16-byte stores: a
+// warp writes 512 contiguous bytes of a row (1 KiB for m = 16).  Every output element is written exactly once.
+// ------------------------------------------------------------------------------------------------
+template <int M_>
+__global__ void __launch_bounds__(256) decompress_direct_kernel(const uint32_t *__restrict__ values, const uint32_t *__restrict__ meta,
+                                                                const uint32_t *__restrict__ colloc, int V, int tiles, uint32_t spans,
+                                                                uint32_t items, __half *__restrict__ dense, int64_t ldd)
+{
+    constexpr int NW = M_ / 2;             // 32-bit words per group
+    constexpr int GPT = M_ == 4 ? 2 : 1;   // groups per thread
+    constexpr int TW = GPT * NW;           // words per thread and row
+    constexpr int TL = 4 / GPT;            // lanes per tile
+    constexpr int TPW = 32 / TL;           // tiles per warp
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g0 = (lane % TL) * GPT;
+    const int64_t Ksp = (int64_t)tiles * 8;
+    for (uint32_t item = blockIdx.x; item < items; item += gridDim.x) {
+        const uint32_t strip = item / spans;
+        const int T = (int)(item - strip * spans) * (8 * TPW) + warp * TPW + lane / TL;
+        if (T >= tiles) continue;   // no exchange between lanes: threads past the last tile have nothing to do
+        const int64_t G = (int64_t)T * 4 + g0;
+        // the candidates of a group as four bytes of one word: candidate `sel` is one byte permute away
+        uint32_t candpack[GPT];
+        {
+            const uint4 *c4p = reinterpret_cast<const uint4 *>(colloc + ((int64_t)(strip * 16u / (uint32_t)V) * (Ksp / 2) + G) * 4);
+#pragma unroll
+            for (int j = 0; j < GPT; j++) {
+                const uint4 c4 = __ldg(c4p + j);
+                candpack[j] = (c4.x & 0xFFu) | ((c4.y & 0xFFu) << 8) | ((c4.z & 0xFFu) << 16) | ((c4.w & 0xFFu) << 24);
+            }
+        }
+        const uint4 *vsrc = reinterpret_cast<const uint4 *>(values) + ((int64_t)strip * 16 * Ksp + (int64_t)T * 128) / 8 + g0;
+        const uint4 *msrc = reinterpret_cast<const uint4 *>(meta + (int64_t)(strip >> 1) * 16 * tiles + (int64_t)T * 16 + (strip & 1u) * 8);
+        uint4 vals[4][GPT];
+#pragma unroll
+        for (int sb = 0; sb < 4; sb++)
+#pragma unroll
+            for (int j = 0; j < GPT; j++) vals[sb][j] = __ldg(vsrc + sb * 4 + j);
+        const uint4 ma = __ldg(msrc), mb = __ldg(msrc + 1);
+        const uint32_t mw[8] = {ma.x, ma.y, ma.z, ma.w, mb.x, mb.y, mb.z, mb.w};   // word 2*sb + (r >> 1): rows r, r+1 of sub-block sb
+        __half *drow0 = dense + (int64_t)strip * 16 * ldd + G * M_;
+#pragma unroll
+        for (int sb = 0; sb < 4; sb++) {
+#pragma unroll
+            for (int r = 0; r < 4; r++) {
+                const uint32_t hw = mw[sb * 2 + (r >> 1)] >> ((r & 1) * 16);
+                uint32_t w[TW];
+#pragma unroll
+                for (int j = 0; j < GPT; j++) {
+                    const uint32_t two = r == 0 ? vals[sb][j].x : r == 1 ? vals[sb][j].y : r == 2 ? vals[sb][j].z : vals[sb][j].w;
+                    const uint32_t nib = hw >> ((g0 + j) * 4);
+                    const uint32_t p0 = __byte_perm(candpack[j], 0u, 0x4440u | (nib & 3u));          // column of slot 0 inside the group
+                    const uint32_t p1 = __byte_perm(candpack[j], 0u, 0x4440u | ((nib >> 2) & 3u));   // column of slot 1
+                    const uint32_t lo0 = two & 0xFFFFu, hi0 = two << 16;          // slot 0 as a low / high half
+                    const uint32_t lo1 = two >> 16, hi1 = two & 0xFFFF0000u;      // slot 1
+#pragma unroll
+                    for (int k = 0; k < NW; k++) {
+                        uint32_t x = 0;
+                        if ((p0 >> 1) == (uint32_t)k) x = (p0 & 1u) ? hi0 : lo0;
+                        if ((p1 >> 1) == (uint32_t)k) x = (p1 & 1u) ? ((x & 0xFFFFu) | hi1) : ((x & 0xFFFF0000u) | lo1);
+                        w[j * NW + k] = x;
+                    }
+                }
+                uint4 *dst = reinterpret_cast<uint4 *>(drow0 + (int64_t)(sb * 4 + r) * ldd);
+#pragma unroll
+                for (int i = 0; i < TW / 4; i++) dst[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+            }
+        }
+    }
+}
+
+template <int M_>
+static int decompress_direct_wave()
+{
+    static int cached[64] = {0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) dev = 0;
+    if (cached[dev] == 0) {
+        int per_sm = 0, sms = 0;
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decompress_direct_kernel<M_>, 256, 0);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        cached[dev] = (per_sm > 0 && sms > 0) ? per_sm * sms : 148 * 4;
+    }
+    return cached[dev];
+}
+
 cudaError_t launch_decompress(const void *values, const uint32_t *meta, const uint32_t *colloc, int M, int K, int V, int m,
                               void *dense, int64_t ldd, cudaStream_t stream)
 {
     const int64_t Ksp = ksp_of(K, m);
+    // register form: whole tiles, 16-byte aligned rows and arrays (m = 16 measured slower than the tiled kernel: a lane's
+    // 32 bytes per row leave through two strided 16-byte stores)
+    if ((m == 4 || m == 8) && K % (4 * m) == 0 && Ksp == (int64_t)K / m * 2 && M % 16 == 0 && V % 16 == 0 && ldd % 8 == 0 &&
+        ((uintptr_t)dense & 15) == 0 && ((uintptr_t)values & 15) == 0 && ((uintptr_t)colloc & 15) == 0 && ((uintptr_t)meta & 15) == 0) {
+        const int tiles = (int)(Ksp / 8);
+        const int tiles_per_item = m == 4 ? 8 * 16 : 8 * 8;   // 8 warps x tiles per warp
+        const int64_t spans = (tiles + tiles_per_item - 1) / tiles_per_item, items = (int64_t)(M / 16) * spans;
+        if (items < ((int64_t)1 << 31)) {
+            const int wave = m == 4 ? decompress_direct_wave<4>() : decompress_direct_wave<8>();
+            const unsigned blocks = items < wave ? (unsigned)items : (unsigned)wave;
+            if (m == 4)
+                decompress_direct_kernel<4><<<blocks, 256, 0, stream>>>((const uint32_t *)values, meta, colloc, V, tiles, (uint32_t)spans, (uint32_t)items, (__half *)dense, ldd);
+            else
+                decompress_direct_kernel<8><<<blocks, 256, 0, stream>>>((const uint32_t *)values, meta, colloc, V, tiles, (uint32_t)spans, (uint32_t)items, (__half *)dense, ldd);
+            return cudaGetLastError();
+        }
+    }
     const bool aligned = ldd % 4 == 0 && ((uintptr_t)dense & 7) == 0 && ((uintptr_t)values & 15) == 0 && ((uintptr_t)meta & 15) == 0 &&
                          m <= 128 && M % 32 == 0 && V % 32 == 0;
     if (aligned) {
