@@ -277,8 +277,9 @@ int vnm_mgpu_spmm_gathered(vnm_mgpu_t ctx, vnm_handle_t handle, const void *B_sh
  * the peers' over NVLink), so the transfer of a tile overlaps the MMAs of the next ones; a small ncclAllGather on
  * `stream` before the launch (nobody still reads last call's result) and after it (every rank's rows have landed)
  * orders the ranks.  Needs the operand in dense-B form, world <= VNM_MAX_OUTS, ldo == M, N_total % (8 x world) == 0;
- * VNM_ERR_UNSUPPORTED otherwise, and callers fall back to vnm_mgpu_spmm_gathered.  unregister is collective too
- * (it synchronises the device and the ranks before it unmaps). */
+ * VNM_ERR_UNSUPPORTED otherwise, and callers fall back to vnm_mgpu_spmm_gathered.  unregister is collective too: it
+ * synchronises the device and the ranks before it unmaps, and returns only after every rank has unmapped, so the
+ * buffer may be freed right after it. */
 int vnm_mgpu_register_output(vnm_mgpu_t ctx, void *out_full, size_t bytes);
 int vnm_mgpu_unregister_output(vnm_mgpu_t ctx, void *out_full);
 int vnm_mgpu_spmm_gathered_p2p(vnm_mgpu_t ctx, vnm_handle_t handle, const void *B_shard, int64_t ldb, int N_total,

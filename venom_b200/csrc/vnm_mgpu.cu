@@ -508,6 +508,9 @@ int vnm_mgpu_unregister_output(vnm_mgpu_t c, void *out_full)
     for (int r = 0; r < c->world; ++r)
         if (r != c->rank) release_mapping(c, r, c->registered[at].peer[r]);
     c->registered.erase(c->registered.begin() + (long)at);
+    // and nobody may free its buffer while a peer still has it mapped: return only after every rank has unmapped
+    if (int rc = rank_barrier(c, api, c->comm_stream)) return rc;
+    VNM_CU(cudaStreamSynchronize(c->comm_stream), "cudaStreamSynchronize");
     return VNM_OK;
 }
 
