@@ -94,11 +94,15 @@ class ShardedSpmm:
             self.ctx.unregister_output(shared[ptr])
         shared.clear()
 
-    def gathered(self, B_shard, N, bias=None, chunks=4, out=None):
+    def gathered(self, B_shard, N, bias=None, chunks=None, out=None):
         """Replicated output [N, M]: every rank computes its rows and receives the rest.  The shard of rank r is rows
         shard_bounds(N, world, r) of the result.  On GPUs with equal shards this is vnm_mgpu_spmm_gathered: the shard
         goes through in `chunks` column chunks, each exchanged while the next is multiplied (chunks=1: product, then
         one in-place all-gather)."""
+        if chunks is None:
+            # measured on NVSwitch: the chunked exchange pays up to 4 ranks; beyond that its world - 1 messages per chunk
+            # cost more than the overlap hides (8 ranks: 10.6 ms chunked against 9.6 ms plain)
+            chunks = 4 if self.world <= 4 else 1
         lo, hi = shard_bounds(N, self.world, self.rank)
         if self.ctx is not None and N % (8 * self.world) == 0:
             if B_shard.shape[1] != hi - lo:
