@@ -216,6 +216,10 @@ int vnm_set_producer_warps(vnm_handle_t handle, int warps);
  * fill the SM pairs, else one, whose two accumulators alternate between consecutive tiles).  Ablation switches; all
  * give identical bits. */
 int vnm_set_pair_mode(vnm_handle_t handle, int mode);
+/* Two-SM kernel: the producers also send L2-only prefetches (cp.async.bulk.prefetch) for the operands of the k-tile
+ * `ktiles_ahead` further on (0 .. 32; 0 = none), beyond the three k-tiles the shared-memory rings hold.  Never changes a
+ * result. */
+int vnm_set_l2_prefetch(vnm_handle_t handle, int ktiles_ahead);
 /* Caps the number of persistent CTAs (one per SM) the product of this handle launches; 0 = all SMs (default).  A caller
  * that runs something else beside the product (the multi-GPU launcher's all-gather, another stream's kernels) keeps SMs
  * free this way: a persistent CTA that has to wait for an SM would otherwise run after all the others.  No counterpart

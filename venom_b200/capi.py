@@ -68,6 +68,8 @@ def lib():
         L.vnm_set_gather_split.restype = C.c_int
         L.vnm_set_pair_mode.argtypes = [C.c_void_p, C.c_int]
         L.vnm_set_pair_mode.restype = C.c_int
+        L.vnm_set_l2_prefetch.argtypes = [C.c_void_p, C.c_int]
+        L.vnm_set_l2_prefetch.restype = C.c_int
         L.vnm_set_epilogue.argtypes = [C.c_void_p, C.c_int]
         L.vnm_set_epilogue.restype = C.c_int
         L.vnm_set_max_ctas.argtypes = [C.c_void_p, C.c_int]
@@ -300,6 +302,10 @@ class Prepared:
         """Dense-B form: 1 = two-SM (cta_group::2) kernel where it applies (default), 0 = single-SM kernel only,
         2 = pairs without L2 hints, 3 / 4 = pairs with one / two row tiles per CTA forced where the shape allows."""
         _check(lib().vnm_set_pair_mode(self._h, mode))
+
+    def set_l2_prefetch(self, ktiles_ahead):
+        """Two-SM kernel: L2-only prefetches this many k-tiles ahead of the loads into shared memory (0 = none)."""
+        _check(lib().vnm_set_l2_prefetch(self._h, ktiles_ahead))
 
     def set_epilogue(self, mode):
         """0 = staged 128-bit stores (default), 1 = 32-bit stores per thread (ablation; gather form, layout MN)."""

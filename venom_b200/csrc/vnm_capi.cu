@@ -153,6 +153,7 @@ struct vnm_prepared_s {
     int dense_b;       // 1: A re-expressed as 2:4 over all K columns, B read as plain tiles
     int out32;         // ablation: 32-bit epilogue stores (gather form, layout MN)
     int hybrid_rows;   // gather form: rows of every 64-row stage fetched by TMA gather4 beside the per-thread copies
+    int l2_ahead;      // pair kernel: k-tiles of L2 prefetch ahead of the shared-memory loads (0 = none)
     int pair_rows;     // pair kernel: 0 = row tiles per CTA chosen per problem, 1 / 2 = forced where possible (ablation)
     int l2_hints;      // pair kernel: 1 = ask L2 to keep the banded operand (default), 0 = no eviction-priority hints
     int pair_mode;     // dense-B form: 1 = use the two-SM (cta_group::2) kernel where it applies (default), 0 = never
@@ -331,6 +332,14 @@ int vnm_set_pair_mode(vnm_handle_t h, int mode)
     h->pair_mode = mode != 0;
     h->l2_hints = mode != 2;
     h->pair_rows = mode == 3 ? 1 : mode == 4 ? 2 : 0;
+    return VNM_OK;
+}
+
+int vnm_set_l2_prefetch(vnm_handle_t h, int ktiles_ahead)
+{
+    if (!h) return fail(VNM_ERR_BAD_ARG, "vnm_set_l2_prefetch: null handle");
+    if (ktiles_ahead < 0 || ktiles_ahead > 32) return fail(VNM_ERR_BAD_ARG, "vnm_set_l2_prefetch: 0 .. 32 k-tiles (got %d)", ktiles_ahead);
+    h->l2_ahead = ktiles_ahead;
     return VNM_OK;
 }
 
@@ -537,6 +546,7 @@ static int spmm_impl(vnm_handle_t h, const void *B, int64_t ldb, int N, int b_nk
     p.hybrid_rows = h->hybrid_rows;
     p.b_nk = b_nk;
     p.b_wide_ok = h->tm_wide ? 1 : 0;
+    p.l2_ahead = h->l2_ahead;
     p.n_out = 1;
     if (h->dense_b) {
         // The result leaves through TMA stores: [M,N] as boxes of 40 columns x 128 rows, [N,M] as boxes of 128

@@ -163,6 +163,19 @@ __device__ __forceinline__ void tma_load_4d_hint(void *smem_dst, const void *tma
                  "l"(tmap), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(smem_u32(bar)), "l"(policy)
                  : "memory");
 }
+// Prefetches into L2 only (no shared-memory destination, no barrier): a contiguous range, or the box of a tiled load.
+__device__ __forceinline__ void bulk_prefetch_l2(const void *gsrc, uint32_t bytes)
+{
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(gsrc), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_2d(const void *tmap, int col, int row)
+{
+    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(tmap), "r"(col), "r"(row) : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_4d(const void *tmap, int c0, int c1, int c2, int c3)
+{
+    asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.tile [%0, {%1, %2, %3, %4}];" ::"l"(tmap), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
 // TMA gather: four rows (r.x..r.w) of a 2-D tensor, `col` = first element of the inner box.
 __device__ __forceinline__ void tma_gather4(void *smem_dst, const void *tmap, int col, int4 r, uint64_t *bar)
 {

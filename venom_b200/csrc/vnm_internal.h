@@ -36,6 +36,7 @@ struct SpmmParams {
     int out32;            // gather kernel, layout MN: 32-bit stores from registers instead of staged 128-bit stores (ablation)
     int b_nk;             // dense-B kernel only: the dense operand is given as [N, K] row-major (K contiguous)
     int b_wide_ok;        // dense-B kernel only: the 4-D tensor map exists (column tiles with 256 columns inside N use one box per stage)
+    int l2_ahead;         // pair kernel: k-tiles by which L2 prefetches run ahead of the loads into shared memory (0 = none)
     int n_out;            // dense-B kernels: destinations of every output tile (1 = `out` only; more: the OutMaps argument, e.g. peers' buffers)
 };
 

@@ -130,6 +130,7 @@ extern "C" int vnm_spmm_f16_noalloc(const void *values, const uint32_t *meta, co
 
     SpmmParams p;
     p.n_out = 1;
+    p.l2_ahead = 0;
     p.am = (const uint8_t *)am;
     p.rows = (const int4 *)rows;
     p.bias = (const __half *)bias;

@@ -243,6 +243,23 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_pair_kernel(const
                         bulk_g2s_hint(a_ring + s * A_STAGE_BYTES + rt * AM_BLOCK_BYTES, p.am + ((size_t)mt * p.ktiles + kt) * AM_BLOCK_BYTES, AM_BLOCK_BYTES,
                                       &a_full[s], p.hint_a);
                     }
+                    if (p.l2_ahead > 0) {
+                        // the same blocks of a later k-tile (of this tile, or of the next one of this pair) on their way into L2
+                        int kp = kt + p.l2_ahead, mqp = mq;
+                        bool ok = true;
+                        if (kp >= p.ktiles) {
+                            kp -= p.ktiles;
+                            ok = kp < p.ktiles && tile + npairs < total_tiles;
+                            if (ok) tile_coords(tile + npairs, mquads, p.ntiles, p.group_m, &mqp, &nt_unused);
+                        }
+                        if (ok) {
+#pragma unroll
+                            for (int rt = 0; rt < R; rt++) {
+                                const int mt = row_tile(mqp, rt) < p.mtiles ? row_tile(mqp, rt) : p.mtiles - 1;
+                                bulk_prefetch_l2(p.am + ((size_t)mt * p.ktiles + kp) * AM_BLOCK_BYTES, AM_BLOCK_BYTES);
+                            }
+                        }
+                    }
                 }
             }
             if (*abort_flag) {
@@ -285,6 +302,25 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_pair_kernel(const
                     tma_load_4d_hint(dst, &tmap_tile, 0, jl * 64, 0, n0 / 8, &b_full[s], p.hint_b);  // {64 columns, 64 rows, 2 slices} from column n0
                 } else {  // ragged right edge: two boxes that clip (and zero-fill) at N
                     for (int c = 0; c < 2; c++) tma_load_2d_hint(dst + c * B_CHUNK_BYTES, &tmap_tile2, n0 + c * 64, jl * 64, &b_full[s], p.hint_b);
+                }
+                if (p.l2_ahead > 0) {
+                    // this warp's stage a few of its own turns later, on its way into L2
+                    int jlp = jl + NBP * ((STAGES_PER_KT * p.l2_ahead + NBP - 1) / NBP), n0p = n0;
+                    bool ok = true;
+                    if (jlp >= per_tile) {
+                        jlp -= per_tile;
+                        ok = jlp < per_tile && tile + npairs < total_tiles;
+                        if (ok) {
+                            int ntp;
+                            tile_coords(tile + npairs, mquads, p.ntiles, p.group_m, &mq_unused, &ntp);
+                            n0p = ntp * BN + (int)crank * HALF_N;
+                        }
+                    }
+                    if (ok) {
+                        if (p.b_nk) tma_prefetch_2d(&tmap_tile, jlp * 64, n0p);
+                        else if (p.b_wide_ok && n0p + 128 <= p.N) tma_prefetch_4d(&tmap_tile, 0, jlp * 64, 0, n0p / 8);
+                        else for (int c = 0; c < 2; c++) tma_prefetch_2d(&tmap_tile2, n0p + c * 64, jlp * 64);
+                    }
                 }
                 jl += NBP;
                 while (jl >= per_tile) { jl -= per_tile; ++tile_i; }
