@@ -216,6 +216,9 @@ int vnm_set_producer_warps(vnm_handle_t handle, int warps);
  * fill the SM pairs, else one, whose two accumulators alternate between consecutive tiles).  Ablation switches; all
  * give identical bits. */
 int vnm_set_pair_mode(vnm_handle_t handle, int mode);
+/* Host-buffer entry points: number of equal column slices of the upload / product / download pipeline (1 .. 32; slices
+ * are multiples of 256 columns and at least 1024 wide; 0 = the default, 8). */
+int vnm_set_host_slices(vnm_handle_t handle, int slices);
 /* Two-SM kernel: the producers also send L2-only prefetches (cp.async.bulk.prefetch) for the operands of the k-tile
  * `ktiles_ahead` further on (0 .. 32; 0 = none), beyond the three k-tiles the shared-memory rings hold.  Never changes a
  * result. */

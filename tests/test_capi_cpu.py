@@ -56,7 +56,7 @@ def test_cpu_tensors_are_rejected():
 def test_handle_setters_and_launcher_entry_points_reject_bad_arguments_without_a_gpu(lib):
     """Every switch and every vnm_mgpu_* entry point checks its arguments before touching CUDA or NCCL."""
     import ctypes as C
-    for name in ("vnm_set_gather_mode", "vnm_set_gather_split", "vnm_set_pair_mode", "vnm_set_l2_prefetch", "vnm_set_epilogue", "vnm_set_max_ctas",
+    for name in ("vnm_set_gather_mode", "vnm_set_gather_split", "vnm_set_pair_mode", "vnm_set_l2_prefetch", "vnm_set_host_slices", "vnm_set_epilogue", "vnm_set_max_ctas",
                  "vnm_set_producer_warps"):
         fn = getattr(lib, name)
         fn.argtypes = [C.c_void_p, C.c_int]

@@ -69,6 +69,8 @@ def lib():
         L.vnm_set_pair_mode.argtypes = [C.c_void_p, C.c_int]
         L.vnm_set_pair_mode.restype = C.c_int
         L.vnm_set_l2_prefetch.argtypes = [C.c_void_p, C.c_int]
+        L.vnm_set_host_slices.argtypes = [C.c_void_p, C.c_int]
+        L.vnm_set_host_slices.restype = C.c_int
         L.vnm_set_l2_prefetch.restype = C.c_int
         L.vnm_set_epilogue.argtypes = [C.c_void_p, C.c_int]
         L.vnm_set_epilogue.restype = C.c_int
@@ -302,6 +304,10 @@ class Prepared:
         """Dense-B form: 1 = two-SM (cta_group::2) kernel where it applies (default), 0 = single-SM kernel only,
         2 = pairs without L2 hints, 3 / 4 = pairs with one / two row tiles per CTA forced where the shape allows."""
         _check(lib().vnm_set_pair_mode(self._h, mode))
+
+    def set_host_slices(self, slices):
+        """Equal column slices of the host-buffer pipeline (spmm_host): 1 .. 32; 0 = the default (8)."""
+        _check(lib().vnm_set_host_slices(self._h, slices))
 
     def set_l2_prefetch(self, ktiles_ahead):
         """Two-SM kernel: L2-only prefetches this many k-tiles ahead of the loads into shared memory (0 = none)."""

@@ -118,7 +118,7 @@ bool choose_dense_b(int K, int V, int m, int strategy)
 
 }  // namespace
 
-constexpr int HOST_CHUNKS_MAX = 8;
+constexpr int HOST_CHUNKS_MAX = 32;   // upper bound of vnm_set_host_slices
 
 struct vnm_prepared_s {
     int M, K, V, n, m;
@@ -149,6 +149,7 @@ struct vnm_prepared_s {
     cudaStream_t copy_in, copy_out;   // host-buffer entry point: the device's two copy streams (shared by all handles)
     cudaEvent_t ev[2 * HOST_CHUNKS_MAX + 2];
     bool host_pipe_ready;
+    int host_slices;   // column slices of the host-buffer pipeline (vnm_set_host_slices)
     int gather_mode;
     int dense_b;       // 1: A re-expressed as 2:4 over all K columns, B read as plain tiles
     int out32;         // ablation: 32-bit epilogue stores (gather form, layout MN)
@@ -332,6 +333,14 @@ int vnm_set_pair_mode(vnm_handle_t h, int mode)
     h->pair_mode = mode != 0;
     h->l2_hints = mode != 2;
     h->pair_rows = mode == 3 ? 1 : mode == 4 ? 2 : 0;
+    return VNM_OK;
+}
+
+int vnm_set_host_slices(vnm_handle_t h, int slices)
+{
+    if (!h) return fail(VNM_ERR_BAD_ARG, "vnm_set_host_slices: null handle");
+    if (slices < 0 || slices > HOST_CHUNKS_MAX) return fail(VNM_ERR_BAD_ARG, "vnm_set_host_slices: 0 .. %d slices (got %d)", HOST_CHUNKS_MAX, slices);
+    h->host_slices = slices;
     return VNM_OK;
 }
 
@@ -642,13 +651,20 @@ static int spmm_host_impl(vnm_handle_t h, const void *B_host, int N, const void 
         for (cudaEvent_t &e : h->ev) VNM_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming), "cudaEventCreate");
         h->host_pipe_ready = true;
     }
-    // The columns are cut into up to HOST_CHUNKS_MAX slices of a multiple of 256 columns.  Slice c+1 goes up
-    // (copy engine 1) while slice c is multiplied and slice c-1 comes down (copy engine 2), so the call costs
-    // about the larger of the two transfers instead of their sum.  On the device every slice is its own
-    // compact matrix, [K, nc] in and [M, nc] or [nc, M] out.
-    int nc = ((N + HOST_CHUNKS_MAX - 1) / HOST_CHUNKS_MAX + 255) / 256 * 256;
-    if (nc < 1024) nc = 1024;
-    const int chunks = (N + nc - 1) / nc;
+    // The columns are cut into slices of a multiple of 256 columns.  Slice c+1 goes up (copy engine 1) while slice c is
+    // multiplied and slice c-1 comes down (copy engine 2), so the call costs about the larger of the two transfers
+    // instead of their sum.  On the device every slice is its own compact matrix, [K, w] in and [M, w] or [w, M] out.
+    // Equal slices, eight by default (vnm_set_host_slices).  Measured on cfg4: a schedule of growing slices (short head, long
+    // rows for the later 2-D copies) changes nothing; the [M, N] result costs 70-72 ms with 4-16 slices against 60-63 ms
+    // for the [N, M] result, whose slices come down as plain 1-D copies.
+    int widths[HOST_CHUNKS_MAX];
+    int chunks = 0;
+    {
+        const int slices = h->host_slices > 0 ? h->host_slices : 8;
+        int nc = ((N + slices - 1) / slices + 255) / 256 * 256;
+        if (nc < 1024) nc = 1024;
+        for (int n0 = 0; n0 < N; n0 += nc) widths[chunks++] = N - n0 < nc ? N - n0 : nc;
+    }
     cudaEvent_t ev_start = h->ev[2 * HOST_CHUNKS_MAX], ev_done = h->ev[2 * HOST_CHUNKS_MAX + 1];
     VNM_CUDA(cudaEventRecord(ev_start, s), "event record");
     VNM_CUDA(cudaStreamWaitEvent(h->copy_in, ev_start, 0), "stream wait");
@@ -657,8 +673,8 @@ static int spmm_host_impl(vnm_handle_t h, const void *B_host, int N, const void 
         if (!h->stage_bias) VNM_CUDA(cudaMalloc(&h->stage_bias, (size_t)h->M * 2), "bias cudaMalloc");
         VNM_CUDA(cudaMemcpyAsync(h->stage_bias, bias_host, (size_t)h->M * 2, cudaMemcpyHostToDevice, h->copy_in), "H2D copy of bias");
     }
-    for (int c = 0; c < chunks; ++c) {
-        const int n0 = c * nc, w = N - n0 < nc ? N - n0 : nc;
+    for (int c = 0, n0 = 0; c < chunks; n0 += widths[c], ++c) {
+        const int w = widths[c];
         uint8_t *dB = (uint8_t *)h->stage_B + (size_t)h->K * n0 * 2;
         uint8_t *dO = (uint8_t *)h->stage_out + (size_t)h->M * n0 * 2;
         VNM_CUDA(cudaMemcpy2DAsync(dB, (size_t)w * 2, (const uint8_t *)B_host + (size_t)n0 * 2, (size_t)N * 2, (size_t)w * 2, h->K,
