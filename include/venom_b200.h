@@ -107,7 +107,8 @@ int vnm_spmm_f16(vnm_handle_t handle, const void *B, int64_t ldb, int N,
 /* The same product stored to n_outs buffers of one geometry (1 <= n_outs <= VNM_MAX_OUTS; same ldo, layout and
  * alignment rules as `out` above): every output tile leaves shared memory through one TMA store per destination, so
  * the operands are read and multiplied once.  The destinations may be peer-mapped buffers of other GPUs -- this is the
- * store side of vnm_mgpu_spmm_gathered_p2p.  Only for operands held in dense-B form (VNM_ERR_UNSUPPORTED otherwise). */
+ * store side of vnm_mgpu_spmm_gathered_p2p.  Operands held in dense-B form: both layouts; in gather form: layout NM with
+ * ldo % 8 == 0 and 16-byte aligned buffers (the epilogue that leaves through TMA stores); VNM_ERR_UNSUPPORTED otherwise. */
 #define VNM_MAX_OUTS 8
 int vnm_spmm_f16_multi(vnm_handle_t handle, const void *B, int64_t ldb, int N, const void *bias,
                        void *const *outs, int n_outs, int64_t ldo, int layout, void *stream);
@@ -189,10 +190,13 @@ int vnm_set_gather_mode(vnm_handle_t handle, int mode);
 /* Gather mode 3 only: of the 64 gathered rows of every stage, `tma_rows` (0, 16, 32 or 48) are fetched by TMA
  * tile::gather4 and the others by the per-thread copies, so that both paths into the SM are busy at once. */
 int vnm_set_gather_split(vnm_handle_t handle, int tma_rows);
-/* Epilogue of the V:N:M (gather) form for layout MN: 0 = results staged in shared memory and stored as full 128-bit
- * sectors (default); 1 = every thread stores its own row in 32-bit words, the reference's OUT_32B experiment
- * (include/spatha/block_sparse/common/epilogue.h:34-61, blockwise_kernel.h:911-943).  VNM_ERR_UNSUPPORTED for operands
- * held in dense-B form, whose epilogue leaves through TMA stores. */
+/* Epilogue of the V:N:M (gather) form.  0 (default): layout MN staged in shared memory and stored as full 128-bit
+ * sectors; layout NM as fp16 stores from registers (several destinations -- vnm_spmm_f16_multi -- staged as [n][m] and
+ * stored with TMA, boxes of 128 m x 32 n).  1 = layout MN: every thread stores its own row in 32-bit words, the
+ * reference's OUT_32B experiment (include/spatha/block_sparse/common/epilogue.h:34-61, blockwise_kernel.h:911-943).
+ * 2 = layout NM through TMA stores also for a single destination, where ldo % 8 == 0 and out is 16-byte aligned
+ * (ablation: measured 1-4 % slower).  All give identical bits.  VNM_ERR_UNSUPPORTED for operands held in dense-B form,
+ * whose epilogue always leaves through TMA stores. */
 int vnm_set_epilogue(vnm_handle_t handle, int mode);
 
 /* How vnm_prepare lays the sparse operand out for the kernel (process-wide, applies to later calls):
@@ -283,7 +287,7 @@ int vnm_mgpu_spmm_gathered(vnm_mgpu_t ctx, vnm_handle_t handle, const void *B_sh
  * whose epilogue stores every output tile of this rank's rows to the same rows of all `world` buffers (its own first,
  * the peers' over NVLink), so the transfer of a tile overlaps the MMAs of the next ones; a small ncclAllGather on
  * `stream` before the launch (nobody still reads last call's result) and after it (every rank's rows have landed)
- * orders the ranks.  Needs the operand in dense-B form, world <= VNM_MAX_OUTS, ldo == M, N_total % (8 x world) == 0;
+ * orders the ranks.  Needs world <= VNM_MAX_OUTS, ldo == M with M % 8 == 0, N_total % (8 x world) == 0;
  * VNM_ERR_UNSUPPORTED otherwise, and callers fall back to vnm_mgpu_spmm_gathered.  unregister is collective too: it
  * synchronises the device and the ranks before it unmaps, and returns only after every rank has unmapped, so the
  * buffer may be freed right after it. */

@@ -199,6 +199,41 @@ def test_product_stored_to_several_destinations(capi, shape):
                 assert bool((buf[:8] == 7.0).all()) and bool((buf[8 + rows:] == 7.0).all())
     with pytest.raises(capi.VenomError):
         prep.spmm_multi(B, [torch.empty_like(want)] * 9, layout=capi.VNM_LAYOUT_NM)
+    # gather form: several destinations only where its epilogue leaves through TMA stores, i.e. layout NM
     gather = capi.Prepared(values, meta, colloc, M, K, V, m, strategy=capi.STRATEGY_GATHER)
     with pytest.raises(capi.VenomError):
         gather.spmm_multi(B, [torch.empty((M, N), dtype=torch.float16, device="cuda")] * 2)
+    want = gather.spmm(B, bias=bias, layout=capi.VNM_LAYOUT_NM)
+    bufs = [torch.full((N + 16, M), 7.0, dtype=torch.float16, device="cuda") for _ in range(3)]
+    outs = [buf[8:8 + N] for buf in bufs]
+    gather.spmm_multi(B, outs, bias=bias, layout=capi.VNM_LAYOUT_NM)
+    assert gather.device_status() == 0
+    for buf, o in zip(bufs, outs):
+        assert torch.equal(o, want)
+        assert bool((buf[:8] == 7.0).all()) and bool((buf[8 + N:] == 7.0).all())
+
+
+@pytest.mark.parametrize("shape", [(1024, 1024, 128, 16, 16384), (192, 512, 64, 32, 1000), (96, 256, 32, 8, 4104), (4096, 1024, 64, 32, 8200),
+                                   (256, 2048, 128, 8, 72)], ids=lambda p: "%dx%d_V%d_2:%d_N%d" % p)
+def test_gather_form_nm_epilogues_give_identical_bits(capi, oracle, shape):
+    """[N,M] + bias from the gather kernel: through shared memory and TMA stores (`set_epilogue(2)`; what a product with
+    several destinations uses) against fp16 stores from registers (default), bit for bit, with ragged N, a last row tile that is partly outside M, one to four vector
+    blocks per tile, and against the CPU oracle; a leading dimension that TMA cannot take falls back to register stores."""
+    import torch
+    M, K, V, m, N = shape
+    dense, colloc, values, meta, B = _operands(capi, M, K, V, m, N, seed=M + 3 * K + N)
+    prep = capi.Prepared(values, meta, colloc, M, K, V, m, strategy=capi.STRATEGY_GATHER)
+    bias = (torch.rand(M, device="cuda") - 0.5).half()
+    regs = prep.spmm(B, bias=bias, layout=capi.VNM_LAYOUT_NM)
+    assert prep.device_status() == 0
+    prep.set_epilogue(2)
+    canvas = torch.full((N + 2, M), 3.0, dtype=torch.float16, device="cuda")
+    tma = prep.spmm(B, bias=bias, layout=capi.VNM_LAYOUT_NM, out=canvas[1:N + 1])
+    assert prep.device_status() == 0
+    assert bool((canvas[0] == 3.0).all()) and bool((canvas[N + 1] == 3.0).all())
+    assert torch.equal(tma, regs)
+    _check_rows(oracle, tma, 1, values, meta, colloc, M, K, V, m, B, bias=bias, nrows=32)
+    # ldo = M + 4 is not a multiple of 8: the same request silently takes the register path
+    wide = torch.zeros((N, M + 4), dtype=torch.float16, device="cuda")
+    prep.spmm(B, bias=bias, layout=capi.VNM_LAYOUT_NM, out=wide[:, :M])
+    assert torch.equal(wide[:, :M], regs) and bool((wide[:, M:] == 0).all())

@@ -28,49 +28,52 @@ def _worker(rank, world, port, q):
         from oracle.oracle import Oracle
         from venom_b200.sharded import ShardedSpmm, shard_bounds
         from venom_b200.synth import random_dense_b, random_vnm_dense
-        M, K, V, m, N = 256, 1024, 128, 8, 4096
-        dense, cols, _ = random_vnm_dense(M, K, V, m, seed=1)
-        B = random_dense_b(K, N, seed=2)
-        orc = Oracle()
-        ov, om, _ = orc.compress(dense, cols, V, m)
-        if rank == 0:
-            args = (torch.from_numpy(ov), torch.from_numpy(om.view(np.int32)), torch.from_numpy(cols.view(np.int32)))
-        else:
-            args = (None, None, None)
-        op = ShardedSpmm.from_reference_arrays(*args, M, K, V, m)
-        lo, hi = shard_bounds(N, world, rank)
-        want = orc.spmm(ov, om, cols, M, K, V, m, B, layout=1)
-        Bs = torch.from_numpy(B[:, lo:hi].copy()).cuda()
-        bad_total, worst = 0, 0.0
-        assert op.ctx is not None                      # the library's own communicator (vnm_mgpu_create)
-        for chunks in (1, 4):                          # product then all-gather; chunked exchange beside the product
-            full = op.gathered(Bs, N, chunks=chunks)
-            torch.cuda.synchronize()
-            bad, _, w = orc.check(full.cpu().numpy(), want, mode=1, tol=1e-2)
-            bad_total += bad
-            worst = max(worst, w)
-        # peer-store form: the epilogue writes this rank's rows into both ranks' registered buffers; no exchange step.
-        # Same kernel and operands as the NCCL forms, so the bits must agree.  Two calls: the second overwrites the first.
-        p2p = "ok"
-        shared = torch.zeros((N, M), dtype=torch.float16, device="cuda")
-        try:
-            for _ in range(2):
-                got = op.gathered_p2p(Bs, N, shared)
+        bad_total, worst, p2p = 0, 0.0, "ok"
+        for m in (8, 16):                              # 2:8 is held in dense-B form, 2:16 in gather form
+            M, K, V, N = 256, 1024, 128, 4096
+            dense, cols, _ = random_vnm_dense(M, K, V, m, seed=1)
+            B = random_dense_b(K, N, seed=2)
+            orc = Oracle()
+            ov, om, _ = orc.compress(dense, cols, V, m)
+            if rank == 0:
+                args = (torch.from_numpy(ov), torch.from_numpy(om.view(np.int32)), torch.from_numpy(cols.view(np.int32)))
+            else:
+                args = (None, None, None)
+            op = ShardedSpmm.from_reference_arrays(*args, M, K, V, m)
+            lo, hi = shard_bounds(N, world, rank)
+            want = orc.spmm(ov, om, cols, M, K, V, m, B, layout=1)
+            Bs = torch.from_numpy(B[:, lo:hi].copy()).cuda()
+            assert op.ctx is not None                      # the library's own communicator (vnm_mgpu_create)
+            for chunks in (1, 4):                          # product then all-gather; chunked exchange beside the product
+                full = op.gathered(Bs, N, chunks=chunks)
                 torch.cuda.synchronize()
-                bad, _, w = orc.check(got.cpu().numpy(), want, mode=1, tol=1e-2)
+                bad, _, w = orc.check(full.cpu().numpy(), want, mode=1, tol=1e-2)
                 bad_total += bad
                 worst = max(worst, w)
-                if not torch.equal(got, full):
-                    bad_total += 1
-            op.release_outputs()
-        except Exception as exc:   # CUDA IPC between the ranks' processes is the one thing a box may not allow
-            if "could not be shared" not in str(exc):
-                raise
-            p2p = str(exc)
-        local = op.ctx.spmm_shard(op.prepared, Bs)     # [M, n_shard], no communication
-        bad, _, w = orc.check(local.cpu().numpy(), np.ascontiguousarray(want[lo:hi].T), mode=1, tol=1e-2)
-        assert op.prepared.device_status() == 0
-        q.put((rank, bad_total + bad, max(worst, w), p2p))
+            # peer-store form: the epilogue writes this rank's rows into both ranks' registered buffers; no exchange step.
+            # Same kernel and operands as the NCCL forms, so the bits must agree.  Two calls: the second overwrites the first.
+            shared = torch.zeros((N, M), dtype=torch.float16, device="cuda")
+            try:
+                for _ in range(2):
+                    got = op.gathered_p2p(Bs, N, shared)
+                    torch.cuda.synchronize()
+                    bad, _, w = orc.check(got.cpu().numpy(), want, mode=1, tol=1e-2)
+                    bad_total += bad
+                    worst = max(worst, w)
+                    if not torch.equal(got, full):
+                        bad_total += 1
+                op.release_outputs()
+            except Exception as exc:   # CUDA IPC between the ranks' processes is the one thing a box may not allow
+                if "could not be shared" not in str(exc):
+                    raise
+                p2p = str(exc)
+            local = op.ctx.spmm_shard(op.prepared, Bs)     # [M, n_shard], no communication
+            bad, _, w = orc.check(local.cpu().numpy(), np.ascontiguousarray(want[lo:hi].T), mode=1, tol=1e-2)
+            bad_total += bad
+            worst = max(worst, w)
+            assert op.prepared.device_status() == 0
+            assert op.prepared.dense_b_form() == (m == 8)
+        q.put((rank, bad_total, worst, p2p))
     finally:
         dist.destroy_process_group()
 

@@ -246,7 +246,8 @@ class Prepared:
         return out
 
     def spmm_multi(self, B, outs, bias=None, layout=VNM_LAYOUT_MN):
-        """One product stored to every tensor of `outs` (1 .. 8 tensors of one shape and stride; dense-B form only)."""
+        """One product stored to every tensor of `outs` (1 .. 8 tensors of one shape and stride; dense-B form, or gather form
+        with layout NM)."""
         _need_cuda(B, bias, *outs)
         if B.dtype != torch.float16 or B.dim() != 2 or B.shape[0] != self.K or B.stride(1) != 1:
             raise VenomError("B must be a [K,N] fp16 tensor with unit inner stride (K=%d)" % self.K)
@@ -314,7 +315,8 @@ class Prepared:
         _check(lib().vnm_set_l2_prefetch(self._h, ktiles_ahead))
 
     def set_epilogue(self, mode):
-        """0 = staged 128-bit stores (default), 1 = 32-bit stores per thread (ablation; gather form, layout MN)."""
+        """Gather form: 0 = default, 1 = 32-bit stores per thread for layout MN, 2 = layout NM through TMA stores also for a single
+        destination (ablations)."""
         _check(lib().vnm_set_epilogue(self._h, mode))
 
     def set_max_ctas(self, n):

@@ -154,6 +154,7 @@ struct vnm_prepared_s {
     int dense_b;       // 1: A re-expressed as 2:4 over all K columns, B read as plain tiles
     int out32;         // ablation: 32-bit epilogue stores (gather form, layout MN)
     int hybrid_rows;   // gather form: rows of every 64-row stage fetched by TMA gather4 beside the per-thread copies
+    int nm_tma_always; // gather kernel: 1 = the [N,M] result leaves through TMA stores even for a single destination (ablation: measured 1-4 % slower)
     int l2_ahead;      // pair kernel: k-tiles of L2 prefetch ahead of the shared-memory loads (0 = none)
     int pair_rows;     // pair kernel: 0 = row tiles per CTA chosen per problem, 1 / 2 = forced where possible (ablation)
     int l2_hints;      // pair kernel: 1 = ask L2 to keep the banded operand (default), 0 = no eviction-priority hints
@@ -355,9 +356,10 @@ int vnm_set_l2_prefetch(vnm_handle_t h, int ktiles_ahead)
 int vnm_set_epilogue(vnm_handle_t h, int mode)
 {
     if (!h) return fail(VNM_ERR_BAD_ARG, "null handle");
-    if (mode != 0 && mode != 1) return fail(VNM_ERR_BAD_ARG, "unknown epilogue mode %d", mode);
-    if (mode == 1 && h->dense_b) return fail(VNM_ERR_UNSUPPORTED, "the 32-bit epilogue exists for the V:N:M (gather) form only; this operand is held in dense-B form");
-    h->out32 = mode;
+    if (mode < 0 || mode > 2) return fail(VNM_ERR_BAD_ARG, "unknown epilogue mode %d", mode);
+    if (mode != 0 && h->dense_b) return fail(VNM_ERR_UNSUPPORTED, "the alternative epilogues exist for the V:N:M (gather) form only; this operand is held in dense-B form");
+    h->out32 = mode == 1;
+    h->nm_tma_always = mode == 2;
     return VNM_OK;
 }
 
@@ -410,8 +412,9 @@ static int spmm_impl(vnm_handle_t h, const void *B, int64_t ldb, int N, int b_nk
     if (!h || !B || !out) return fail(VNM_ERR_BAD_ARG, "vnm_spmm_f16: null pointer");
     if (n_more < 0 || n_more > MAX_OUTS - 1 || (n_more > 0 && !more_outs))
         return fail(VNM_ERR_BAD_ARG, "vnm_spmm_f16_multi: between 1 and %d destinations", MAX_OUTS);
-    if (n_more > 0 && !h->dense_b)
-        return fail(VNM_ERR_UNSUPPORTED, "vnm_spmm_f16_multi: several destinations need an operand prepared in dense-B form (TMA-store epilogue)");
+    if (n_more > 0 && !h->dense_b && (layout != VNM_LAYOUT_NM || ldo % 8 != 0 || ((uintptr_t)out & 15)))
+        return fail(VNM_ERR_UNSUPPORTED, "vnm_spmm_f16_multi: with an operand in gather form several destinations need layout NM, ldo %% 8 == 0 and "
+                                         "16-byte aligned buffers (only that epilogue leaves through TMA stores)");
     for (int d = 0; d < n_more; d++)
         if (!more_outs[d] || ((uintptr_t)more_outs[d] & 15)) return fail(VNM_ERR_BAD_ARG, "vnm_spmm_f16_multi: destination %d is null or not 16-byte aligned", d + 1);
     {
@@ -583,7 +586,31 @@ static int spmm_impl(vnm_handle_t h, const void *B, int64_t ldb, int N, int b_nk
         if (pair) VNM_CUDA(launch_spmm_dense_b_pair(cfg, h->tmap_tile, h->tmap_tile2, tmap_out, more, p, (cudaStream_t)stream), "spmm launch");
         else VNM_CUDA(launch_spmm_dense_b(cfg, h->tmap_tile, h->tmap_tile2, tmap_out, more, p, (cudaStream_t)stream), "spmm launch");
     } else {
-        VNM_CUDA(launch_spmm(cfg, h->tmap_rows, h->tmap_tile, p, (cudaStream_t)stream), "spmm launch");
+        // Gather form: the epilogue stores from registers.  Only a [N,M] result with several destinations (or on request)
+        // leaves through shared memory and TMA stores (boxes of 128 m x 32 n; needs ldo % 8 == 0 and 16-byte alignment):
+        // for a single destination that path measured 1-4 % slower.
+        CUtensorMap tmap_out;
+        OutMaps more;
+        memset(&tmap_out, 0, sizeof(tmap_out));
+        memset(&more, 0, sizeof(more));
+        p.nm_tma = 0;
+        if (layout == VNM_LAYOUT_NM && ldo % 8 == 0 && ((uintptr_t)out & 15) == 0 && (n_more > 0 || h->nm_tma_always)) {
+            cuuint32_t oestr[2] = {1, 1};
+            cuuint64_t ostrides[1] = {(cuuint64_t)ldo * 2};
+            cuuint64_t odims[2] = {(cuuint64_t)h->M, (cuuint64_t)N};
+            cuuint32_t obox[2] = {128, 32};
+            for (int d = 0; d <= n_more; d++) {
+                CUresult r = enc(d == 0 ? &tmap_out : &more.m[d - 1], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, d == 0 ? out : more_outs[d - 1], odims, ostrides, obox,
+                                 oestr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                if (r != CUDA_SUCCESS) return fail(VNM_ERR_CUDA, "cuTensorMapEncodeTiled (output %d) failed with CUresult %d", d, (int)r);
+            }
+            p.nm_tma = 1;
+            p.n_out = 1 + n_more;
+        } else if (n_more > 0) {
+            return fail(VNM_ERR_UNSUPPORTED, "vnm_spmm_f16_multi: the register-store epilogue of the gather form writes one destination");
+        }
+        VNM_CUDA(launch_spmm(cfg, h->tmap_rows, h->tmap_tile, tmap_out, more, p, (cudaStream_t)stream), "spmm launch");
     }
     return VNM_OK;
 }

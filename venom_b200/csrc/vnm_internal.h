@@ -37,7 +37,8 @@ struct SpmmParams {
     int b_nk;             // dense-B kernel only: the dense operand is given as [N, K] row-major (K contiguous)
     int b_wide_ok;        // dense-B kernel only: the 4-D tensor map exists (column tiles with 256 columns inside N use one box per stage)
     int l2_ahead;         // pair kernel: k-tiles by which L2 prefetches run ahead of the loads into shared memory (0 = none)
-    int n_out;            // dense-B kernels: destinations of every output tile (1 = `out` only; more: the OutMaps argument, e.g. peers' buffers)
+    int nm_tma;           // gather kernel, layout NM: the result leaves through shared memory and TMA stores (tmap_out / OutMaps valid)
+    int n_out;            // dense-B kernels, and the gather kernel with nm_tma: destinations of every output tile (1 = `out` only; more: the OutMaps argument, e.g. peers' buffers)
 };
 
 // Destinations 2 .. MAX_OUTS of a product whose every output tile is stored to several buffers of one geometry
@@ -90,7 +91,8 @@ cudaError_t launch_prune(const float *w, int64_t ldw, int M, int K, int V, int m
 bool spmm_select_config(int V, int N, int M, int producer_warps, int max_ctas, SpmmConfig *cfg);  // max_ctas: 0 = one per SM
 // Opt-in to large dynamic shared memory for every kernel instance on the CURRENT device (call once per device).
 cudaError_t spmm_init_kernels();
-cudaError_t launch_spmm(const SpmmConfig &cfg, const CUtensorMap &tmap_rows, const CUtensorMap &tmap_tile, const SpmmParams &p,
+cudaError_t launch_spmm(const SpmmConfig &cfg, const CUtensorMap &tmap_rows, const CUtensorMap &tmap_tile, const CUtensorMap &tmap_out,
+                        const OutMaps &more_out, const SpmmParams &p,
                         cudaStream_t stream);
 
 // Dense-B form: 256 x 128 tiles, two accumulators sharing every B stage (vnm_spmm_dense_b.cu).

@@ -522,10 +522,8 @@ int vnm_mgpu_spmm_gathered_p2p(vnm_mgpu_t c, vnm_handle_t h, const void *B_shard
     if (W > MAX_OUTS) return mfail(VNM_ERR_UNSUPPORTED, "vnm_mgpu_spmm_gathered_p2p: at most %d ranks", MAX_OUTS);
     if (N_total <= 0 || N_total % (8 * W) != 0)
         return mfail(VNM_ERR_UNSUPPORTED, "vnm_mgpu_spmm_gathered_p2p: N (%d) must be a multiple of 8 x ranks (%d)", N_total, 8 * W);
-    int M = 0, dense_b = 0;
+    int M = 0;
     if (int rc = vnm_handle_info(h, &M, nullptr, nullptr, nullptr, nullptr)) return rc;
-    if (int rc = vnm_operand_form(h, &dense_b)) return rc;
-    if (!dense_b) return mfail(VNM_ERR_UNSUPPORTED, "vnm_mgpu_spmm_gathered_p2p: the operand is not held in dense-B form (its epilogue has no TMA stores)");
     if (ldo != M) return mfail(VNM_ERR_UNSUPPORTED, "vnm_mgpu_spmm_gathered_p2p: the gathered [N, M] result must be dense (ldo == M = %d, got %lld)", M, (long long)ldo);
     const Registered *reg = nullptr;
     for (const Registered &r : c->registered)

@@ -15,6 +15,7 @@
 
 #include <cstdarg>
 #include <cstdio>
+#include <cstring>
 #include <mutex>
 
 using namespace vnm;
@@ -131,6 +132,7 @@ extern "C" int vnm_spmm_f16_noalloc(const void *values, const uint32_t *meta, co
     SpmmParams p;
     p.n_out = 1;
     p.l2_ahead = 0;
+    p.nm_tma = 0;
     p.am = (const uint8_t *)am;
     p.rows = (const int4 *)rows;
     p.bias = (const __half *)bias;
@@ -150,7 +152,13 @@ extern "C" int vnm_spmm_f16_noalloc(const void *values, const uint32_t *meta, co
     p.hybrid_rows = 0;
     p.b_nk = 0;
     p.b_wide_ok = 0;
-    e = launch_spmm(cfg, tmap_rows, tmap_tile, p, s);
+    {
+        CUtensorMap no_map;   // this entry point keeps the register-store epilogue: no output tensor maps
+        OutMaps no_maps;
+        memset(&no_map, 0, sizeof(no_map));
+        memset(&no_maps, 0, sizeof(no_maps));
+        e = launch_spmm(cfg, tmap_rows, tmap_tile, no_map, no_maps, p, s);
+    }
     if (e != cudaSuccess) return nfail(VNM_ERR_CUDA, "product launch: %s", cudaGetErrorString(e));
 
     // The status word lives in the shared scratch, so it is read back before the next call can clear it.

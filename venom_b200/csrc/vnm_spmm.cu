@@ -129,7 +129,8 @@ __device__ __forceinline__ void drain_slot(uint64_t *bar, uint32_t parity, int *
 
 template <int BN, int NB, int SA, int SB, int PB>
 __global__ void __launch_bounds__(Traits<BN, NB, SA, SB, PB>::NUM_THREADS, 1)
-    spmm_kernel(const __grid_constant__ CUtensorMap tmap_rows, const __grid_constant__ CUtensorMap tmap_tile, const SpmmParams p)
+    spmm_kernel(const __grid_constant__ CUtensorMap tmap_rows, const __grid_constant__ CUtensorMap tmap_tile, const __grid_constant__ CUtensorMap tmap_out,
+                const __grid_constant__ OutMaps more_out, const SpmmParams p)
 {
     using T = Traits<BN, NB, SA, SB, PB>;
     extern __shared__ uint8_t smem_raw[];
@@ -456,7 +457,13 @@ __global__ void __launch_bounds__(Traits<BN, NB, SA, SB, PB>::NUM_THREADS, 1)
             int mt, nt_cur;
             tile_coords(tile, p.mtiles, p.ntiles, p.group_m, &mt, &nt_cur);
             const int n0 = nt_cur * BN;
-            if (!wait_bounded(acc_full_bar, (uint32_t)ti & 1u, abort_flag, p.status, DEV_TIMEOUT_EPILOGUE)) break;
+            const bool nm_tma = p.layout == 1 && p.nm_tma != 0;   // [N,M] through shared memory and TMA stores (the four warps of a group meet at named barriers)
+            const bool got = wait_bounded(acc_full_bar, (uint32_t)ti & 1u, abort_flag, p.status, DEV_TIMEOUT_EPILOGUE);
+            if (nm_tma && !(BN / 64 < 2 && ew >= 4)) {
+                if (!named_barrier_and(1 + (ew >> 2), 128, got)) break;   // the group leaves the loop together
+            } else if (!got) {
+                break;
+            }
             tc_fence_after();
             // The tile is drained in parts of 64 columns to bound the register footprint; the
             // accumulator goes back to the MMA warp as soon as the last part is in registers.
@@ -496,7 +503,35 @@ __global__ void __launch_bounds__(Traits<BN, NB, SA, SB, PB>::NUM_THREADS, 1)
                     __syncwarp();
                     if (lane == 0) mbar_arrive(acc_empty_bar);
                 }
-                if (row_ok) {
+                if (nm_tma) {
+                    // [N,M] + bias: the group's 128 rows x 32 columns go through 8 KiB of shared memory as [n][m] and leave
+                    // as one TMA store per destination (boxes of 128 m x 32 n, clipped at M and N by the tensor map)
+                    const int grp = ew >> 2;
+                    uint8_t *stg = out_stage + grp * (4 * 32 * 64);
+                    const bool leader = (ew & 3) == 0 && lane == 0;
+#pragma unroll
+                    for (int sub = 0; sub < 2; sub++) {
+                        const int nsub = n0 + part * PART + sub * 32;
+                        if (leader) bulk_wait_group_read0();   // the previous store has finished reading the staging buffer
+                        named_barrier_sync(1 + grp, 128);
+                        __half *col = reinterpret_cast<__half *>(stg) + arow;
+#pragma unroll
+                        for (int jj = 0; jj < 16; jj++) {
+                            __half2 h = *reinterpret_cast<__half2 *>(&pk[sub * 16 + jj]);
+                            __half lo = __low2half(h), hi = __high2half(h);
+                            if (has_bias) { lo = __hadd(lo, bias); hi = __hadd(hi, bias); }
+                            col[(2 * jj) * TILE_M] = lo;
+                            col[(2 * jj + 1) * TILE_M] = hi;
+                        }
+                        fence_proxy_async();
+                        named_barrier_sync(1 + grp, 128);
+                        if (leader && nsub < p.N) {
+                            tma_store_2d(&tmap_out, stg, mt * TILE_M, nsub);
+                            for (int d = 1; d < p.n_out; d++) tma_store_2d(&more_out.m[d - 1], stg, mt * TILE_M, nsub);
+                            bulk_commit_group();
+                        }
+                    }
+                } else if (row_ok) {
                     const int nbase = n0 + part * PART;
                     if (p.layout == 0) {
                         // handled below, by the whole warp
@@ -553,6 +588,7 @@ __global__ void __launch_bounds__(Traits<BN, NB, SA, SB, PB>::NUM_THREADS, 1)
                 }
             }
         }
+        if (p.layout == 1 && p.nm_tma != 0 && (ew & 3) == 0 && lane == 0) bulk_wait_group0();  // stores read shared memory until they are done
     }
 
     tc_fence_before();
@@ -571,11 +607,11 @@ cudaError_t set_attr()
 }
 
 template <int BN, int NB, int SA, int SB, int PB>
-cudaError_t launch_one(const SpmmConfig &cfg, const CUtensorMap &tmap_rows, const CUtensorMap &tmap_tile, const SpmmParams &p,
-                       cudaStream_t stream)
+cudaError_t launch_one(const SpmmConfig &cfg, const CUtensorMap &tmap_rows, const CUtensorMap &tmap_tile, const CUtensorMap &tmap_out,
+                       const OutMaps &more_out, const SpmmParams &p, cudaStream_t stream)
 {
     using T = Traits<BN, NB, SA, SB, PB>;
-    spmm_kernel<BN, NB, SA, SB, PB><<<(unsigned)cfg.grid, T::NUM_THREADS, T::SMEM_BYTES, stream>>>(tmap_rows, tmap_tile, p);
+    spmm_kernel<BN, NB, SA, SB, PB><<<(unsigned)cfg.grid, T::NUM_THREADS, T::SMEM_BYTES, stream>>>(tmap_rows, tmap_tile, tmap_out, more_out, p);
     return cudaGetLastError();
 }
 
@@ -625,17 +661,17 @@ cudaError_t spmm_init_kernels()
     return cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
 }
 
-cudaError_t launch_spmm(const SpmmConfig &cfg, const CUtensorMap &tmap_rows, const CUtensorMap &tmap_tile, const SpmmParams &p,
-                        cudaStream_t stream)
+cudaError_t launch_spmm(const SpmmConfig &cfg, const CUtensorMap &tmap_rows, const CUtensorMap &tmap_tile, const CUtensorMap &tmap_out,
+                        const OutMaps &more_out, const SpmmParams &p, cudaStream_t stream)
 {
     if (cfg.stages == 4) {
-        if (cfg.nb == 1) return launch_one<256, 1, kSA, kSB, 4>(cfg, tmap_rows, tmap_tile, p, stream);
-        if (cfg.nb == 2) return launch_one<128, 2, kSA, kSB, 4>(cfg, tmap_rows, tmap_tile, p, stream);
-        if (cfg.nb == 4) return launch_one<64, 4, kSA, kSB, 4>(cfg, tmap_rows, tmap_tile, p, stream);
+        if (cfg.nb == 1) return launch_one<256, 1, kSA, kSB, 4>(cfg, tmap_rows, tmap_tile, tmap_out, more_out, p, stream);
+        if (cfg.nb == 2) return launch_one<128, 2, kSA, kSB, 4>(cfg, tmap_rows, tmap_tile, tmap_out, more_out, p, stream);
+        if (cfg.nb == 4) return launch_one<64, 4, kSA, kSB, 4>(cfg, tmap_rows, tmap_tile, tmap_out, more_out, p, stream);
     } else {
-        if (cfg.nb == 1) return launch_one<256, 1, kSA, kSB, 8>(cfg, tmap_rows, tmap_tile, p, stream);
-        if (cfg.nb == 2) return launch_one<128, 2, kSA, kSB, 8>(cfg, tmap_rows, tmap_tile, p, stream);
-        if (cfg.nb == 4) return launch_one<64, 4, kSA, kSB, 8>(cfg, tmap_rows, tmap_tile, p, stream);
+        if (cfg.nb == 1) return launch_one<256, 1, kSA, kSB, 8>(cfg, tmap_rows, tmap_tile, tmap_out, more_out, p, stream);
+        if (cfg.nb == 2) return launch_one<128, 2, kSA, kSB, 8>(cfg, tmap_rows, tmap_tile, tmap_out, more_out, p, stream);
+        if (cfg.nb == 4) return launch_one<64, 4, kSA, kSB, 8>(cfg, tmap_rows, tmap_tile, tmap_out, more_out, p, stream);
     }
     return cudaErrorInvalidValue;
 }

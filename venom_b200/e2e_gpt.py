@@ -97,6 +97,9 @@ def main(argv=None):
     ap.add_argument("--skip-dense", action="store_true")
     ap.add_argument("--gather-every-layer", action="store_true",
                     help="additionally all-gather the output of every linear (communication-bound variant; the gathered copies are discarded)")
+    ap.add_argument("--peer-store", action="store_true",
+                    help="with --gather-every-layer: no exchange step, every sparse linear stores its output tiles into all ranks' buffers "
+                         "(vnm_mgpu_spmm_gathered_p2p) instead of the chunked NCCL exchange")
     args = ap.parse_args(argv)
     if not torch.cuda.is_available():
         raise SystemExit("needs a CUDA device (there is no CPU path)")
@@ -129,6 +132,7 @@ def main(argv=None):
 
     hooks = []
     mgpu_ctx = None
+    shared_bufs = []   # result buffers registered for peer stores
 
     def install_gather_hooks():
         """The replicated copy of every linear's output, as a caller that does not shard the following op would need it.
@@ -157,7 +161,13 @@ def main(argv=None):
                 key = (ns * world, self.sp.nrows_sp)
                 if key not in bufs:
                     bufs[key] = torch.empty(key, dtype=flat.dtype, device=flat.device)
-                full = mgpu_ctx.spmm_gathered(self.prep, flat.t().contiguous(), ns * world, bias=self.sp.bias, out=bufs[key], chunks=4)
+                    if args.peer_store:
+                        mgpu_ctx.register_output(bufs[key])   # collective: every rank reaches a new shape at the same layer
+                        shared_bufs.append(bufs[key])
+                if args.peer_store:
+                    full = mgpu_ctx.spmm_gathered_p2p(self.prep, flat.t().contiguous(), ns * world, bufs[key], bias=self.sp.bias)
+                else:
+                    full = mgpu_ctx.spmm_gathered(self.prep, flat.t().contiguous(), ns * world, bias=self.sp.bias, out=bufs[key], chunks=4)
                 return full[rank * ns:(rank + 1) * ns].reshape(*x.shape[:-1], -1)
 
         for h in hooks:
@@ -205,12 +215,15 @@ def main(argv=None):
             line("0,0,", d_ms)
         line("%d,%d," % (args.n, args.m), s_ms)
         msg = "# %d GPUs%s, %d linears replaced (%s mask); %d:%d:%d %.0f tokens/s" % (
-            world, ", all-gather after every linear" if args.gather_every_layer and world > 1 else "", replaced,
+            world, (", every linear's output replicated by peer stores" if args.peer_store else ", all-gather after every linear") if args.gather_every_layer and world > 1 else "", replaced,
             "fixed" if args.fixed_mask else "magnitude", args.v, args.n, args.m, tokens / statistics.median(s_ms) * 1e3)
         if d_ms:
             msg += "; dense %.0f tokens/s, speed-up %.2fx" % (tokens / statistics.median(d_ms) * 1e3, statistics.median(d_ms) / statistics.median(s_ms))
         print(msg)
     if world > 1:
+        if args.peer_store and mgpu_ctx is not None:
+            for buf in shared_bufs:
+                mgpu_ctx.unregister_output(buf)
         dist.destroy_process_group()
     return (statistics.median(d_ms) if d_ms else None), statistics.median(s_ms)
 
