@@ -560,6 +560,7 @@ static int spmm_impl(vnm_handle_t h, const void *B, int64_t ldb, int N, int b_nk
     p.b_wide_ok = h->tm_wide ? 1 : 0;
     p.l2_ahead = h->l2_ahead;
     p.n_out = 1;
+    p.nm_tma = 0;
     if (h->dense_b) {
         // The result leaves through TMA stores: [M,N] as boxes of 40 columns x 128 rows, [N,M] as boxes of 128
         // columns (m) x 40 rows (n).

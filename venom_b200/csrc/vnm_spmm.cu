@@ -588,7 +588,7 @@ __global__ void __launch_bounds__(Traits<BN, NB, SA, SB, PB>::NUM_THREADS, 1)
                 }
             }
         }
-        if (p.layout == 1 && p.nm_tma != 0 && (ew & 3) == 0 && lane == 0) bulk_wait_group0();  // stores read shared memory until they are done
+        if (p.layout == 1 && p.nm_tma != 0 && (ew & 3) == 0 && lane == 0) bulk_wait_group_read0();  // the stores have read shared memory (their global writes complete with the grid)
     }
 
     tc_fence_before();

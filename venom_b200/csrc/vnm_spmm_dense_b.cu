@@ -382,7 +382,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_kernel(const __gr
         }
     }
 
-    if (warp >= EPI_WARP0 && ((warp - EPI_WARP0) & 3) == 0 && lane == 0) bulk_wait_group0();  // this thread's TMA stores are complete
+    if (warp >= EPI_WARP0 && ((warp - EPI_WARP0) & 3) == 0 && lane == 0) bulk_wait_group_read0();  // this thread's TMA stores have read shared memory (their global writes complete with the grid)
     tc_fence_before();
     __syncthreads();
     if (warp == 3) {

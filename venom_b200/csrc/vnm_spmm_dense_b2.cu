@@ -466,7 +466,6 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_pair_kernel(const
                 const bool row_ok = mt < p.mtiles && row < p.M;
                 const bool has_bias = p.layout == 1 && p.bias != nullptr;
                 const __half bias = (has_bias && row_ok) ? p.bias[row] : __ushort_as_half((unsigned short)0);
-                uint8_t *stg = out_ring + grp * OUT_STAGE_BYTES;
                 const bool leader = (warp == EPI_WARP0 + 4 * grp) && lane == 0;
                 const uint32_t trow = tmem_base + ((uint32_t)(q * 32) << 16) + acc_col(grp);
                 // 40 accumulator columns of this thread's row -> 20 registers of packed halves
@@ -486,11 +485,20 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_pair_kernel(const
                         pk[16 + jj] = *reinterpret_cast<uint32_t *>(&h1);
                     }
                 };
-                // one part -> staging buffer -> one TMA store (which clips at M and N)
+                // one part -> staging buffer -> one TMA store (which clips at M and N).  In the CTA's last tile nothing hides the
+                // stores behind later MMAs any more, and the operand rings are idle (every load has landed and every MMA that
+                // read them has completed, or this tile's accumulator would not be full): each part then gets a buffer of its
+                // own inside the rings, so no part waits for the previous store to release the staging buffer (final epilogue 9.6k ->
+                // 6.5k clocks; laying the six parts side by side and storing the 128 x 240 image at once measured slower, 8.1k).
+                const bool last_tile = ti == my_tiles - 1;
+                static_assert(RT * (BN / PART) * OUT_STAGE_BYTES <= A_RING_BYTES + B_RING_BYTES, "the last tile's staging does not fit into the rings");
                 auto store_part = [&](int part, const uint32_t *pk) {
                     const bool in_range = mt < p.mtiles && n0 + part * PART < p.N;
-                    if (leader) bulk_wait_group_read0();  // the previous store has finished reading the staging buffer
-                    named_barrier_sync(1 + grp, 128);
+                    uint8_t *stg = last_tile ? a_ring + (size_t)(grp * (BN / PART) + part) * OUT_STAGE_BYTES : out_ring + grp * OUT_STAGE_BYTES;
+                    if (!last_tile) {
+                        if (leader) bulk_wait_group_read0();  // the previous store has finished reading the staging buffer
+                        named_barrier_sync(1 + grp, 128);
+                    }
                     if (p.layout == 0) {
 #pragma unroll
                         for (int c = 0; c < PART / 8; c++)
@@ -536,7 +544,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) spmm_dense_b_pair_kernel(const
         }
     }
 
-    if (warp >= EPI_WARP0 && ((warp - EPI_WARP0) & 3) == 0 && lane == 0) bulk_wait_group0();  // this thread's TMA stores are complete
+    if (warp >= EPI_WARP0 && ((warp - EPI_WARP0) & 3) == 0 && lane == 0) bulk_wait_group_read0();  // this thread's TMA stores have read shared memory (their global writes complete with the grid)
     tc_fence_before();
     __syncthreads();
     cluster_sync_all();  // the peer's shared and tensor memory stay alive until the leader's last MMA and commit are done
